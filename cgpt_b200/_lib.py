@@ -1,0 +1,118 @@
+"""ctypes binding of ``libcgpt_b200.so`` (the C ABI declared in ``include/cgpt_b200.h``).
+
+There is no fallback: if the shared library is missing the import fails with the build command to
+run, and every op raises if the library reports an error.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import torch  # noqa: F401  (loads libcudart.so.12 first so the library binds to the same runtime)
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "libcgpt_b200.so"
+
+F16, BF16, F32 = 0, 1, 2
+_TORCH_TO_CODE = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32}
+
+ERRORS = {
+    1: "null pointer", 2: "unsupported dtype", 3: "invalid shape", 4: "invalid option",
+    5: "misaligned pointer", 6: "unsupported configuration", 7: "invalid state",
+    8: "device-side wait timed out",
+}
+
+
+class CgptError(RuntimeError):
+    """A CUDA runtime/driver failure reported by the library (negative status)."""
+
+
+class CgptInvalidArgument(ValueError):
+    """An argument error class reported by the library (positive status); the reference throws
+    std::invalid_argument for the same conditions."""
+
+
+def _load() -> C.CDLL:
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m cgpt_b200.build` (needs nvcc; no GPU required). "
+            "cgpt_b200 has no CPU or PyTorch fallback."
+        )
+    return C.CDLL(str(LIB_PATH), mode=C.RTLD_GLOBAL)
+
+
+lib = _load()
+
+_vp, _sz, _i, _f, _u64 = C.c_void_p, C.c_size_t, C.c_int, C.c_float, C.c_uint64
+
+
+class AdamWTensor(C.Structure):
+    _fields_ = [("param", _vp), ("grad", _vp), ("master", _vp), ("m", _vp), ("v", _vp),
+                ("count", C.c_uint64), ("dtype", C.c_int32), ("reserved", C.c_int32)]
+
+
+class AdamWOptions(C.Structure):
+    _fields_ = [("learning_rate", _f), ("beta1", _f), ("beta2", _f), ("epsilon", _f),
+                ("weight_decay", _f), ("loss_scale", _f), ("max_grad_norm", _f)]
+
+
+SIGNATURES = {
+    "cgpt_b200_version": (C.c_char_p, []),
+    "cgpt_b200_launch_count": (C.c_uint64, []),
+    "cgpt_rmsnorm_forward": (_i, [_vp, _vp, _vp, _sz, _sz, _f, _i, _vp]),
+    "cgpt_rmsnorm_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _f, _i, _vp]),
+    "cgpt_rope_forward": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _i, _vp]),
+    "cgpt_rope_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _i, _vp]),
+    "cgpt_swiglu_forward": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),
+    "cgpt_swiglu_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _vp]),
+    "cgpt_embedding_forward": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _i, _vp]),
+    "cgpt_embedding_backward": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _i, _i, _i, _vp]),
+    "cgpt_add": (_i, [_vp, _vp, _vp, _vp, _sz, _i, _vp]),
+    "cgpt_cross_entropy": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _f, _i, _vp]),
+    "cgpt_adamw_create": (_i, [C.POINTER(_vp), C.POINTER(AdamWTensor), _sz, _u64, _vp]),
+    "cgpt_adamw_destroy": (_i, [_vp]),
+    "cgpt_adamw_step": (_i, [_vp, C.POINTER(AdamWOptions), _vp]),
+    "cgpt_adamw_check": (_i, [_vp, C.POINTER(_u64), C.POINTER(_i), _vp]),
+    "cgpt_adamw_last_stats": (_i, [_vp, C.POINTER(_f), C.POINTER(_f), _vp]),
+}
+
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def check(status: int, what: str) -> None:
+    """Raises for a non-zero status of a library call."""
+    if status == 0:
+        return
+    if status > 0:
+        raise CgptInvalidArgument(f"{what}: {ERRORS.get(status, 'error ' + str(status))}")
+    raise CgptError(f"{what}: CUDA error {-status}")
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _TORCH_TO_CODE[t.dtype]
+    except KeyError:
+        raise CgptInvalidArgument(f"unsupported dtype {t.dtype}") from None
+
+
+def ptr(t) -> int | None:
+    """Device pointer of a tensor (None passes NULL)."""
+    if t is None:
+        return None
+    if not t.is_contiguous():
+        raise CgptInvalidArgument("tensor must be contiguous")
+    return t.data_ptr()
+
+
+def stream_ptr(stream=None) -> int:
+    """cudaStream_t of `stream` (a torch.cuda.Stream) or of torch's current stream."""
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    return stream.cuda_stream
+
+
+def launch_count() -> int:
+    return int(lib.cgpt_b200_launch_count())

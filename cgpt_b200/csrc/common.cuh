@@ -1,0 +1,138 @@
+// Shared device/host helpers for the cgpt_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/cgpt_b200.h"
+
+namespace cgpt {
+
+constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs; grids are sized in multiples of this.
+
+// ---------------------------------------------------------------------------------------------
+// Status helpers. Every C-ABI entry point returns 0, a positive CGPT_ERR_* argument class, or
+// the negated cudaError_t of the failing runtime call. Nothing throws and nothing exits.
+// ---------------------------------------------------------------------------------------------
+inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? CGPT_OK : -static_cast<int>(e); }
+
+#define CGPT_CUDA_TRY(expr)                                        \
+    do {                                                           \
+        cudaError_t cgpt_err__ = (expr);                           \
+        if (cgpt_err__ != cudaSuccess) return -static_cast<int>(cgpt_err__); \
+    } while (0)
+
+#define CGPT_TRY(expr)                      \
+    do {                                    \
+        int cgpt_rc__ = (expr);             \
+        if (cgpt_rc__ != CGPT_OK) return cgpt_rc__; \
+    } while (0)
+
+#define CGPT_LAUNCH_CHECK() CGPT_CUDA_TRY(cudaGetLastError())
+
+inline bool valid_float_dtype(int dtype) {
+    return dtype == CGPT_DTYPE_F16 || dtype == CGPT_DTYPE_BF16 || dtype == CGPT_DTYPE_F32;
+}
+inline std::size_t dtype_size(int dtype) { return dtype == CGPT_DTYPE_F32 ? 4 : 2; }
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<std::uintptr_t>(p) & 15u) == 0; }
+
+// Per-device scratch arena owned by the library. Grown with cudaMalloc on first use (never during
+// stream capture: a growth request while the stream is capturing returns an error instead).
+// Every kernel that needs global scratch and was not handed a caller workspace takes it from here.
+int scratch_get(void** out, std::size_t bytes, cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------
+// Scalar conversion
+// ---------------------------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// ---------------------------------------------------------------------------------------------
+// Vector access: N consecutive elements of T moved with the widest possible single instruction
+// (16 bytes for N*sizeof(T) == 16). The address must be aligned to N*sizeof(T).
+// ---------------------------------------------------------------------------------------------
+template <int BYTES> struct RawVec;
+template <> struct RawVec<2> { using type = unsigned short; };
+template <> struct RawVec<4> { using type = unsigned int; };
+template <> struct RawVec<8> { using type = uint2; };
+template <> struct RawVec<16> { using type = uint4; };
+template <> struct RawVec<32> { using type = ulonglong4; };
+
+template <typename T, int N>
+struct alignas(sizeof(T) * N) Pack {
+    T v[N];
+};
+
+template <typename T, int N>
+__device__ __forceinline__ void load_vec(float (&out)[N], const T* __restrict__ p) {
+    using Raw = typename RawVec<sizeof(T) * N>::type;
+    Pack<T, N> pk;
+    *reinterpret_cast<Raw*>(&pk) = *reinterpret_cast<const Raw*>(p);
+#pragma unroll
+    for (int i = 0; i < N; ++i) out[i] = to_f32<T>(pk.v[i]);
+}
+
+// Streaming (read-once) variant: bypasses L1 allocation.
+template <typename T, int N>
+__device__ __forceinline__ void load_vec_stream(float (&out)[N], const T* __restrict__ p) {
+    using Raw = typename RawVec<sizeof(T) * N>::type;
+    Pack<T, N> pk;
+    *reinterpret_cast<Raw*>(&pk) = __ldcs(reinterpret_cast<const Raw*>(p));
+#pragma unroll
+    for (int i = 0; i < N; ++i) out[i] = to_f32<T>(pk.v[i]);
+}
+
+template <typename T, int N>
+__device__ __forceinline__ void store_vec(T* __restrict__ p, const float (&in)[N]) {
+    using Raw = typename RawVec<sizeof(T) * N>::type;
+    Pack<T, N> pk;
+#pragma unroll
+    for (int i = 0; i < N; ++i) pk.v[i] = from_f32<T>(in[i]);
+    *reinterpret_cast<Raw*>(p) = *reinterpret_cast<const Raw*>(&pk);
+}
+
+template <typename T, int N>
+__device__ __forceinline__ void store_vec_stream(T* __restrict__ p, const float (&in)[N]) {
+    using Raw = typename RawVec<sizeof(T) * N>::type;
+    Pack<T, N> pk;
+#pragma unroll
+    for (int i = 0; i < N; ++i) pk.v[i] = from_f32<T>(in[i]);
+    __stcs(reinterpret_cast<Raw*>(p), *reinterpret_cast<const Raw*>(&pk));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Reductions
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Dispatch a lambda-like macro body over the storage dtype.
+#define CGPT_DISPATCH_DTYPE(dtype, T, ...)                       \
+    switch (dtype) {                                             \
+        case CGPT_DTYPE_F16: { using T = __half; __VA_ARGS__; break; }        \
+        case CGPT_DTYPE_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; } \
+        case CGPT_DTYPE_F32: { using T = float; __VA_ARGS__; break; }          \
+        default: return CGPT_ERR_DTYPE;                          \
+    }
+
+}  // namespace cgpt

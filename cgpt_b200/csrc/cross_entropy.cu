@@ -1,0 +1,145 @@
+// Softmax cross-entropy on materialised logits (loss + gradient) for sm_100a.
+//
+// Math follows the reference kernel (src/ops/cross_entropy.cu:134-245): per row max, sum of
+// __expf(logit - max), loss_row = __logf(sum) + max - logit[target], grad = (__expf(logit - max) *
+// __frcp_rn(sum) - onehot) * (1/rows) * gradient_scale; a row whose target is outside the vocabulary
+// contributes no loss and gets no -1. The reference adds row losses with a float atomicAdd; here row
+// losses go to scratch and one CTA sums them in a fixed order, so the loss is reproducible.
+//
+// Memory-bound: the row is staged once in shared memory (up to 200 KB) so logits are read from HBM
+// once and the gradient written once: 2 * rows * vocab * sizeof(T) algorithmic bytes.
+#include <math_constants.h>
+
+#include "common.cuh"
+#include "launch_counter.h"
+
+namespace cgpt {
+namespace {
+
+constexpr int kCeThreads = 512;
+constexpr int kCeWarps = kCeThreads / 32;
+
+__device__ __forceinline__ float block_max_512(float v, float* red) {
+    v = warp_max(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = red[0];
+#pragma unroll
+    for (int i = 1; i < kCeWarps; ++i) r = fmaxf(r, red[i]);
+    return r;
+}
+__device__ __forceinline__ float block_sum_512(float v, float* red) {
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = 0.f;
+#pragma unroll
+    for (int i = 0; i < kCeWarps; ++i) r += red[i];
+    return r;
+}
+
+template <typename T, bool STAGED>
+__global__ void __launch_bounds__(kCeThreads)
+cross_entropy_kernel(float* __restrict__ row_loss, T* __restrict__ grad, const T* __restrict__ logits,
+                     const std::uint32_t* __restrict__ targets, long long rows, int vocab, float inv_rows,
+                     float gradient_scale) {
+    extern __shared__ __align__(16) unsigned char ce_smem[];
+    __shared__ float red[kCeWarps];
+    T* staged = reinterpret_cast<T*>(ce_smem);
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* src = logits + row * vocab;
+        float local_max = -CUDART_INF_F;
+        for (int c = threadIdx.x; c < vocab; c += kCeThreads) {
+            const T raw = src[c];
+            if (STAGED) staged[c] = raw;
+            local_max = fmaxf(local_max, to_f32<T>(raw));
+        }
+        const float maximum = block_max_512(local_max, red);  // also orders the staging writes
+        const T* cached = STAGED ? staged : src;
+        float local_sum = 0.f;
+        for (int c = threadIdx.x; c < vocab; c += kCeThreads) local_sum += __expf(to_f32<T>(cached[c]) - maximum);
+        const float denominator = block_sum_512(local_sum, red);
+        const float inv_denominator = __frcp_rn(denominator);
+        const std::uint32_t target = targets[row];
+        const bool valid = target < static_cast<std::uint32_t>(vocab);
+        if (threadIdx.x == 0) {
+            row_loss[row] = valid ? (__logf(denominator) + maximum - to_f32<T>(cached[target])) * inv_rows : 0.f;
+        }
+        if (grad != nullptr) {
+            T* dst = grad + row * vocab;
+            for (int c = threadIdx.x; c < vocab; c += kCeThreads) {
+                float v = __expf(to_f32<T>(cached[c]) - maximum) * inv_denominator;
+                if (valid && static_cast<std::uint32_t>(c) == target) v -= 1.0f;
+                dst[c] = from_f32<T>(v * inv_rows * gradient_scale);
+            }
+        }
+        __syncthreads();  // staged row is reused by the next iteration
+    }
+}
+
+// Fixed-order sum of n floats by one CTA.
+__global__ void __launch_bounds__(1024)
+sum_floats_kernel(float* __restrict__ out, const float* __restrict__ in, long long n) {
+    __shared__ float red[32];
+    float acc = 0.f;
+    for (long long i = threadIdx.x; i < n; i += 1024) acc += in[i];
+    acc = warp_sum(acc);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = red[threadIdx.x];
+        v = warp_sum(v);
+        if (threadIdx.x == 0) *out = v;
+    }
+}
+
+}  // namespace
+
+// Shared with the fused LM-head loss: deterministic sum of per-row losses into loss[0].
+int sum_floats(float* out, const float* in, long long n, cudaStream_t s) {
+    sum_floats_kernel<<<1, 1024, 0, s>>>(out, in, n);
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+    return CGPT_OK;
+}
+
+}  // namespace cgpt
+
+using namespace cgpt;
+
+extern "C" int cgpt_cross_entropy(float* loss, void* grad, const void* logits, const uint32_t* targets,
+                                  size_t rows, size_t vocab, float gradient_scale, int dtype,
+                                  cgpt_stream_t stream) {
+    if (!loss || !logits || !targets) return CGPT_ERR_NULL;
+    if (!valid_float_dtype(dtype)) return CGPT_ERR_DTYPE;
+    if (rows == 0 || vocab == 0 || vocab > 0x7fffffffull || rows > (1ull << 40)) return CGPT_ERR_SHAPE;
+    auto s = static_cast<cudaStream_t>(stream);
+    void* scratch = nullptr;
+    CGPT_TRY(scratch_get(&scratch, rows * sizeof(float), s));
+    const float inv_rows = 1.0f / static_cast<float>(rows);
+    const std::size_t row_bytes = vocab * dtype_size(dtype);
+    const bool staged = row_bytes <= 200 * 1024;
+    const unsigned grid = static_cast<unsigned>(rows < kNumSMs * 4ull ? rows : kNumSMs * 4ull);
+    CGPT_DISPATCH_DTYPE(dtype, T, {
+        if (staged) {
+            static bool attr_done[3] = {false, false, false};
+            if (!attr_done[dtype]) {
+                CGPT_CUDA_TRY(cudaFuncSetAttribute(cross_entropy_kernel<T, true>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+                attr_done[dtype] = true;
+            }
+            cross_entropy_kernel<T, true><<<grid, kCeThreads, row_bytes, s>>>(
+                static_cast<float*>(scratch), static_cast<T*>(grad), static_cast<const T*>(logits), targets,
+                static_cast<long long>(rows), static_cast<int>(vocab), inv_rows, gradient_scale);
+        } else {
+            cross_entropy_kernel<T, false><<<grid, kCeThreads, 0, s>>>(
+                static_cast<float*>(scratch), static_cast<T*>(grad), static_cast<const T*>(logits), targets,
+                static_cast<long long>(rows), static_cast<int>(vocab), inv_rows, gradient_scale);
+        }
+        count_launch();
+        CGPT_LAUNCH_CHECK();
+    });
+    return sum_floats(loss, static_cast<const float*>(scratch), static_cast<long long>(rows), s);
+}

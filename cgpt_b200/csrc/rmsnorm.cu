@@ -1,0 +1,347 @@
+// RMSNorm forward and fused backward (dx + dw in one pass over x and dy) for sm_100a.
+//
+// Math follows the reference kernels: forward  y = x * inv * w  with inv = rsqrtf(mean(x^2) + eps)
+// (src/ops/rmsnorm.cu:60,122-125 of the reference); backward
+//   c  = sum(dy*w*x) / hidden * inv^3,  dx = fma(-x, c, dy*w*inv)      (rmsnorm_backward.cu:276-293)
+//   dw = sum_rows dy * (x*inv)                                          (rmsnorm_backward.cu:374-398)
+//
+// Memory-bound. Layout of work: a row is owned by `wpr` whole warps (1, 2, 4 or 8); a CTA of 256
+// threads therefore works on 8/wpr rows at a time and walks the rows with a grid stride. Each thread
+// keeps its CPT*VEC elements of x and dy in registers (one 16-byte load each for 16-bit types), so x
+// and dy are read from HBM exactly once. The thread's columns are the same for every row it visits,
+// which lets it accumulate its dw contributions in registers over the whole row loop; per-CTA
+// partials go to a [grid, hidden] fp32 scratch and a second, tiny kernel sums them in a fixed order
+// (deterministic, no atomics). Algorithmic HBM bytes per row: 3 * hidden * sizeof(T)
+// (+ hidden * sizeof(T) per residual operand).
+#include "common.cuh"
+#include "launch_counter.h"
+
+namespace cgpt {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+// Sum over the `wpr` warps that share a row. `slot` is this row group's index inside the CTA.
+// All threads of the CTA must call this (it contains __syncthreads()).
+template <int NV>
+__device__ __forceinline__ void row_group_sum(float (&vals)[NV], int wpr, int warp_in_row, int slot,
+                                              float* smem /* [kWarps * NV] */) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) vals[i] = warp_sum(vals[i]);
+    if (wpr == 1) return;
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    __syncthreads();  // protect smem reuse across successive calls
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) smem[warp * NV + i] = vals[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        float acc = 0.f;
+        for (int w = 0; w < wpr; ++w) acc += smem[(slot * wpr + w) * NV + i];
+        vals[i] = acc;
+    }
+    (void)warp_in_row;
+}
+
+template <typename T, int VEC, int CPT>
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_forward_kernel(T* __restrict__ y, const T* __restrict__ x, const T* __restrict__ w,
+                       long long rows, int hidden, float epsilon, int wpr) {
+    __shared__ float red[kWarps];
+    const int tpr = wpr * 32;
+    const int rows_per_cta = kWarps / wpr;
+    const int slot = threadIdx.x / tpr;
+    const int tid_in_row = threadIdx.x % tpr;
+    const float inv_hidden = 1.0f / static_cast<float>(hidden);
+
+    float wv[CPT][VEC];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        const int col = (c * tpr + tid_in_row) * VEC;
+        if (col < hidden) load_vec<T, VEC>(wv[c], w + col);
+        else {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) wv[c][i] = 0.f;
+        }
+    }
+    const long long row_step = static_cast<long long>(gridDim.x) * rows_per_cta;
+    const long long iters = (rows + row_step - 1) / row_step;
+    for (long long it = 0; it < iters; ++it) {
+        const long long row = it * row_step + static_cast<long long>(blockIdx.x) * rows_per_cta + slot;
+        const bool active = row < rows;
+        float xv[CPT][VEC];
+        float ss[1] = {0.f};
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+            const int col = (c * tpr + tid_in_row) * VEC;
+            if (active && col < hidden) {
+                load_vec_stream<T, VEC>(xv[c], x + row * hidden + col);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) ss[0] = fmaf(xv[c][i], xv[c][i], ss[0]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) xv[c][i] = 0.f;
+            }
+        }
+        row_group_sum<1>(ss, wpr, 0, slot, red);
+        const float inv = rsqrtf(ss[0] * inv_hidden + epsilon);
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+            const int col = (c * tpr + tid_in_row) * VEC;
+            if (active && col < hidden) {
+                float out[VEC];
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) out[i] = xv[c][i] * inv * wv[c][i];
+                store_vec<T, VEC>(y + row * hidden + col, out);
+            }
+        }
+    }
+}
+
+template <typename T, int VEC, int CPT>
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_backward_kernel(T* __restrict__ dx, float* __restrict__ dw_partial,
+                        const T* __restrict__ dy, const T* __restrict__ x,
+                        const T* __restrict__ w, const T* __restrict__ res_a,
+                        const T* __restrict__ res_b, long long rows, int hidden, float epsilon,
+                        int wpr) {
+    __shared__ float red[kWarps * 2];
+    const int tpr = wpr * 32;
+    const int rows_per_cta = kWarps / wpr;
+    const int slot = threadIdx.x / tpr;
+    const int tid_in_row = threadIdx.x % tpr;
+    const float inv_hidden = 1.0f / static_cast<float>(hidden);
+
+    float wv[CPT][VEC], dwacc[CPT][VEC];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        const int col = (c * tpr + tid_in_row) * VEC;
+        if (col < hidden) load_vec<T, VEC>(wv[c], w + col);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            if (col >= hidden) wv[c][i] = 0.f;
+            dwacc[c][i] = 0.f;
+        }
+    }
+
+    const long long row_step = static_cast<long long>(gridDim.x) * rows_per_cta;
+    const long long iters = (rows + row_step - 1) / row_step;
+    for (long long it = 0; it < iters; ++it) {
+        const long long row = it * row_step + static_cast<long long>(blockIdx.x) * rows_per_cta + slot;
+        const bool active = row < rows;
+        float xv[CPT][VEC], gv[CPT][VEC];
+        float sums[2] = {0.f, 0.f};  // sum x^2, sum dy*w*x
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+            const int col = (c * tpr + tid_in_row) * VEC;
+            if (active && col < hidden) {
+                load_vec_stream<T, VEC>(xv[c], x + row * hidden + col);
+                load_vec_stream<T, VEC>(gv[c], dy + row * hidden + col);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) {
+                    sums[0] = fmaf(xv[c][i], xv[c][i], sums[0]);
+                    sums[1] = fmaf(gv[c][i] * wv[c][i], xv[c][i], sums[1]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) { xv[c][i] = 0.f; gv[c][i] = 0.f; }
+            }
+        }
+        row_group_sum<2>(sums, wpr, 0, slot, red);
+        const float inv = rsqrtf(sums[0] * inv_hidden + epsilon);
+        const float corr = sums[1] * inv_hidden * inv * inv * inv;
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+            const int col = (c * tpr + tid_in_row) * VEC;
+            if (active && col < hidden) {
+                float out[VEC];
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) {
+                    out[i] = fmaf(-xv[c][i], corr, gv[c][i] * wv[c][i] * inv);
+                    dwacc[c][i] = fmaf(gv[c][i], xv[c][i] * inv, dwacc[c][i]);
+                }
+                if (res_a != nullptr) {
+                    float r[VEC];
+                    load_vec_stream<T, VEC>(r, res_a + row * hidden + col);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) out[i] += r[i];
+                }
+                if (res_b != nullptr) {
+                    float r[VEC];
+                    load_vec_stream<T, VEC>(r, res_b + row * hidden + col);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) out[i] += r[i];
+                }
+                store_vec<T, VEC>(dx + row * hidden + col, out);
+            }
+        }
+    }
+
+    // Combine the CTA's row slots (fixed order) and publish one fp32 partial row per CTA.
+    __shared__ float slots[kThreads];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            __syncthreads();
+            slots[threadIdx.x] = dwacc[c][i];
+            __syncthreads();
+            if (slot == 0) {
+                const int col = (c * tpr + tid_in_row) * VEC + i;
+                if (col < hidden) {
+                    float acc = 0.f;
+                    for (int s = 0; s < rows_per_cta; ++s) acc += slots[s * tpr + tid_in_row];
+                    dw_partial[static_cast<long long>(blockIdx.x) * hidden + col] = acc;
+                }
+            }
+        }
+    }
+}
+
+// dw[col] = sum over partial rows, in a fixed tree order: each thread sums a strided subset, then the
+// CTA's 8 row-lanes are combined through shared memory.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_dw_reduce_kernel(T* __restrict__ dw, const float* __restrict__ partial, int parts, int hidden) {
+    __shared__ float tile[8][33];
+    const int col = blockIdx.x * 32 + (threadIdx.x & 31);
+    const int lane_row = threadIdx.x >> 5;
+    float acc = 0.f;
+    if (col < hidden) {
+        for (int p = lane_row; p < parts; p += 8) acc += partial[static_cast<long long>(p) * hidden + col];
+    }
+    tile[lane_row][threadIdx.x & 31] = acc;
+    __syncthreads();
+    if (lane_row == 0 && col < hidden) {
+        float total = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) total += tile[r][threadIdx.x & 31];
+        dw[col] = from_f32<T>(total);
+    }
+}
+
+struct Plan {
+    int vec, cpt, wpr;
+};
+
+// Chooses vector width, chunks per thread and warps per row. Returns false if hidden is too large
+// for the register-cached layout.
+template <typename T>
+bool make_plan(std::size_t hidden, bool all_aligned16, Plan* plan) {
+    constexpr int kMaxVec = 16 / sizeof(T);
+    int vec = (all_aligned16 && hidden % kMaxVec == 0) ? kMaxVec : 1;
+    if (vec == 8 && hidden <= 128 && hidden % 4 == 0) vec = 4;  // keep all 32 lanes busy on head_dim rows
+    const std::size_t chunks = (hidden + vec - 1) / vec;
+    int wpr = 1;
+    while (wpr < kWarps && chunks > static_cast<std::size_t>(wpr) * 32) wpr *= 2;
+    const std::size_t per_thread = (chunks + wpr * 32 - 1) / (wpr * 32);
+    int cpt = 1;
+    while (cpt < static_cast<int>(per_thread)) cpt *= 2;
+    if (cpt > 4) return false;
+    *plan = {vec, cpt, wpr};
+    return true;
+}
+
+int grid_for(std::size_t rows, int wpr, int ctas_per_sm) {
+    const std::size_t rows_per_cta = kWarps / wpr;
+    const std::size_t need = (rows + rows_per_cta - 1) / rows_per_cta;
+    const std::size_t cap = static_cast<std::size_t>(kNumSMs) * ctas_per_sm;
+    return static_cast<int>(need < cap ? (need == 0 ? 1 : need) : cap);
+}
+
+template <typename T, int VEC>
+int launch_forward(void* y, const void* x, const void* w, std::size_t rows, std::size_t hidden,
+                   float eps, const Plan& p, cudaStream_t s) {
+    const int grid = grid_for(rows, p.wpr, 8);
+#define CGPT_RMS_FWD(CPT)                                                                      \
+    rmsnorm_forward_kernel<T, VEC, CPT><<<grid, kThreads, 0, s>>>(                              \
+        static_cast<T*>(y), static_cast<const T*>(x), static_cast<const T*>(w),               \
+        static_cast<long long>(rows), static_cast<int>(hidden), eps, p.wpr)
+    switch (p.cpt) {
+        case 1: CGPT_RMS_FWD(1); break;
+        case 2: CGPT_RMS_FWD(2); break;
+        default: CGPT_RMS_FWD(4); break;
+    }
+#undef CGPT_RMS_FWD
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+    return CGPT_OK;
+}
+
+template <typename T, int VEC>
+int launch_backward(void* dx, void* dw, const void* dy, const void* x, const void* w,
+                    const void* ra, const void* rb, std::size_t rows, std::size_t hidden, float eps,
+                    const Plan& p, cudaStream_t s) {
+    const int grid = grid_for(rows, p.wpr, 4);
+    void* scratch = nullptr;
+    CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(grid) * hidden * sizeof(float), s));
+#define CGPT_RMS_BWD(CPT)                                                                       \
+    rmsnorm_backward_kernel<T, VEC, CPT><<<grid, kThreads, 0, s>>>(                              \
+        static_cast<T*>(dx), static_cast<float*>(scratch), static_cast<const T*>(dy),          \
+        static_cast<const T*>(x), static_cast<const T*>(w), static_cast<const T*>(ra),         \
+        static_cast<const T*>(rb), static_cast<long long>(rows), static_cast<int>(hidden), eps, p.wpr)
+    switch (p.cpt) {
+        case 1: CGPT_RMS_BWD(1); break;
+        case 2: CGPT_RMS_BWD(2); break;
+        default: CGPT_RMS_BWD(4); break;
+    }
+#undef CGPT_RMS_BWD
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+    rmsnorm_dw_reduce_kernel<T><<<static_cast<unsigned>((hidden + 31) / 32), 256, 0, s>>>(
+        static_cast<T*>(dw), static_cast<const float*>(scratch), grid, static_cast<int>(hidden));
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+    return CGPT_OK;
+}
+
+}  // namespace
+}  // namespace cgpt
+
+using namespace cgpt;
+
+extern "C" int cgpt_rmsnorm_forward(void* y, const void* x, const void* w, size_t rows, size_t hidden,
+                                    float epsilon, int dtype, cgpt_stream_t stream) {
+    if (!y || !x || !w) return CGPT_ERR_NULL;
+    if (!valid_float_dtype(dtype)) return CGPT_ERR_DTYPE;
+    if (rows == 0 || hidden == 0 || hidden > 0x7fffffffull || rows > (1ull << 40)) return CGPT_ERR_SHAPE;
+    if (!(epsilon > 0.f)) return CGPT_ERR_OPTION;
+    auto s = static_cast<cudaStream_t>(stream);
+    const bool al = aligned16(y) && aligned16(x) && aligned16(w);
+    CGPT_DISPATCH_DTYPE(dtype, T, {
+        Plan p;
+        if (!make_plan<T>(hidden, al, &p)) return CGPT_ERR_UNSUPPORTED;
+        constexpr int kMaxVec = 16 / sizeof(T);
+        if (p.vec == kMaxVec) return launch_forward<T, kMaxVec>(y, x, w, rows, hidden, epsilon, p, s);
+        if (p.vec == 4) return launch_forward<T, 4>(y, x, w, rows, hidden, epsilon, p, s);
+        return launch_forward<T, 1>(y, x, w, rows, hidden, epsilon, p, s);
+    });
+    return CGPT_OK;
+}
+
+extern "C" int cgpt_rmsnorm_backward(void* dx, void* dw, const void* dy, const void* x, const void* w,
+                                     const void* residual_a, const void* residual_b, size_t rows,
+                                     size_t hidden, float epsilon, int dtype, cgpt_stream_t stream) {
+    if (!dx || !dw || !dy || !x || !w) return CGPT_ERR_NULL;
+    if (!valid_float_dtype(dtype)) return CGPT_ERR_DTYPE;
+    if (rows == 0 || hidden == 0 || hidden > 0x7fffffffull || rows > (1ull << 40)) return CGPT_ERR_SHAPE;
+    if (!(epsilon > 0.f)) return CGPT_ERR_OPTION;
+    auto s = static_cast<cudaStream_t>(stream);
+    const bool al = aligned16(dx) && aligned16(dy) && aligned16(x) && aligned16(w) &&
+                    aligned16(residual_a) && aligned16(residual_b);
+    CGPT_DISPATCH_DTYPE(dtype, T, {
+        Plan p;
+        if (!make_plan<T>(hidden, al, &p)) return CGPT_ERR_UNSUPPORTED;
+        constexpr int kMaxVec = 16 / sizeof(T);
+        if (p.vec == kMaxVec)
+            return launch_backward<T, kMaxVec>(dx, dw, dy, x, w, residual_a, residual_b, rows, hidden, epsilon, p, s);
+        if (p.vec == 4)
+            return launch_backward<T, 4>(dx, dw, dy, x, w, residual_a, residual_b, rows, hidden, epsilon, p, s);
+        return launch_backward<T, 1>(dx, dw, dy, x, w, residual_a, residual_b, rows, hidden, epsilon, p, s);
+    });
+    return CGPT_OK;
+}

@@ -1,0 +1,56 @@
+// Library-wide host state: version string, launch counter, per-device scratch arena.
+#include <mutex>
+
+#include "common.cuh"
+#include "launch_counter.h"
+
+namespace cgpt {
+
+std::atomic<std::uint64_t> g_launch_count{0};
+
+namespace {
+constexpr int kMaxDevices = 64;
+struct Arena {
+    void* ptr = nullptr;
+    std::size_t bytes = 0;
+};
+Arena g_arena[kMaxDevices];
+std::mutex g_arena_mutex;
+}  // namespace
+
+// One arena per device, shared by every op on that device. Ops on one stream are ordered, so reuse
+// is safe there; ops issued concurrently on different streams of the same device must pass their own
+// workspace instead (none of the training path does). Growth frees the old block with cudaFree,
+// which synchronises the device, so earlier users have finished.
+int scratch_get(void** out, std::size_t bytes, cudaStream_t stream) {
+    int device = 0;
+    CGPT_CUDA_TRY(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) return CGPT_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_arena_mutex);
+    Arena& a = g_arena[device];
+    if (a.bytes < bytes) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone) {
+            // Growing would need cudaMalloc, which is illegal while capturing.
+            return CGPT_ERR_STATE;
+        }
+        std::size_t want = bytes < (std::size_t{64} << 20) ? (std::size_t{64} << 20) : bytes;
+        want = (want + (std::size_t{1} << 20) - 1) & ~((std::size_t{1} << 20) - 1);
+        if (a.ptr != nullptr) {
+            CGPT_CUDA_TRY(cudaFree(a.ptr));
+            a.ptr = nullptr;
+            a.bytes = 0;
+        }
+        CGPT_CUDA_TRY(cudaMalloc(&a.ptr, want));
+        a.bytes = want;
+    }
+    *out = a.ptr;
+    return CGPT_OK;
+}
+
+}  // namespace cgpt
+
+extern "C" const char* cgpt_b200_version(void) { return "cgpt_b200 0.1 (sm_100a)"; }
+extern "C" uint64_t cgpt_b200_launch_count(void) {
+    return cgpt::g_launch_count.load(std::memory_order_relaxed);
+}

@@ -1,0 +1,206 @@
+"""Host-side mirror of CGPT's operator API for the training hot path.
+
+Each function has the name, argument order (outputs first, then inputs, then ``stream``, then the
+options object) and error behaviour of the C++ function it stands for; ``ValueError`` plays the role
+of ``std::invalid_argument``. Tensors are ``torch`` CUDA tensors used purely as device-memory handles;
+all arithmetic happens in ``libcgpt_b200.so`` through the C ABI.
+
+Reference declarations: ``include/ops/backward/*.h``, ``include/ops/{rmsnorm,rope,swiglu,embedding,
+cross_entropy,cut_cross_entropy}.h``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from ._lib import check, dtype_code, lib, ptr, stream_ptr
+
+
+@dataclass
+class RopeOptions:
+    """include/ops/rope.h:6-11"""
+    rotary_dim: int = 0
+    position_offset: int = 0
+
+
+@dataclass
+class SwiGLUBackwardOptions:
+    """include/ops/backward/swiglu_backward.h:6-13"""
+    accumulate_gate: bool = False
+    accumulate_up: bool = False
+    accumulate_gate_up: bool = False
+
+
+@dataclass
+class EmbeddingBackwardOptions:
+    """include/ops/backward/embedding_backward.h:6-14"""
+    block_size: int = 0
+    bounds_check: bool = True
+    accumulate_weight: bool = False
+
+
+def _require(cond: bool, message: str) -> None:
+    if not cond:
+        raise _lib.CgptInvalidArgument(message)
+
+
+def _same_cuda_dtype(name: str, *tensors: torch.Tensor) -> None:
+    first = tensors[0]
+    for t in tensors:
+        _require(t.is_cuda, f"{name}: all tensors must be CUDA tensors")
+        _require(t.dtype == first.dtype, f"{name}: all tensors must share one dtype")
+        _require(t.is_contiguous(), f"{name}: tensors must be contiguous")
+
+
+def _ids(t: torch.Tensor, count: int, name: str) -> torch.Tensor:
+    _require(t is not None and t.is_cuda, f"{name}: token ids must be a CUDA buffer")
+    _require(t.dtype in (torch.int32, torch.uint32), f"{name}: token ids must be 32-bit")
+    _require(t.numel() >= count, f"{name}: token id buffer too small")
+    return t
+
+
+# --------------------------------------------------------------------------------------------- RMSNorm
+def rmsnorm_forward(output, input, weight, epsilon, stream=None):
+    """rmsnorm_forward(Tensor& output, const Tensor& input, const Tensor& weight, float eps, stream)."""
+    _same_cuda_dtype("rmsnorm_forward", output, input, weight)
+    _require(input.dim() == 2 and output.shape == input.shape and weight.dim() == 1
+             and weight.shape[0] == input.shape[1], "rmsnorm_forward: incompatible shapes")
+    check(lib.cgpt_rmsnorm_forward(ptr(output), ptr(input), ptr(weight), input.shape[0], input.shape[1],
+                                   float(epsilon), dtype_code(input), stream_ptr(stream)), "rmsnorm_forward")
+
+
+def rmsnorm_backward(grad_input, grad_weight, grad_output, input, weight, epsilon, stream=None,
+                     residual_a=None, residual_b=None):
+    """rmsnorm_backward (include/ops/backward/rmsnorm_backward.h:21-29). ``residual_a/b`` are this
+    library's extension: tensors added to grad_input inside the kernel."""
+    extra = [t for t in (residual_a, residual_b) if t is not None]
+    _same_cuda_dtype("rmsnorm_backward", grad_input, grad_weight, grad_output, input, weight, *extra)
+    _require(input.dim() == 2 and grad_output.shape == input.shape and grad_input.shape == input.shape
+             and weight.dim() == 1 and weight.shape[0] == input.shape[1] and grad_weight.shape == weight.shape
+             and all(t.shape == input.shape for t in extra), "rmsnorm_backward: incompatible shapes")
+    check(lib.cgpt_rmsnorm_backward(ptr(grad_input), ptr(grad_weight), ptr(grad_output), ptr(input), ptr(weight),
+                                    ptr(residual_a), ptr(residual_b), input.shape[0], input.shape[1],
+                                    float(epsilon), dtype_code(input), stream_ptr(stream)), "rmsnorm_backward")
+
+
+# ------------------------------------------------------------------------------------------------ RoPE
+def _rope_dims(q, k, cos_cache, sin_cache, opts, name):
+    _require(q.dim() == 4 and k.dim() == 4 and q.shape[0] == k.shape[0] and q.shape[1] == k.shape[1]
+             and q.shape[3] == k.shape[3], f"{name}: query/key must be [batch, seq, heads, head_dim]")
+    rotary = opts.rotary_dim or q.shape[3]
+    _require(rotary <= q.shape[3] and rotary % 2 == 0, f"{name}: invalid rotary_dim")
+    _require(cos_cache.dim() == 2 and sin_cache.shape == cos_cache.shape and cos_cache.shape[1] == rotary // 2,
+             f"{name}: caches must be [max_seq, rotary_dim/2]")
+    _require(opts.position_offset + q.shape[1] <= cos_cache.shape[0], f"{name}: position exceeds cache")
+    return rotary
+
+
+def rope_forward(query, key, cos_cache, sin_cache, stream=None, rope_options: RopeOptions | None = None):
+    """rope_forward: rotates query and key in place (include/ops/rope.h:13-39)."""
+    opts = rope_options or RopeOptions()
+    _same_cuda_dtype("rope_forward", query, key, cos_cache, sin_cache)
+    rotary = _rope_dims(query, key, cos_cache, sin_cache, opts, "rope_forward")
+    b, s, hq, d = query.shape
+    check(lib.cgpt_rope_forward(ptr(query), ptr(key), ptr(cos_cache), ptr(sin_cache), b, s, hq, key.shape[2], d,
+                                rotary, opts.position_offset, cos_cache.shape[0], dtype_code(query),
+                                stream_ptr(stream)), "rope_forward")
+
+
+def rope_backward(grad_query, grad_key, grad_rotated_query, grad_rotated_key, cos_cache, sin_cache, stream=None,
+                  rope_options: RopeOptions | None = None):
+    """rope_backward (include/ops/backward/rope_backward.h:22-31)."""
+    opts = rope_options or RopeOptions()
+    _same_cuda_dtype("rope_backward", grad_query, grad_key, grad_rotated_query, grad_rotated_key, cos_cache,
+                     sin_cache)
+    _require(grad_query.shape == grad_rotated_query.shape and grad_key.shape == grad_rotated_key.shape,
+             "rope_backward: gradient shapes differ")
+    rotary = _rope_dims(grad_query, grad_key, cos_cache, sin_cache, opts, "rope_backward")
+    b, s, hq, d = grad_query.shape
+    check(lib.cgpt_rope_backward(ptr(grad_query), ptr(grad_key), ptr(grad_rotated_query), ptr(grad_rotated_key),
+                                 ptr(cos_cache), ptr(sin_cache), b, s, hq, grad_key.shape[2], d, rotary,
+                                 opts.position_offset, cos_cache.shape[0], dtype_code(grad_query),
+                                 stream_ptr(stream)), "rope_backward")
+
+
+# ---------------------------------------------------------------------------------------------- SwiGLU
+def swiglu_forward(output, gate, up, stream=None):
+    _same_cuda_dtype("swiglu_forward", output, gate, up)
+    _require(output.shape == gate.shape == up.shape, "swiglu_forward: shapes differ")
+    check(lib.cgpt_swiglu_forward(ptr(output), ptr(gate), ptr(up), gate.numel(), dtype_code(gate),
+                                  stream_ptr(stream)), "swiglu_forward")
+
+
+def swiglu_backward(grad_gate, grad_up, grad_output, gate, up, stream=None,
+                    options: SwiGLUBackwardOptions | None = None):
+    """swiglu_backward, separate gate/up layout (include/ops/backward/swiglu_backward.h:29-37)."""
+    o = options or SwiGLUBackwardOptions()
+    _same_cuda_dtype("swiglu_backward", grad_gate, grad_up, grad_output, gate, up)
+    _require(grad_gate.shape == grad_up.shape == grad_output.shape == gate.shape == up.shape,
+             "swiglu_backward: shapes differ")
+    check(lib.cgpt_swiglu_backward(ptr(grad_gate), ptr(grad_up), ptr(grad_output), ptr(gate), ptr(up), gate.numel(),
+                                   int(o.accumulate_gate), int(o.accumulate_up), dtype_code(gate),
+                                   stream_ptr(stream)), "swiglu_backward")
+
+
+# ------------------------------------------------------------------------------------------- Embedding
+def embedding_forward(output, device_token_ids, token_count, weight, stream=None):
+    _same_cuda_dtype("embedding_forward", output, weight)
+    _ids(device_token_ids, token_count, "embedding_forward")
+    _require(weight.dim() == 2 and output.numel() == token_count * weight.shape[1],
+             "embedding_forward: output must hold token_count * hidden elements")
+    check(lib.cgpt_embedding_forward(ptr(output), ptr(device_token_ids), ptr(weight), token_count, weight.shape[0],
+                                     weight.shape[1], dtype_code(weight), stream_ptr(stream)), "embedding_forward")
+
+
+def embedding_backward(grad_weight, grad_output, device_token_ids, token_count, stream=None,
+                       options: EmbeddingBackwardOptions | None = None):
+    """embedding_backward (include/ops/backward/embedding_backward.h:35-42)."""
+    o = options or EmbeddingBackwardOptions()
+    _same_cuda_dtype("embedding_backward", grad_weight, grad_output)
+    _ids(device_token_ids, token_count, "embedding_backward")
+    _require(grad_weight.dim() == 2 and grad_output.numel() == token_count * grad_weight.shape[1],
+             "embedding_backward: grad_output must hold token_count * hidden elements")
+    check(lib.cgpt_embedding_backward(ptr(grad_weight), ptr(grad_output), ptr(device_token_ids), token_count,
+                                      grad_weight.shape[0], grad_weight.shape[1], int(o.bounds_check),
+                                      int(o.accumulate_weight), dtype_code(grad_weight), stream_ptr(stream)),
+          "embedding_backward")
+
+
+# --------------------------------------------------------------------------------------- Residual adds
+def add_tensors(output, a, b, stream=None, c=None):
+    """add_tensors / add_inplace of src/core/transformer_block.cu:161-215,261-288 (output may alias a)."""
+    extra = [c] if c is not None else []
+    _same_cuda_dtype("add_tensors", output, a, b, *extra)
+    _require(output.shape == a.shape == b.shape, "add_tensors: shapes differ")
+    check(lib.cgpt_add(ptr(output), ptr(a), ptr(b), ptr(c), a.numel(), dtype_code(a), stream_ptr(stream)),
+          "add_tensors")
+
+
+# --------------------------------------------------------------------------------------- Cross entropy
+def _ce_check(loss, logits, targets, target_count, name):
+    _require(loss.is_cuda and loss.dtype == torch.float32 and tuple(loss.shape) == (1,),
+             f"{name}: loss must be a CUDA F32 tensor with shape [1]")
+    _require(logits.is_cuda and logits.dim() == 2 and logits.shape[0] > 0 and logits.shape[1] > 0,
+             f"{name}: logits must be a non-empty CUDA matrix")
+    _require(target_count == logits.shape[0], f"{name}: target count must equal logits rows")
+    _ids(targets, target_count, name)
+
+
+def cross_entropy_forward_backward(loss, gradient, logits, device_targets, target_count, stream=None,
+                                   gradient_scale: float = 1.0):
+    """cross_entropy_forward_backward (include/ops/cross_entropy.h:25-32)."""
+    _ce_check(loss, logits, device_targets, target_count, "cross_entropy")
+    _same_cuda_dtype("cross_entropy", gradient, logits)
+    _require(gradient.shape == logits.shape, "cross_entropy: gradient shape must match logits")
+    check(lib.cgpt_cross_entropy(ptr(loss), ptr(gradient), ptr(logits), ptr(device_targets), logits.shape[0],
+                                 logits.shape[1], float(gradient_scale), dtype_code(logits), stream_ptr(stream)),
+          "cross_entropy_forward_backward")
+
+
+def cross_entropy_forward(loss, logits, device_targets, target_count, stream=None):
+    """cross_entropy_forward (include/ops/cross_entropy.h:37-42)."""
+    _ce_check(loss, logits, device_targets, target_count, "cross_entropy")
+    check(lib.cgpt_cross_entropy(ptr(loss), None, ptr(logits), ptr(device_targets), logits.shape[0], logits.shape[1],
+                                 1.0, dtype_code(logits), stream_ptr(stream)), "cross_entropy_forward")

@@ -1,0 +1,193 @@
+/*
+ * cgpt_b200 -- C ABI of the B200 (sm_100a) training hot path for CGPT.
+ *
+ * Every function is `extern "C"`, takes raw DEVICE pointers, plain integer sizes, option scalars and
+ * a CUDA stream (passed as `void*` so the header needs no CUDA include), is asynchronous on that
+ * stream unless stated otherwise, and returns an int status:
+ *      0  CGPT_OK
+ *    > 0  an argument error class (CGPT_ERR_*); nothing was launched
+ *    < 0  the negated cudaError_t of the CUDA runtime/driver call that failed
+ * Nothing throws, nothing calls exit(). The C++ shim that re-creates CGPT's own `Tensor&` functions
+ * on top of this ABI turns CGPT_ERR_* into std::invalid_argument, as CGPT's validators do.
+ *
+ * All tensors are contiguous row-major. `dtype` is one of CGPT_DTYPE_* and applies to every
+ * floating-point tensor of the call unless a parameter says otherwise (CGPT uses one storage dtype
+ * per op, see `include/core/dtype.h:12-21` of the reference; the numeric codes are the same).
+ *
+ * Scratch memory: ops that need global scratch take it from a per-device arena inside the library,
+ * grown with cudaMalloc on first use of a given size. Run each op once eagerly before capturing it
+ * in a CUDA graph (CGPT's trainer does exactly that, `train/train.cpp:545-548`).
+ */
+#ifndef CGPT_B200_H_
+#define CGPT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CGPT_DTYPE_F16 0
+#define CGPT_DTYPE_BF16 1
+#define CGPT_DTYPE_F32 2
+
+#define CGPT_OK 0
+#define CGPT_ERR_NULL 1      /* a required pointer is NULL */
+#define CGPT_ERR_DTYPE 2     /* unsupported dtype for this op */
+#define CGPT_ERR_SHAPE 3     /* zero / inconsistent / overflowing dimensions */
+#define CGPT_ERR_OPTION 4    /* invalid option scalar (epsilon <= 0, beta outside [0,1), ...) */
+#define CGPT_ERR_ALIGN 5     /* pointer not aligned to the element size */
+#define CGPT_ERR_UNSUPPORTED 6 /* valid for CGPT but outside what this build implements */
+#define CGPT_ERR_STATE 7     /* object used in a state it does not allow (changed entry list, ...) */
+#define CGPT_ERR_DEVICE 8    /* device-side bounded wait ran out (status word set by a kernel) */
+
+typedef void* cgpt_stream_t; /* a cudaStream_t */
+
+/* Library / build information. Returns a static string such as "cgpt_b200 sm_100a". */
+const char* cgpt_b200_version(void);
+/* Number of kernel launches issued by this library in the calling process since load (a host-side
+ * counter incremented next to every `<<<>>>`); bench.py reports the difference over the timed
+ * region. */
+uint64_t cgpt_b200_launch_count(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * RMSNorm  y = x * rsqrt(mean(x^2) + eps) * w
+ * Replaces rmsnorm_forward  (reference include/ops/rmsnorm.h:36-52, src/ops/rmsnorm.cu:812-906)
+ *      and rmsnorm_backward (reference include/ops/backward/rmsnorm_backward.h:21-29,
+ *                            src/ops/backward/rmsnorm_backward.cu:529-547).
+ * x, y, dy, dx: [rows, hidden]; w, dw: [hidden]. fp32 math, one rounding on store.
+ * Backward overwrites dx and dw:  inv = rsqrt(mean(x^2)+eps); c = sum(dy*w*x) * inv^3 / hidden;
+ *      dx = dy*w*inv - x*c (+ residual_a + residual_b when given);  dw = sum_rows dy*x*inv.
+ * residual_a / residual_b (may be NULL) are [rows, hidden] tensors added to dx in fp32 before the
+ * single rounding: they fold the reference's `add_inplace` passes
+ * (src/core/transformer_block.cu:678-681,747) into this kernel.
+ * ---------------------------------------------------------------------------------------------- */
+int cgpt_rmsnorm_forward(void* y, const void* x, const void* w, size_t rows, size_t hidden,
+                         float epsilon, int dtype, cgpt_stream_t stream);
+int cgpt_rmsnorm_backward(void* dx, void* dw, const void* dy, const void* x, const void* w,
+                          const void* residual_a, const void* residual_b, size_t rows,
+                          size_t hidden, float epsilon, int dtype, cgpt_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * RoPE on adjacent pairs (x[2p], x[2p+1]) of the first rotary_dim dims of each head, angle index
+ * (position_offset + s, p), tables [max_seq, rotary_dim/2] in the tensors' dtype.
+ * Replaces rope_forward (reference include/ops/rope.h:13-39, in place on q and k) and rope_backward
+ * (reference include/ops/backward/rope_backward.h:22-31, src/ops/backward/rope_backward.cu:318-389).
+ * q-like tensors [batch, seq, q_heads, head_dim], k-like [batch, seq, kv_heads, head_dim].
+ * Backward: dx0 = dy0*c + dy1*s, dx1 = -dy0*s + dy1*c; dims >= rotary_dim are copied. In-place
+ * (dq == dq_rot) is allowed. rotary_dim == 0 means head_dim.
+ * ---------------------------------------------------------------------------------------------- */
+int cgpt_rope_forward(void* q, void* k, const void* cos_table, const void* sin_table, size_t batch,
+                      size_t seq, size_t q_heads, size_t kv_heads, size_t head_dim,
+                      size_t rotary_dim, size_t position_offset, size_t max_seq, int dtype,
+                      cgpt_stream_t stream);
+int cgpt_rope_backward(void* dq, void* dk, const void* dq_rot, const void* dk_rot,
+                       const void* cos_table, const void* sin_table, size_t batch, size_t seq,
+                       size_t q_heads, size_t kv_heads, size_t head_dim, size_t rotary_dim,
+                       size_t position_offset, size_t max_seq, int dtype, cgpt_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * SwiGLU  y = silu(gate) * up.
+ * Replaces swiglu_forward (reference include/ops/swiglu.h) and swiglu_backward
+ * (reference include/ops/backward/swiglu_backward.h:6-38, src/ops/backward/swiglu_backward.cu:760-883):
+ *      s = 1/(1+exp(-g));  dgate = dy*up*s*(1+g*(1-s));  dup = dy*g*s.
+ * accumulate_* != 0 adds to the existing output instead of overwriting it. count = number of
+ * elements of each tensor.
+ * ---------------------------------------------------------------------------------------------- */
+int cgpt_swiglu_forward(void* y, const void* gate, const void* up, size_t count, int dtype,
+                        cgpt_stream_t stream);
+int cgpt_swiglu_backward(void* dgate, void* dup, const void* dy, const void* gate, const void* up,
+                         size_t count, int accumulate_gate, int accumulate_up, int dtype,
+                         cgpt_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Embedding gather and its backward.
+ * Replaces embedding_forward (reference include/ops/embedding.h) and embedding_backward
+ * (reference include/ops/backward/embedding_backward.h:6-42, src/ops/backward/embedding_backward.cu:207-254):
+ *      grad_weight[ids[t], :] += grad_output[t, :]   for ids[t] < vocab (others skipped when
+ *      bounds_check != 0), after zeroing grad_weight unless accumulate != 0.
+ * Deterministic: tokens are grouped by id and each table row is summed in fp32 in token order, then
+ * rounded once (the reference uses storage-dtype atomics in arrival order).
+ * ids: uint32 device buffer of `tokens` entries.
+ * ---------------------------------------------------------------------------------------------- */
+int cgpt_embedding_forward(void* out, const uint32_t* ids, const void* weight, size_t tokens,
+                           size_t vocab, size_t hidden, int dtype, cgpt_stream_t stream);
+int cgpt_embedding_backward(void* grad_weight, const void* grad_output, const uint32_t* ids,
+                            size_t tokens, size_t vocab, size_t hidden, int bounds_check,
+                            int accumulate, int dtype, cgpt_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Residual adds. Replaces add_tensors / add_inplace (reference src/core/transformer_block.cu:161-215,
+ * 261-288). out = a + b (+ c when c != NULL), fp32 add, one rounding. out may alias a.
+ * ---------------------------------------------------------------------------------------------- */
+int cgpt_add(void* out, const void* a, const void* b, const void* c, size_t count, int dtype,
+             cgpt_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Softmax cross-entropy on materialised logits.
+ * Replaces cross_entropy_forward_backward / cross_entropy_forward (reference
+ * include/ops/cross_entropy.h:25-42, src/ops/cross_entropy.cu:352-410).
+ * logits, grad: [rows, vocab] in `dtype`; loss: fp32 [1], overwritten with the mean over `rows` of
+ * (log sum exp - logit[target]); rows whose target >= vocab add nothing to the loss and get no -1.
+ * grad = (softmax - onehot) / rows * gradient_scale. grad == NULL computes the loss only.
+ * ---------------------------------------------------------------------------------------------- */
+int cgpt_cross_entropy(float* loss, void* grad, const void* logits, const uint32_t* targets,
+                       size_t rows, size_t vocab, float gradient_scale, int dtype,
+                       cgpt_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * AdamW over a list of tensors, fp32 master weights / moments, loss-scale unscale, non-finite skip,
+ * optional global-norm clip, device-side step counter.
+ * Replaces AdamWWorkspace, adamw_step_many_async, adamw_check (reference include/optim/adamw.h:12-136,
+ * src/optim/adamw.cu:269-359). Math per element (expression tree kept for 1e-6 parity):
+ *      g = float(grad) / loss_scale * clip
+ *      m = b1*m + (1-b1)*g;  v = b2*v + (1-b2)*g*g
+ *      n = m / bc1 / (sqrtf(v / bc2) + eps),  bc_i = 1 - powf(b_i, float(step))   (on device)
+ *      master = master*(1 - lr*wd) - lr*n;  param = (T)master
+ * clip = max_grad_norm / norm when norm = sqrt(sum (grad/loss_scale)^2 over ALL entries) exceeds a
+ * finite max_grad_norm, else 1. A non-finite unscaled gradient or norm skips the whole step: no
+ * tensor changes, the step counter does not advance, and a sticky flag is raised.
+ *
+ * cgpt_adamw_create binds the workspace to `count` tensors (the reference binds on first use and
+ * rejects a changed list, adamw.cu:283-305). Pointers are device pointers; dtype applies to param
+ * and grad. `initial_step` seeds the device counter. The handle owns small device buffers; it is
+ * created and destroyed outside stream capture. cgpt_adamw_step is capturable and launches a fixed
+ * number of kernels regardless of `count`. cgpt_adamw_check copies {sticky flag, step} to the host,
+ * synchronises the stream, clears the sticky flag, writes the step to *step_out and the flag to
+ * *non_finite_out.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct cgpt_adamw_tensor {
+    void* param;        /* [count] in `dtype`, updated in place */
+    const void* grad;   /* [count] in `dtype` */
+    float* master;      /* [count] fp32 */
+    float* m;           /* [count] fp32 */
+    float* v;           /* [count] fp32 */
+    uint64_t count;     /* elements */
+    int32_t dtype;      /* CGPT_DTYPE_* of param and grad */
+    int32_t reserved;
+} cgpt_adamw_tensor;
+
+typedef struct cgpt_adamw_options {
+    float learning_rate, beta1, beta2, epsilon, weight_decay, loss_scale, max_grad_norm;
+} cgpt_adamw_options;
+
+typedef struct cgpt_adamw_workspace cgpt_adamw_workspace;
+
+int cgpt_adamw_create(cgpt_adamw_workspace** out, const cgpt_adamw_tensor* tensors, size_t count,
+                      uint64_t initial_step, cgpt_stream_t stream);
+int cgpt_adamw_destroy(cgpt_adamw_workspace* ws);
+int cgpt_adamw_step(cgpt_adamw_workspace* ws, const cgpt_adamw_options* options,
+                    cgpt_stream_t stream);
+int cgpt_adamw_check(cgpt_adamw_workspace* ws, uint64_t* step_out, int* non_finite_out,
+                     cgpt_stream_t stream);
+/* Reads back the statistics of the last step (sum of squared unscaled gradients, clip factor).
+ * Synchronises the stream. For tests and logging. */
+int cgpt_adamw_last_stats(cgpt_adamw_workspace* ws, float* squared_norm, float* clip,
+                          cgpt_stream_t stream);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#endif /* CGPT_B200_H_ */

@@ -1,0 +1,90 @@
+"""Builds the reference's own CPU operators into ``oracle/_ref/libcgpt_ref_cpu.so`` (TEST INFRASTRUCTURE).
+
+Sources are compiled where they lie under the reference checkout (default ``/root/reference``); nothing
+is copied. The only file of this repository in the link is ``oracle/ref_wrap.cpp``, a flat C wrapper.
+The recipe replaces the reference's CMake build (which pins sm_86/sm_90a and needs CMake >= 4.3) with
+direct compiler calls and the flags of its ``CMakeLists.txt:57-66`` (``-O3 -mavx2 -mfma -mf16c``,
+OpenMP on), plus ``-include cstdint`` because ``include/core/dtype.h:12`` uses ``std::uint8_t`` without
+including ``<cstdint>``.
+
+Usage: ``python oracle/build_ref.py [--reference /root/reference]``. Does nothing (and says so) when the
+reference checkout is absent, e.g. on a GPU box, where the prebuilt library is used.
+"""
+from __future__ import annotations
+
+import argparse
+import concurrent.futures
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+OUT = HERE / "_ref"
+LIB = OUT / "libcgpt_ref_cpu.so"
+
+CPU_SOURCES = [
+    "src/ops/cpu/attention_cpu.cpp", "src/ops/cpu/cross_entropy_cpu.cpp", "src/ops/cpu/embedding_cpu.cpp",
+    "src/ops/cpu/linear_cpu.cpp", "src/ops/cpu/rmsnorm_cpu.cpp", "src/ops/cpu/rope_cpu.cpp",
+    "src/ops/cpu/softmax_cpu.cpp", "src/ops/cpu/swiglu_cpu.cpp",
+    "src/ops/cpu/backward/attention_backward_cpu.cpp", "src/ops/cpu/backward/cross_entropy_backward_cpu.cpp",
+    "src/ops/cpu/backward/embedding_backward_cpu.cpp", "src/ops/cpu/backward/linear_backward_cpu.cpp",
+    "src/ops/cpu/backward/rmsnorm_backward_cpu.cpp", "src/ops/cpu/backward/rope_backward_cpu.cpp",
+    "src/ops/cpu/backward/swiglu_backward_cpu.cpp",
+]
+CUDA_SOURCES = ["src/core/tensor.cu", "src/optim/adamw.cu"]  # host code paths only are exercised
+
+
+def build(reference: Path, force: bool = False) -> Path | None:
+    if not (reference / "src" / "ops" / "cpu").is_dir():
+        print(f"[oracle/_ref] reference checkout not found at {reference}; keeping prebuilt files", file=sys.stderr)
+        return LIB if LIB.exists() else None
+    OUT.mkdir(parents=True, exist_ok=True)
+    wrap = HERE / "ref_wrap.cpp"
+    inputs = [reference / s for s in CPU_SOURCES + CUDA_SOURCES] + [wrap]
+    if LIB.exists() and not force and all(LIB.stat().st_mtime > p.stat().st_mtime for p in inputs):
+        return LIB
+    inc = ["-I", str(reference / "include"), "-I", str(reference / "include" / "core"), "-I", "/usr/local/cuda/include"]
+    cxx = ["/usr/bin/g++", "-std=c++20", "-O3", "-mavx2", "-mfma", "-mf16c", "-fopenmp", "-fPIC", "-include", "cstdint",
+           "-DCGPT_ENABLE_OPENMP=1", *inc]
+    nvcc = ["/usr/local/cuda/bin/nvcc", "-ccbin", "/usr/bin/g++", "-std=c++20", "-O3", "-include", "cstdint",
+            "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC,-fopenmp", *inc]
+    jobs = []
+    objects = []
+    for rel in CPU_SOURCES:
+        obj = OUT / (rel.replace("/", "_") + ".o")
+        objects.append(obj)
+        jobs.append([*cxx, "-c", str(reference / rel), "-o", str(obj)])
+    for rel in CUDA_SOURCES:
+        obj = OUT / (rel.replace("/", "_") + ".o")
+        objects.append(obj)
+        jobs.append([*nvcc, "-c", str(reference / rel), "-o", str(obj)])
+    obj = OUT / "ref_wrap.o"
+    objects.append(obj)
+    jobs.append([*cxx, "-c", str(wrap), "-o", str(obj)])
+
+    def run(cmd):
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError("command failed: " + " ".join(cmd) + "\n" + proc.stdout + proc.stderr)
+
+    with concurrent.futures.ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as pool:
+        list(pool.map(run, jobs))
+    run(["/usr/local/cuda/bin/nvcc", "-ccbin", "/usr/bin/g++", "-shared", "-cudart", "shared", "-Xcompiler", "-fopenmp",
+         "-gencode", "arch=compute_100a,code=sm_100a", "-Xlinker", "-rpath,/usr/local/cuda/lib64", "-o", str(LIB),
+         *map(str, objects)])
+    for o in objects:
+        o.unlink(missing_ok=True)
+    return LIB
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__)
+    ap.add_argument("--reference", default=os.environ.get("CGPT_REFERENCE", "/root/reference"))
+    ap.add_argument("--force", action="store_true")
+    args = ap.parse_args()
+    print(build(Path(args.reference), args.force))
+
+
+if __name__ == "__main__":
+    main()
