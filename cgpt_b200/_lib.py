@@ -59,6 +59,11 @@ class AdamWOptions(C.Structure):
 SIGNATURES = {
     "cgpt_b200_version": (C.c_char_p, []),
     "cgpt_b200_launch_count": (C.c_uint64, []),
+    "cgpt_b200_device_status": (_i, [C.POINTER(C.c_uint), _i]),
+    "cgpt_b200_reserve_scratch": (_i, [_sz]),
+    "cgpt_gemm": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _i, _i, _i, _i, _i, _vp]),
+    "cgpt_linear_forward": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _i, _vp]),
+    "cgpt_linear_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _i, _i, _i, _i, _vp]),
     "cgpt_rmsnorm_forward": (_i, [_vp, _vp, _vp, _sz, _sz, _f, _i, _vp]),
     "cgpt_rmsnorm_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _f, _i, _vp]),
     "cgpt_rope_forward": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _i, _vp]),
@@ -112,6 +117,13 @@ def stream_ptr(stream=None) -> int:
     if stream is None:
         stream = torch.cuda.current_stream()
     return stream.cuda_stream
+
+
+def device_status(clear: bool = True) -> int:
+    """Status word of the tensor-core kernels: non-zero if a bounded device-side wait ran out."""
+    v = C.c_uint(0)
+    check(lib.cgpt_b200_device_status(C.byref(v), int(clear)), "device_status")
+    return int(v.value)
 
 
 def launch_count() -> int:

@@ -1,0 +1,506 @@
+// Dense 16-bit GEMM with fp32 accumulation on the sm_100a tensor cores (tcgen05.mma, accumulator in
+// TMEM, operands staged by TMA into 128-byte-swizzled shared memory), plus a plain SIMT kernel for
+// fp32 tensors and shapes TMA cannot address.
+//
+// It serves the three contractions of a linear layer Y = X W^T (reference: src/ops/linear.cu and
+// src/ops/backward/linear_backward.cu:135-148, which call cuBLASLt):
+//   forward  Y [T,out]  = X [T,in]  * W [out,in]^T     A K-major,  B K-major
+//   dX       dX[T,in]   = dY[T,out] * W [out,in]       A K-major,  B N-major (MN-major tile)
+//   dW       dW[out,in] = dY[T,out]^T * X [T,in]       A M-major,  B N-major, reduction over T
+//
+// Kernel shape: one CTA computes a 128 x BN tile (BN = 128 or 256) for a slice of K. Warp 0 issues the
+// TMA loads into a STAGES-deep ring, warp 1 issues tcgen05.mma (128 x BN x 16 per instruction, four
+// per 64-wide K block) and commits each stage back to the producer, warps 2-5 drain the fp32
+// accumulator from TMEM (tcgen05.ld), convert and store. Split-K writes fp32 partials that a small
+// kernel sums in a fixed order (deterministic; used when the tile count alone cannot fill 148 SMs,
+// e.g. dW with K = tokens). Algorithmic work: 2*M*N*K flops.
+#include <mutex>
+#include <type_traits>
+
+#include "launch_counter.h"
+#include "sm100.cuh"
+
+namespace cgpt {
+
+// ------------------------------------------------------------------------------------ tensor maps
+namespace {
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn g_encode = nullptr;
+std::once_flag g_encode_once;
+
+void load_encode() {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+        g_encode = reinterpret_cast<EncodeFn>(fn);
+}
+}  // namespace
+
+int make_tensor_map(CUtensorMap* map, int dtype, const void* base, int rank, const std::uint64_t* dims,
+                    const std::uint64_t* strides_bytes, const std::uint32_t* box) {
+    std::call_once(g_encode_once, load_encode);
+    if (g_encode == nullptr) return CGPT_ERR_UNSUPPORTED;
+    cuuint64_t gdim[5], gstride[5];
+    cuuint32_t gbox[5], estride[5];
+    for (int i = 0; i < rank; ++i) {
+        gdim[i] = dims[i];
+        gbox[i] = box[i];
+        estride[i] = 1;
+        if (i + 1 < rank) gstride[i] = strides_bytes[i];
+    }
+    const CUtensorMapDataType dt = dtype == CGPT_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                 : dtype == CGPT_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                            : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    const CUresult r = g_encode(map, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdim, gstride, gbox,
+                                estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? CGPT_OK : CGPT_ERR_SHAPE;
+}
+
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128;
+constexpr int BK = 64;          // 64 x 16-bit = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kGemmThreads = 192;
+
+template <int BN> struct GemmCfg {
+    static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr int kABytes = BM * BK * 2;
+    static constexpr int kBBytes = BN * BK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+// Device status word shared by the contraction kernels: non-zero means a bounded wait ran out.
+__device__ unsigned int g_gemm_status = 0;
+
+enum : int { kEpiStore = 0, kEpiAccumulate = 1, kEpiPartial = 2 };
+
+template <typename T, int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    T* __restrict__ C, float* __restrict__ partial, int M, int N, int K, int kb_per_split, int epilogue) {
+    using Cfg = GemmCfg<BN>;
+    extern __shared__ unsigned char gemm_smem_raw[];
+    const std::uint32_t raw = smem_u32(gemm_smem_raw);
+    unsigned char* smem = gemm_smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+    std::uint64_t* bars = reinterpret_cast<std::uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+    std::uint64_t* full = bars;
+    std::uint64_t* empty = bars + Cfg::kStages;
+    std::uint64_t* acc_full = bars + 2 * Cfg::kStages;
+    std::uint32_t* tmem_slot = reinterpret_cast<std::uint32_t*>(bars + 2 * Cfg::kStages + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tile_m = blockIdx.x, tile_n = blockIdx.y, split = blockIdx.z;
+    const int total_kb = (K + BK - 1) / BK;
+    const int kb_begin = split * kb_per_split;
+    int nkb = total_kb - kb_begin;
+    if (nkb > kb_per_split) nkb = kb_per_split;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_full, 1);
+        mbar_init_fence();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, BN);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const std::uint32_t tmem_acc = *tmem_slot;
+    bool failed = false;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % Cfg::kStages;
+                const std::uint32_t ph = (i / Cfg::kStages) & 1;
+                if (!mbar_wait(&empty[s], ph ^ 1u)) { failed = true; break; }
+                mbar_expect_tx(&full[s], Cfg::kStageBytes);
+                unsigned char* a_dst = smem + s * Cfg::kStageBytes;
+                unsigned char* b_dst = a_dst + Cfg::kABytes;
+                const int k0 = (kb_begin + i) * BK;
+                if (!A_MN) {
+                    tma_load_2d(a_dst, &tmap_a, &full[s], k0, tile_m * BM);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * (BK * 128), &tmap_a, &full[s], tile_m * BM + j * 64, k0);
+                }
+                if (!B_MN) {
+                    tma_load_2d(b_dst, &tmap_b, &full[s], k0, tile_n * BN);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * (BK * 128), &tmap_b, &full[s], tile_n * BN + j * 64, k0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr std::uint32_t idesc = idesc_f16(sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0,
+                                                      A_MN ? 1 : 0, B_MN ? 1 : 0, BM, BN);
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % Cfg::kStages;
+                const std::uint32_t ph = (i / Cfg::kStages) & 1;
+                if (!mbar_wait(&full[s], ph)) { failed = true; break; }
+                tc_fence_after_sync();
+                const std::uint32_t a_base = smem_u32(smem + s * Cfg::kStageBytes);
+                const std::uint32_t b_base = a_base + Cfg::kABytes;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    const std::uint64_t adesc = A_MN ? smem_desc_sw128(a_base + k * (UMMA_K * 128), BK * 128, 1024)
+                                                     : smem_desc_sw128(a_base + k * (UMMA_K * 2), 16, 1024);
+                    const std::uint64_t bdesc = B_MN ? smem_desc_sw128(b_base + k * (UMMA_K * 128), BK * 128, 1024)
+                                                     : smem_desc_sw128(b_base + k * (UMMA_K * 2), 16, 1024);
+                    mma_f16_ss(tmem_acc, adesc, bdesc, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                tc_commit(&empty[s]);   // frees the stage once these MMAs have read it
+            }
+            tc_commit(acc_full);        // accumulator complete
+        }
+    } else {
+        // Epilogue: warps 2..5 own TMEM lane quarters (warp % 4).
+        const int quarter = warp & 3;
+        if (!mbar_wait(acc_full, 0)) failed = true;
+        failed = __any_sync(0xffffffffu, failed);   // keep the warp-collective TMEM loads uniform
+        tc_fence_after_sync();
+        const int row = tile_m * BM + quarter * 32 + lane;
+        const long long out_row = static_cast<long long>(row) * N;
+        if (!failed) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                std::uint32_t r[32];
+                tmem_ld_32x32(tmem_acc + (static_cast<std::uint32_t>(quarter * 32) << 16) + c0, r);
+                const int col0 = tile_n * BN + c0;
+                if (row < M && col0 < N) {
+                    if (epilogue == kEpiPartial) {
+                        float* dst = partial + (static_cast<long long>(split) * M + row) * N + col0;
+                        if (col0 + 32 <= N && (N & 3) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                                                  __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                        } else {
+                            for (int j = 0; j < 32 && col0 + j < N; ++j) dst[j] = __uint_as_float(r[j]);
+                        }
+                    } else {
+                        T* dst = C + out_row + col0;
+                        if (col0 + 32 <= N && (N & 7) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                float v[8];
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+                                if (epilogue == kEpiAccumulate) {
+                                    float old[8];
+                                    load_vec<T, 8>(old, dst + j);
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e) v[e] += old[e];
+                                }
+                                store_vec<T, 8>(dst + j, v);
+                            }
+                        } else {
+                            for (int j = 0; j < 32 && col0 + j < N; ++j) {
+                                float v = __uint_as_float(r[j]);
+                                if (epilogue == kEpiAccumulate) v += to_f32<T>(dst[j]);
+                                dst[j] = from_f32<T>(v);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    if (failed) {
+        atomicExch(&g_gemm_status, 1u);
+        // Give outstanding TMA writes into this CTA's shared memory time to land before it exits.
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) { }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_acc, BN);
+    }
+}
+
+// out[m,n] = sum_s partial[s,m,n] (+ old out when accumulate), fixed order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(T* __restrict__ out, const float* __restrict__ partial, long long mn, int splits, int accumulate) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 4;
+    for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < mn; i += stride) {
+        if (i + 4 <= mn && (mn & 3) == 0) {
+            float4 acc = *reinterpret_cast<const float4*>(partial + i);
+            for (int s = 1; s < splits; ++s) {
+                const float4 p = *reinterpret_cast<const float4*>(partial + s * mn + i);
+                acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+            }
+            float v[4] = {acc.x, acc.y, acc.z, acc.w};
+            if (accumulate) {
+                float old[4];
+                load_vec<T, 4>(old, out + i);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[e] += old[e];
+            }
+            store_vec<T, 4>(out + i, v);
+        } else {
+            for (long long j = i; j < mn && j < i + 4; ++j) {
+                float acc = 0.f;
+                for (int s = 0; s < splits; ++s) acc += partial[s * mn + j];
+                if (accumulate) acc += to_f32<T>(out[j]);
+                out[j] = from_f32<T>(acc);
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------- SIMT fallback
+// C[m,n] (+)= sum_k A(m,k) * B(n,k) with arbitrary element strides; 64x64 tile, 4x4 per thread, fp32.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gemm_simt_kernel(T* __restrict__ C, const T* __restrict__ A, const T* __restrict__ B, int M, int N, int K,
+                 long long a_sm, long long a_sk, long long b_sn, long long b_sk, int accumulate) {
+    __shared__ float As[16][65];
+    __shared__ float Bs[16][65];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += 16) {
+        for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+            const int kk = i & 15, r = i >> 4;
+            const int m = m0 + r, n = n0 + r, k = k0 + kk;
+            As[kk][r] = (m < M && k < K) ? to_f32<T>(A[m * a_sm + k * a_sk]) : 0.f;
+            Bs[kk][r] = (n < N && k < K) ? to_f32<T>(B[n * b_sn + k * b_sk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { a[i] = As[kk][ty * 4 + i]; b[i] = Bs[kk][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    for (int i = 0; i < 4; ++i)
+        for (int j = 0; j < 4; ++j) {
+            const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+            if (m < M && n < N) {
+                float v = acc[i][j];
+                T* dst = C + static_cast<long long>(m) * N + n;
+                if (accumulate) v += to_f32<T>(*dst);
+                *dst = from_f32<T>(v);
+            }
+        }
+}
+
+// Column sums of a [rows, cols] matrix (bias gradient), coalesced: each CTA owns 32 columns and
+// strides over rows with 8 row lanes; fp32, fixed order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+column_sum_kernel(T* __restrict__ out, const T* __restrict__ in, long long rows, int cols, int accumulate) {
+    __shared__ float tile[8][33];
+    const int col = blockIdx.x * 32 + (threadIdx.x & 31);
+    const int rl = threadIdx.x >> 5;
+    float acc = 0.f;
+    if (col < cols)
+        for (long long r = rl; r < rows; r += 8) acc += to_f32<T>(in[r * cols + col]);
+    tile[rl][threadIdx.x & 31] = acc;
+    __syncthreads();
+    if (rl == 0 && col < cols) {
+        float total = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) total += tile[r][threadIdx.x & 31];
+        if (accumulate) total += to_f32<T>(out[col]);
+        out[col] = from_f32<T>(total);
+    }
+}
+
+template <typename T, int BN, bool A_MN, bool B_MN>
+int launch_tc(T* C, const T* A, const T* B, int M, int N, int K, int accumulate, int dtype, cudaStream_t s) {
+    using Cfg = GemmCfg<BN>;
+    CUtensorMap ta, tb;
+    {
+        // innermost dimension first
+        const std::uint64_t dims_k[2] = {static_cast<std::uint64_t>(K), static_cast<std::uint64_t>(M)};
+        const std::uint64_t dims_m[2] = {static_cast<std::uint64_t>(M), static_cast<std::uint64_t>(K)};
+        const std::uint64_t st_k[1] = {static_cast<std::uint64_t>(K) * 2}, st_m[1] = {static_cast<std::uint64_t>(M) * 2};
+        const std::uint32_t box_k[2] = {BK, BM}, box_m[2] = {64, BK};
+        CGPT_TRY(make_tensor_map(&ta, dtype, A, 2, A_MN ? dims_m : dims_k, A_MN ? st_m : st_k, A_MN ? box_m : box_k));
+    }
+    {
+        const std::uint64_t dims_k[2] = {static_cast<std::uint64_t>(K), static_cast<std::uint64_t>(N)};
+        const std::uint64_t dims_n[2] = {static_cast<std::uint64_t>(N), static_cast<std::uint64_t>(K)};
+        const std::uint64_t st_k[1] = {static_cast<std::uint64_t>(K) * 2}, st_n[1] = {static_cast<std::uint64_t>(N) * 2};
+        const std::uint32_t box_k[2] = {BK, BN}, box_n[2] = {64, BK};
+        CGPT_TRY(make_tensor_map(&tb, dtype, B, 2, B_MN ? dims_n : dims_k, B_MN ? st_n : st_k, B_MN ? box_n : box_k));
+    }
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+    const int total_kb = (K + BK - 1) / BK;
+    // Split K when the output tiles alone leave most SMs idle and K is long enough to amortise it.
+    int splits = 1;
+    const int tiles = tiles_m * tiles_n;
+    if (tiles < kNumSMs) {
+        splits = kNumSMs / tiles;
+        const int max_by_k = total_kb / 8 > 0 ? total_kb / 8 : 1;   // at least 8 K blocks (512) per split
+        if (splits > max_by_k) splits = max_by_k;
+        if (splits > 32) splits = 32;
+        if (splits < 1) splits = 1;
+    }
+    int kb_per_split = (total_kb + splits - 1) / splits;
+    splits = (total_kb + kb_per_split - 1) / kb_per_split;   // no empty split
+    float* partial = nullptr;
+    if (splits > 1) {
+        void* scratch = nullptr;
+        CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(splits) * M * N * sizeof(float), s));
+        partial = static_cast<float*>(scratch);
+    }
+    auto kernel = gemm_tcgen05_kernel<T, BN, A_MN, B_MN>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        CGPT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        attr_done = true;
+    }
+    const dim3 grid(tiles_m, tiles_n, splits);
+    const int epi = splits > 1 ? kEpiPartial : (accumulate ? kEpiAccumulate : kEpiStore);
+    kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, C, partial, M, N, K, kb_per_split, epi);
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+    if (splits > 1) {
+        const long long mn = static_cast<long long>(M) * N;
+        long long blocks = (mn / 4 + 255) / 256;
+        if (blocks > kNumSMs * 8) blocks = kNumSMs * 8;
+        if (blocks < 1) blocks = 1;
+        splitk_reduce_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, s>>>(C, partial, mn, splits, accumulate);
+        count_launch();
+        CGPT_LAUNCH_CHECK();
+    }
+    return CGPT_OK;
+}
+
+template <typename T>
+int launch_tc_layout(T* C, const T* A, const T* B, int M, int N, int K, int a_mn, int b_mn, int accumulate, int dtype,
+                     cudaStream_t s) {
+    // 128x256 tiles when that still gives every SM a tile; 128x128 otherwise.
+    const long long tiles256 = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256);
+    const bool wide = N >= 256 && tiles256 >= kNumSMs;
+#define CGPT_GEMM_CASE(AM, BMN)                                                                  \
+    if (a_mn == AM && b_mn == BMN)                                                               \
+        return wide ? launch_tc<T, 256, AM != 0, BMN != 0>(C, A, B, M, N, K, accumulate, dtype, s) \
+                    : launch_tc<T, 128, AM != 0, BMN != 0>(C, A, B, M, N, K, accumulate, dtype, s);
+    CGPT_GEMM_CASE(0, 0)
+    CGPT_GEMM_CASE(0, 1)
+    CGPT_GEMM_CASE(1, 1)
+    CGPT_GEMM_CASE(1, 0)
+#undef CGPT_GEMM_CASE
+    return CGPT_ERR_OPTION;
+}
+
+}  // namespace
+
+// C[M,N] (+)= A * B. a_mn = 0: A stored [M,K] (K contiguous); 1: A stored [K,M]. b_mn = 0: B stored
+// [N,K]; 1: B stored [K,N]. Chooses the tensor-core kernel for 16-bit dtypes when TMA can address the
+// operands (16-byte aligned bases, leading dimensions a multiple of 8 elements), else the SIMT kernel.
+int gemm_dispatch(void* C, const void* A, const void* B, long long M, long long N, long long K, int a_mn, int b_mn,
+                  int accumulate, int dtype, bool force_simt, cudaStream_t s) {
+    if (!C || !A || !B) return CGPT_ERR_NULL;
+    if (!valid_float_dtype(dtype)) return CGPT_ERR_DTYPE;
+    if (M <= 0 || N <= 0 || K <= 0 || M > 0x7fffffffll || N > 0x7fffffffll || K > 0x7fffffffll) return CGPT_ERR_SHAPE;
+    const long long a_ld = a_mn ? M : K, b_ld = b_mn ? N : K;
+    const bool tc_ok = !force_simt && dtype != CGPT_DTYPE_F32 && aligned16(A) && aligned16(B) &&
+                       (reinterpret_cast<std::uintptr_t>(C) % 2 == 0) && a_ld % 8 == 0 && b_ld % 8 == 0 &&
+                       M * N >= 64 * 64 && K >= 32;
+    if (tc_ok) {
+        if (dtype == CGPT_DTYPE_F16)
+            return launch_tc_layout<__half>(static_cast<__half*>(C), static_cast<const __half*>(A), static_cast<const __half*>(B),
+                                            static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), a_mn, b_mn, accumulate, dtype, s);
+        return launch_tc_layout<__nv_bfloat16>(static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(A),
+                                               static_cast<const __nv_bfloat16*>(B), static_cast<int>(M), static_cast<int>(N),
+                                               static_cast<int>(K), a_mn, b_mn, accumulate, dtype, s);
+    }
+    const long long a_sm = a_mn ? 1 : K, a_sk = a_mn ? M : 1, b_sn = b_mn ? 1 : K, b_sk = b_mn ? N : 1;
+    const dim3 grid(static_cast<unsigned>((N + 63) / 64), static_cast<unsigned>((M + 63) / 64));
+    CGPT_DISPATCH_DTYPE(dtype, T, {
+        gemm_simt_kernel<T><<<grid, 256, 0, s>>>(static_cast<T*>(C), static_cast<const T*>(A), static_cast<const T*>(B),
+                                                 static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), a_sm, a_sk, b_sn,
+                                                 b_sk, accumulate);
+        count_launch();
+        CGPT_LAUNCH_CHECK();
+    });
+    return CGPT_OK;
+}
+
+int column_sum(void* out, const void* in, long long rows, long long cols, int accumulate, int dtype, cudaStream_t s) {
+    CGPT_DISPATCH_DTYPE(dtype, T, {
+        column_sum_kernel<T><<<static_cast<unsigned>((cols + 31) / 32), 256, 0, s>>>(
+            static_cast<T*>(out), static_cast<const T*>(in), rows, static_cast<int>(cols), accumulate);
+        count_launch();
+        CGPT_LAUNCH_CHECK();
+    });
+    return CGPT_OK;
+}
+
+}  // namespace cgpt
+
+using namespace cgpt;
+
+extern "C" int cgpt_gemm(void* c, const void* a, const void* b, size_t m, size_t n, size_t k, int a_layout,
+                         int b_layout, int accumulate, int dtype, int force_simt, cgpt_stream_t stream) {
+    return gemm_dispatch(c, a, b, static_cast<long long>(m), static_cast<long long>(n), static_cast<long long>(k),
+                         a_layout, b_layout, accumulate, dtype, force_simt != 0, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cgpt_linear_forward(void* y, const void* x, const void* w, size_t rows, size_t in_features,
+                                   size_t out_features, int dtype, cgpt_stream_t stream) {
+    return gemm_dispatch(y, x, w, static_cast<long long>(rows), static_cast<long long>(out_features),
+                         static_cast<long long>(in_features), 0, 0, 0, dtype, false, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cgpt_linear_backward(void* dx, void* dw, void* db, const void* dy, const void* x, const void* w,
+                                    size_t rows, size_t in_features, size_t out_features, int accumulate_input,
+                                    int accumulate_weight, int accumulate_bias, int dtype, cgpt_stream_t stream) {
+    if (!dy) return CGPT_ERR_NULL;
+    auto s = static_cast<cudaStream_t>(stream);
+    const long long T = static_cast<long long>(rows), I = static_cast<long long>(in_features), O = static_cast<long long>(out_features);
+    if (dx != nullptr) {
+        if (!w) return CGPT_ERR_NULL;
+        CGPT_TRY(gemm_dispatch(dx, dy, w, T, I, O, 0, 1, accumulate_input, dtype, false, s));   // dX = dY * W
+    }
+    if (dw != nullptr) {
+        if (!x) return CGPT_ERR_NULL;
+        CGPT_TRY(gemm_dispatch(dw, dy, x, O, I, T, 1, 1, accumulate_weight, dtype, false, s));  // dW = dY^T * X
+    }
+    if (db != nullptr) {
+        if (!valid_float_dtype(dtype) || T <= 0 || O <= 0) return CGPT_ERR_SHAPE;
+        CGPT_TRY(column_sum(db, dy, T, O, accumulate_bias, dtype, s));
+    }
+    return CGPT_OK;
+}
+
+extern "C" int cgpt_b200_device_status(unsigned int* status_out, int clear) {
+    if (!status_out) return CGPT_ERR_NULL;
+    unsigned int v = 0;
+    CGPT_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(v)));
+    if (clear && v != 0) {
+        const unsigned int zero = 0;
+        CGPT_CUDA_TRY(cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(zero)));
+    }
+    *status_out = v;
+    return CGPT_OK;
+}

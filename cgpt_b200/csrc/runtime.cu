@@ -50,6 +50,11 @@ int scratch_get(void** out, std::size_t bytes, cudaStream_t stream) {
 
 }  // namespace cgpt
 
+extern "C" int cgpt_b200_reserve_scratch(size_t bytes) {
+    void* p = nullptr;
+    return cgpt::scratch_get(&p, bytes, nullptr);
+}
+
 extern "C" const char* cgpt_b200_version(void) { return "cgpt_b200 0.1 (sm_100a)"; }
 extern "C" uint64_t cgpt_b200_launch_count(void) {
     return cgpt::g_launch_count.load(std::memory_order_relaxed);

@@ -61,6 +61,55 @@ def _ids(t: torch.Tensor, count: int, name: str) -> torch.Tensor:
     return t
 
 
+# ---------------------------------------------------------------------------------------------- Linear
+@dataclass
+class LinearBackwardOptions:
+    """include/ops/backward/linear_backward.h:10-21 (compute_type / workspace_bytes are accepted and
+    ignored: accumulation is always fp32 and scratch comes from the library's arena)."""
+    compute_type: str = "F32"
+    workspace_bytes: int = 32 * 1024 * 1024
+    accumulate_input: bool = False
+    accumulate_weight: bool = False
+    accumulate_bias: bool = False
+
+
+def linear_forward(output, input, weight, cublas_lt_context=None, stream=None, options=None):
+    """linear_forward(output, input, weight, context, stream, options): Y = X W^T (include/ops/linear.h)."""
+    _same_cuda_dtype("linear_forward", output, input, weight)
+    _require(weight.dim() == 2 and input.shape[-1] == weight.shape[1] and output.shape[-1] == weight.shape[0]
+             and output.numel() // weight.shape[0] == input.numel() // weight.shape[1],
+             "linear_forward: incompatible shapes")
+    rows = input.numel() // weight.shape[1]
+    check(lib.cgpt_linear_forward(ptr(output), ptr(input), ptr(weight), rows, weight.shape[1], weight.shape[0],
+                                  dtype_code(input), stream_ptr(stream)), "linear_forward")
+
+
+def linear_backward(grad_input, grad_weight, grad_bias, grad_output, input, weight, cublas_lt_context=None,
+                    stream=None, options: LinearBackwardOptions | None = None):
+    """linear_backward (include/ops/backward/linear_backward.h:36-46). Any of grad_input / grad_weight /
+    grad_bias may be None to skip that product (extension; the reference always computes all three)."""
+    o = options or LinearBackwardOptions()
+    outs = [t for t in (grad_input, grad_weight, grad_bias) if t is not None]
+    _same_cuda_dtype("linear_backward", grad_output, input, weight, *outs)
+    out_f, in_f = weight.shape
+    rows = input.numel() // in_f
+    _require(weight.dim() == 2 and input.shape[-1] == in_f and grad_output.shape[-1] == out_f
+             and grad_output.numel() == rows * out_f, "linear_backward: incompatible shapes")
+    _require(grad_input is None or grad_input.shape == input.shape, "linear_backward: grad_input shape")
+    _require(grad_weight is None or grad_weight.shape == weight.shape, "linear_backward: grad_weight shape")
+    _require(grad_bias is None or tuple(grad_bias.shape) == (out_f,), "linear_backward: grad_bias shape")
+    check(lib.cgpt_linear_backward(ptr(grad_input), ptr(grad_weight), ptr(grad_bias), ptr(grad_output), ptr(input),
+                                   ptr(weight), rows, in_f, out_f, int(o.accumulate_input), int(o.accumulate_weight),
+                                   int(o.accumulate_bias), dtype_code(input), stream_ptr(stream)), "linear_backward")
+
+
+def gemm(c, a, b, m, n, k, a_layout=0, b_layout=0, accumulate=False, force_simt=False, stream=None):
+    """Raw contraction C[m,n] (+)= A B of the library (see cgpt_gemm in include/cgpt_b200.h)."""
+    _same_cuda_dtype("gemm", c, a, b)
+    check(lib.cgpt_gemm(ptr(c), ptr(a), ptr(b), m, n, k, a_layout, b_layout, int(accumulate), dtype_code(c),
+                        int(force_simt), stream_ptr(stream)), "gemm")
+
+
 # --------------------------------------------------------------------------------------------- RMSNorm
 def rmsnorm_forward(output, input, weight, epsilon, stream=None):
     """rmsnorm_forward(Tensor& output, const Tensor& input, const Tensor& weight, float eps, stream)."""

@@ -51,6 +51,37 @@ const char* cgpt_b200_version(void);
  * region. */
 uint64_t cgpt_b200_launch_count(void);
 
+/* Reads (and with clear != 0 resets) the device status word of the tensor-core kernels. Every wait in
+ * those kernels (on an mbarrier fed by TMA or by tcgen05.commit) is bounded; a kernel whose wait ran out
+ * sets the word to non-zero and returns. Synchronises the device. */
+int cgpt_b200_device_status(unsigned int* status_out, int clear);
+/* Pre-sizes the per-device scratch arena so that later ops (and CUDA graphs that captured them) never
+ * see it move. Call outside stream capture. */
+int cgpt_b200_reserve_scratch(size_t bytes);
+
+/* ------------------------------------------------------------------------------------------------
+ * Linear layer Y = X W^T and its backward, fp32 accumulation.
+ * Replaces linear_forward (reference include/ops/linear.h:30-56, src/ops/linear.cu: cuBLASLt) and
+ * linear_backward (reference include/ops/backward/linear_backward.h:10-46,
+ * src/ops/backward/linear_backward.cu:135-148,181-200,268-285: two cuBLASLt GEMMs + a bias reduction):
+ *      dX[rows,in] = dY[rows,out] W[out,in];  dW[out,in] = dY^T X;  db[out] = sum_rows dY.
+ * dx, dw or db may be NULL to skip that product (the reference always computes all three; CGPT's model
+ * has no biases). accumulate_* != 0 adds to the existing output (read in storage dtype, added in fp32,
+ * rounded once), as the reference's beta = 1.
+ * 16-bit dtypes run on the tensor cores (tcgen05 + TMA) when bases are 16-byte aligned and in/out
+ * features are multiples of 8; everything else (fp32 tensors, odd shapes) runs a plain fp32 SIMT kernel.
+ *
+ * cgpt_gemm is the underlying contraction C[m,n] (+)= A B: a_layout 0 = A stored [m,k], 1 = [k,m];
+ * b_layout 0 = B stored [n,k], 1 = [k,n]; force_simt != 0 selects the SIMT kernel (for tests).
+ * ---------------------------------------------------------------------------------------------- */
+int cgpt_gemm(void* c, const void* a, const void* b, size_t m, size_t n, size_t k, int a_layout,
+              int b_layout, int accumulate, int dtype, int force_simt, cgpt_stream_t stream);
+int cgpt_linear_forward(void* y, const void* x, const void* w, size_t rows, size_t in_features,
+                        size_t out_features, int dtype, cgpt_stream_t stream);
+int cgpt_linear_backward(void* dx, void* dw, void* db, const void* dy, const void* x, const void* w,
+                         size_t rows, size_t in_features, size_t out_features, int accumulate_input,
+                         int accumulate_weight, int accumulate_bias, int dtype, cgpt_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------
  * RMSNorm  y = x * rsqrt(mean(x^2) + eps) * w
  * Replaces rmsnorm_forward  (reference include/ops/rmsnorm.h:36-52, src/ops/rmsnorm.cu:812-906)

@@ -1,0 +1,37 @@
+"""Helpers shared by the ``-m gpu`` parity tests."""
+import numpy as np
+import torch
+
+TORCH = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
+# max |a-b| relative to the RMS of the expected tensor (the "fp32 norm-scaled" error of the parity bar)
+TOL = {"f32": 2e-5, "f16": 2e-3, "bf16": 1.6e-2}
+
+
+def dev(a, dt="f32"):
+    """numpy -> CUDA tensor of storage dtype `dt` (round to nearest even, like Tensor::copy_from_host)."""
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to("cuda").to(TORCH[dt]).contiguous()
+
+
+def ids_dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.int64)).to(torch.int32).to("cuda")
+
+
+def host(t):
+    return t.detach().to(torch.float32).cpu().numpy()
+
+
+def rounded(t):
+    """The values a device tensor actually holds, as fp32 numpy (inputs for the oracle)."""
+    return host(t)
+
+
+def scaled_err(got, want):
+    got = np.asarray(got, np.float64); want = np.asarray(want, np.float64)
+    rms = np.sqrt(np.mean(want ** 2))
+    return float(np.max(np.abs(got - want)) / max(rms, 1e-30))
+
+
+def assert_close(got, want, tol, what=""):
+    e = scaled_err(got, want)
+    assert np.all(np.isfinite(np.asarray(got))), f"{what}: non-finite output"
+    assert e <= tol, f"{what}: norm-scaled max error {e:.3e} > {tol:.1e}"

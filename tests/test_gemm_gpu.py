@@ -1,0 +1,108 @@
+"""GPU parity of the tcgen05 GEMM / linear forward / linear backward (through the C ABI).
+
+The contraction is a floating-point kernel, so it is compared with a plain fp32 matmul of the same
+16-bit inputs (torch on the GPU, numpy oracle for the reference's known answers). Tolerance: the output
+is rounded once to the storage dtype, so the norm-scaled max error must stay below 4e-3 (fp16) /
+3e-2 (bf16); the parity bar for fp16-path gradients is 1e-2.
+"""
+import numpy as np
+import pytest
+import torch
+
+import known_answers as KA
+from gpu_util import assert_close, dev, host
+from oracle import cgpt_oracle as O
+
+pytestmark = pytest.mark.gpu
+TOL = {torch.float16: 4e-3, torch.bfloat16: 3e-2, torch.float32: 1e-5}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from cgpt_b200 import ops as m
+    return m
+
+
+def _operands(m, n, k, a_layout, b_layout, dtype, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    a = torch.randn((k, m) if a_layout else (m, k), generator=g, device="cuda").to(dtype)
+    b = torch.randn((k, n) if b_layout else (n, k), generator=g, device="cuda").to(dtype)
+    a32 = a.float().t() if a_layout else a.float()
+    b32 = b.float() if b_layout else b.float().t()
+    return a, b, a32 @ b32
+
+
+SHAPES = [(128, 128, 64), (128, 128, 16), (128, 256, 128), (256, 128, 192), (128, 128, 1024), (384, 640, 1000),
+          (200, 136, 72), (4096, 1024, 1024), (1024, 1024, 8192), (256, 1024, 8192), (2048, 1024, 4096), (512, 32000, 256)]
+
+
+@pytest.mark.parametrize("a_layout,b_layout", [(0, 0), (0, 1), (1, 1), (1, 0)])
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_gemm_f16_layouts(ops, m, n, k, a_layout, b_layout):
+    a, b, want = _operands(m, n, k, a_layout, b_layout, torch.float16, m + n + k)
+    c = torch.full((m, n), float("nan"), device="cuda", dtype=torch.float16)
+    ops.gemm(c, a, b, m, n, k, a_layout, b_layout)
+    torch.cuda.synchronize()
+    assert_close(host(c), host(want) / 1.0, TOL[torch.float16], f"gemm {m}x{n}x{k} layouts {a_layout}{b_layout}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_gemm_other_dtypes(ops, dtype):
+    for a_layout, b_layout in [(0, 0), (0, 1), (1, 1)]:
+        a, b, want = _operands(256, 384, 512, a_layout, b_layout, dtype, 9)
+        c = torch.empty((256, 384), device="cuda", dtype=dtype)
+        ops.gemm(c, a, b, 256, 384, 512, a_layout, b_layout)
+        assert_close(host(c), host(want), TOL[dtype], f"{dtype} {a_layout}{b_layout}")
+
+
+def test_gemm_accumulate_and_simt_agree(ops):
+    a, b, want = _operands(256, 256, 512, 0, 1, torch.float16, 4)
+    c0 = torch.randn((256, 256), device="cuda").half()
+    c = c0.clone()
+    ops.gemm(c, a, b, 256, 256, 512, 0, 1, accumulate=True)
+    assert_close(host(c), host(want + c0.float()), TOL[torch.float16], "accumulate")
+    c2 = c0.clone()
+    ops.gemm(c2, a, b, 256, 256, 512, 0, 1, accumulate=True, force_simt=True)
+    assert_close(host(c2), host(c), 2e-3, "simt vs tensor core")
+
+
+def test_linear_backward_known_answers(ops):
+    c = KA.LINEAR_BWD
+    x, w, dy = dev(c["input"]), dev(c["weight"]), dev(c["grad_output"])
+    dx, dw, db = torch.empty_like(x), torch.empty_like(w), torch.empty(2, device="cuda")
+    ops.linear_backward(dx, dw, db, dy, x, w)
+    np.testing.assert_allclose(host(dx), c["grad_input"], atol=1e-5); np.testing.assert_allclose(host(dw), c["grad_weight"], atol=1e-5)
+    np.testing.assert_allclose(host(db), c["grad_bias"], atol=1e-5)
+    ops.linear_backward(dx, dw, db, dy, x, w, None, None, ops.LinearBackwardOptions(accumulate_input=True, accumulate_weight=True, accumulate_bias=True))
+    np.testing.assert_allclose(host(dx), 2 * c["grad_input"], atol=1e-5); np.testing.assert_allclose(host(dw), 2 * c["grad_weight"], atol=1e-5)
+    np.testing.assert_allclose(host(db), 2 * c["grad_bias"], atol=1e-5)
+    c = KA.LINEAR_BWD_F16
+    x, w, dy = dev(c["input"], "f16"), dev(c["weight"], "f16"), dev(c["grad_output"], "f16")
+    dx, dw, db = torch.empty_like(x), torch.empty_like(w), torch.empty(3, device="cuda", dtype=torch.float16)
+    ops.linear_backward(dx, dw, db, dy, x, w)
+    np.testing.assert_allclose(host(dx), c["grad_input"], atol=0.1); np.testing.assert_allclose(host(dw), c["grad_weight"], atol=0.2)
+    np.testing.assert_allclose(host(db), c["grad_bias"], atol=0.1)
+
+
+@pytest.mark.parametrize("rows,inf,outf", [(256, 256, 256), (256, 256, 688), (256, 688, 256), (4096, 1024, 2048), (512, 768, 32000), (1000, 64, 128)])
+def test_linear_forward_backward_model_shapes(ops, rows, inf, outf):
+    g = torch.Generator(device="cuda").manual_seed(rows + inf)
+    x = torch.randn((rows, inf), generator=g, device="cuda").half()
+    w = (0.05 * torch.randn((outf, inf), generator=g, device="cuda")).half()
+    dy = torch.randn((rows, outf), generator=g, device="cuda").half()
+    y, dx, dw = torch.empty((rows, outf), device="cuda", dtype=torch.float16), torch.empty_like(x), torch.empty_like(w)
+    db = torch.empty(outf, device="cuda", dtype=torch.float16)
+    ops.linear_forward(y, x, w)
+    ops.linear_backward(dx, dw, db, dy, x, w)
+    assert_close(host(y), host(x.float() @ w.float().t()), 4e-3, "y")
+    assert_close(host(dx), host(dy.float() @ w.float()), 4e-3, "dx")
+    assert_close(host(dw), host(dy.float().t() @ x.float()), 4e-3, "dw")
+    assert_close(host(db), host(dy.float().sum(0)), 4e-3, "db")
+    dx2 = dx.clone()
+    ops.linear_backward(dx2, None, None, dy, x, w, None, None, ops.LinearBackwardOptions(accumulate_input=True))
+    assert_close(host(dx2), 2 * host(dy.float() @ w.float()), 5e-3, "dx accumulate")
+
+
+def test_device_status_clean(ops):
+    from cgpt_b200 import _lib
+    assert _lib.device_status(clear=False) == 0, "a tensor-core kernel gave up on a bounded wait"
