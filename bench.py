@@ -1,0 +1,277 @@
+"""Benchmark of the training hot path: one step = forward + cut-cross-entropy loss + backward + AdamW of the
+reference's `104m` preset (8 layers, d 1024, 8 Q / 2 KV heads, head_dim 128, SwiGLU 2048, vocab 32000, tied
+embedding) at batch 32 x seq 1024 per GPU, fp16 activations/weights, fp32 master weights, loss scale 1024.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N > 1 is launched with torch.distributed.run (one rank per GPU, NCCL): pure data parallelism, gradients
+averaged with bucketed all-reduces, per-GPU work fixed (weak scaling). Rank 0 prints one JSON line.
+
+`value` is whole-job tokens/s with the batch already in HBM, timed on the device (CUDA events, max over
+ranks); `e2e` includes the pinned-host -> device copy of every step's token ids / targets and the
+device -> host read of the loss. `roofline` describes the dominant kernel (the tcgen05 GEMM): algorithmic
+FLOPs of the GEMM launches of one step / their summed CUDA-event durations, against the measured cuBLAS
+bf16 peak in MEASURED_PEAKS.json. `cpu_baseline` times the reference's own CPU forward + loss (its only CPU
+path for this model) on a bounded sample on the host cores.
+
+`--impl reference` times only that CPU path (all host threads) and prints the same line shape.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "104m_train_tokens_per_s"
+UNIT = "tokens/s"
+PRESET = "104m"
+BATCH, SEQ = 32, 1024
+PUBLISHED_TOKENS_PER_S = 151400.0   # reference README.md:168 (4.62 steps/s at 32 x 1024, hardware not stated)
+
+
+def workload_config(n_gpus: int) -> dict:
+    return {"workload": "cgpt 104m preset training step (L8 d1024 Hq8/Hkv2 D128 I2048 V32000 tied), fp16 + fp32 master, "
+                        "loss scale 1024, AdamW lr 3e-4 b(.9,.95) wd .1 clip 1.0, cut-cross-entropy loss",
+            "batch_per_gpu": BATCH, "seq_len": SEQ, "global_batch": BATCH * n_gpus, "parallelism": f"dp{n_gpus}",
+            "l2": "working set per step (activations + weights, several GB) is far larger than the 126 MB L2; no flush needed"}
+
+
+# ------------------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons every 200 ms while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.samples, self.proc, self.thread, self.index = [], None, None, device_index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 9:
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        return False
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], 0, set()
+        for p in self.samples:
+            try:
+                sm.append(float(p[1])); mx = max(mx, float(p[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# -------------------------------------------------------------------------------------------- CPU baseline
+def cpu_baseline(threads: int | None, batch: int = 2, seq: int = 256, repeats: int = 3) -> dict:
+    """Times the reference's CPU forward + cross-entropy loss of the 104m model (oracle/_ref, built from the
+    reference's own src/ops/cpu sources) on a bounded sample of batch x seq tokens."""
+    import numpy as np
+    from oracle import ref_cpu
+    if threads:
+        os.environ["OMP_NUM_THREADS"] = str(threads)
+    if not ref_cpu.available():
+        return {"value": None, "unit": UNIT, "cores": 0, "kind": "reference", "sample": "oracle/_ref/libcgpt_ref_cpu.so is missing"}
+    layers, d, hq, hkv, hd, inter, vocab = 8, 1024, 8, 2, 128, 2048, 32000
+    rng = np.random.default_rng(0)
+    per_layer = d + hq * hd * d + hkv * hd * d + hd + hd + hkv * hd * d + d * hq * hd + d + inter * d + inter * d + d * inter
+    flat = (0.02 * rng.standard_normal(vocab * d + layers * per_layer + d)).astype(np.float32)
+    # norm weights = 1 (positions inside the flat layout)
+    off = vocab * d
+    for _ in range(layers):
+        flat[off:off + d] = 1; o2 = off + d + hq * hd * d + hkv * hd * d
+        flat[o2:o2 + 2 * hd] = 1; o3 = o2 + 2 * hd + hkv * hd * d + d * hq * hd
+        flat[o3:o3 + d] = 1
+        off += per_layer
+    flat[off:off + d] = 1
+    tokens = rng.integers(0, vocab, (batch, seq + 1))
+    secs, loss = ref_cpu.cpu_forward_loss(flat, tokens[:, :-1], tokens[:, 1:], batch, seq, layers, d, hq, hkv, hd, inter, vocab, 1e-5, repeats)
+    cores = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+    return {"value": batch * seq / secs, "unit": UNIT, "cores": cores, "kind": "reference",
+            "sample": f"reference CPU ops (src/ops/cpu, -O3 -mavx2 -mfma -mf16c, OpenMP) forward + cross-entropy loss only "
+                      f"(the reference has no CPU training step), 104m model, batch {batch} x seq {seq}, median of {repeats}; "
+                      f"linear_forward_cpu is single-threaded for rows > 1; {secs:.2f} s per pass, loss {loss:.4f}",
+            "seconds_per_pass": secs}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 3))
+    base = cpu_baseline(None, batch=2, seq=256, repeats=steps)
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": None if base["value"] is None else 1000.0 * BATCH * SEQ / base["value"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args.gpus), "cpu_baseline": {k: v for k, v in base.items() if k != "seconds_per_pass"},
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------ our arm
+def measured_peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return json.loads(p.read_text())
+        except json.JSONDecodeError:
+            pass
+    return {}
+
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    pg = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        pg = dist.group.WORLD
+    from cgpt_b200 import _lib, model as M
+    from cgpt_b200.train import TrainStep
+
+    opts = M.preset(PRESET)
+    ts = TrainStep(opts, BATCH, SEQ, seed=0, process_group=pg)
+    rows = BATCH * SEQ
+    gen = torch.Generator().manual_seed(1234 + rank)
+    pool = 4
+    host_tokens = [torch.randint(0, opts.vocabulary_size, (BATCH, SEQ + 1), generator=gen, dtype=torch.int32) for _ in range(pool)]
+    host_ids = [t[:, :-1].contiguous().pin_memory() for t in host_tokens]
+    host_tgt = [t[:, 1:].contiguous().pin_memory() for t in host_tokens]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # launches of one model step (forward + loss + backward), counted on the eager warm-up inside step()
+    ts.upload_batch(host_ids[0], host_tgt[0])
+    c0 = _lib.launch_count()
+    ts.step()
+    ts.stream.synchronize()
+    launches_first = _lib.launch_count() - c0       # eager pass + capture pass + 3 optimizer launches
+    model_launches = (launches_first - 3) // 2
+    for _ in range(max(0, args.warmup - 1)):
+        ts.step()
+    barrier()
+
+    # ---- device-resident timing: K steps, CUDA events on the step's stream, max over ranks
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        barrier()
+        with torch.cuda.stream(ts.stream):
+            e0.record()
+        for _ in range(args.steps):
+            ts.step()
+        with torch.cuda.stream(ts.stream):
+            e1.record()
+        barrier()
+    ms_total = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms_total, op=dist.ReduceOp.MAX)
+    ms_step = float(ms_total.item()) / args.steps
+    value = world * rows / (ms_step / 1000.0)
+    final_loss = ts.read_loss()
+    ok = ts.check()
+
+    # ---- end to end: pinned host -> device ids/targets every step, loss read back every step
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        ts.upload_batch(host_ids[i % pool], host_tgt[i % pool])
+        ts.step()
+        ts.read_loss()
+    barrier()
+    e2e_s = torch.tensor([time.perf_counter() - t0], device="cuda")
+    if world > 1:
+        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+    e2e_value = world * rows * args.steps / float(e2e_s.item())
+
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": (value / world) / PUBLISHED_TOKENS_PER_S, "dtype": "f16", "data": "synthetic",
+            "config": workload_config(world),
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 2 * rows * 4, "d2h_bytes_per_step": 4},
+            "gpu_launches": args.steps * (model_launches + 3), "clocks": clocks.summary(),
+            "final_loss": final_loss, "optimizer_ok": bool(ok), "device_status": _lib.device_status(clear=False)}
+
+    if rank == 0:
+        # ---- roofline of the dominant kernel (tcgen05 GEMM): eager re-run with CUDA events around every GEMM launch
+        try:
+            from cgpt_b200 import profiling
+            gemm = profiling.time_gemms(ts)
+            peaks = measured_peaks()
+            peak = peaks.get("bf16_tflops_sustained")
+            which = "measured (MEASURED_PEAKS.json bf16_tflops_sustained; B200 fp16 and bf16 dense rates are equal)"
+            if peak is None:
+                peak, which = 1400.0, "fallback (1.4 PFLOP/s sustained)"
+            line["roofline"] = {"bound": "tensor", "achieved": gemm["tflops"], "peak": peak, "unit": "TFLOP/s",
+                                "frac": gemm["tflops"] / peak, "traffic": None, "kernel": "gemm_tcgen05_kernel",
+                                "launches_per_step": gemm["launches"], "ms_per_step_in_kernel": gemm["ms"],
+                                "share_of_step": gemm["ms"] / ms_step, "peak_source": which,
+                                "model_flops_per_step": gemm["model_flops"], "model_tflops": gemm["model_flops"] / ms_step / 1e9}
+        except Exception as exc:  # the bench line must still be printed
+            line["roofline"] = {"bound": "tensor", "achieved": None, "peak": None, "unit": "TFLOP/s", "frac": None,
+                                "traffic": None, "error": repr(exc)}
+        try:
+            line["cpu_baseline"] = {k: v for k, v in cpu_baseline(None).items() if k != "seconds_per_pass"} if world == 1 else None
+        except Exception as exc:
+            line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "reference", "sample": repr(exc)}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

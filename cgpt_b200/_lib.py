@@ -56,14 +56,57 @@ class AdamWOptions(C.Structure):
                 ("weight_decay", _f), ("loss_scale", _f), ("max_grad_norm", _f)]
 
 
+BLOCK_PARAM_FIELDS = ("attention_norm", "q_projection", "k_projection", "q_norm", "k_norm", "v_projection",
+                      "o_projection", "ffn_norm", "gate_proj", "up_proj", "down_proj")
+BLOCK_SAVED_FIELDS = ("norm", "query", "key", "value", "query_pre_norm", "key_pre_norm", "attention_output",
+                      "attention_logsumexp", "gate", "up", "activated")
+
+
+class BlockParams(C.Structure):
+    _fields_ = [(n, _vp) for n in BLOCK_PARAM_FIELDS]
+
+
+class BlockSaved(C.Structure):
+    _fields_ = [(n, _vp) for n in BLOCK_SAVED_FIELDS]
+
+
+class ModelConfig(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("vocab", "layers", "hidden", "intermediate", "q_heads", "kv_heads",
+                                          "head_dim", "rotary_dim", "max_seq")] + \
+               [("rms_epsilon", _f), ("dtype", C.c_int32), ("tied_embeddings", C.c_int32), ("reserved", C.c_int32)]
+
+
+class ModelTensors(C.Structure):
+    _fields_ = [("token_embedding", _vp), ("layers", C.POINTER(BlockParams)), ("final_norm", _vp), ("lm_head", _vp)]
+
+
+class ModelSaved(C.Structure):
+    _fields_ = [("layers", C.POINTER(BlockSaved)), ("layer_inputs", C.POINTER(_vp)), ("hidden", _vp),
+                ("normalized", _vp)]
+
+
+_pBP, _pBS, _pMC, _pMT, _pMS = (C.POINTER(BlockParams), C.POINTER(BlockSaved), C.POINTER(ModelConfig),
+                                C.POINTER(ModelTensors), C.POINTER(ModelSaved))
+
 SIGNATURES = {
+    "cgpt_cut_cross_entropy": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _f, _i, _sz, _i, _vp]),
+    "cgpt_block_workspace_bytes": (_sz, [_pMC, _sz, _sz]),
+    "cgpt_block_forward": (_i, [_vp, _vp, _pBP, _pBS, _vp, _vp, _vp, _pMC, _sz, _sz, _sz, _vp]),
+    "cgpt_block_backward": (_i, [_vp, _vp, _vp, _pBP, _pBP, _pBS, _vp, _vp, _vp, _pMC, _sz, _sz, _sz, _vp]),
+    "cgpt_model_forward": (_i, [_vp, _vp, _pMT, _pMS, _vp, _vp, _vp, _pMC, _sz, _sz, _vp]),
+    "cgpt_model_backward": (_i, [_vp, _vp, _vp, _pMT, _pMT, _pMS, _vp, _vp, _vp, _pMC, _sz, _sz, _vp]),
     "cgpt_b200_version": (C.c_char_p, []),
     "cgpt_b200_launch_count": (C.c_uint64, []),
     "cgpt_b200_device_status": (_i, [C.POINTER(C.c_uint), _i]),
     "cgpt_b200_reserve_scratch": (_i, [_sz]),
+    "cgpt_b200_gemm_timing": (_i, [_i]),
+    "cgpt_b200_gemm_timing_read": (_i, [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(_u64)]),
     "cgpt_gemm": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _i, _i, _i, _i, _i, _vp]),
     "cgpt_linear_forward": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _i, _vp]),
     "cgpt_linear_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _i, _i, _i, _i, _vp]),
+    "cgpt_attention_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _f, _i, _sz, _i, _i, _vp]),
+    "cgpt_attention_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _f, _i,
+                                     _sz, _i, _i, _i, _vp]),
     "cgpt_rmsnorm_forward": (_i, [_vp, _vp, _vp, _sz, _sz, _f, _i, _vp]),
     "cgpt_rmsnorm_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _f, _i, _vp]),
     "cgpt_rope_forward": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _i, _vp]),

@@ -46,6 +46,21 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<std::uintptr_t>(
 // Every kernel that needs global scratch and was not handed a caller workspace takes it from here.
 int scratch_get(void** out, std::size_t bytes, cudaStream_t stream);
 
+// Holds `bytes` of the arena for the lifetime of the object, so that ops called meanwhile (which use
+// scratch_get themselves) are placed behind it. `inner_headroom` is the most scratch those inner ops may
+// ask for; the arena is grown to bytes + inner_headroom up front because it cannot move while held.
+struct ScratchFrame {
+    ScratchFrame(std::size_t bytes, std::size_t inner_headroom, cudaStream_t stream);
+    ~ScratchFrame();
+    ScratchFrame(const ScratchFrame&) = delete;
+    ScratchFrame& operator=(const ScratchFrame&) = delete;
+    void* ptr = nullptr;
+    int status = CGPT_OK;
+
+private:
+    std::size_t held_ = 0;
+};
+
 // ---------------------------------------------------------------------------------------------
 // Scalar conversion
 // ---------------------------------------------------------------------------------------------

@@ -42,7 +42,7 @@ __device__ __forceinline__ float block_sum_512(float v, float* red) {
 
 template <typename T, bool STAGED>
 __global__ void __launch_bounds__(kCeThreads)
-cross_entropy_kernel(float* __restrict__ row_loss, T* __restrict__ grad, const T* __restrict__ logits,
+cross_entropy_kernel(float* __restrict__ row_loss, T* grad, const T* logits,
                      const std::uint32_t* __restrict__ targets, long long rows, int vocab, float inv_rows,
                      float gradient_scale) {
     extern __shared__ __align__(16) unsigned char ce_smem[];
@@ -109,6 +109,37 @@ int sum_floats(float* out, const float* in, long long n, cudaStream_t s) {
 
 using namespace cgpt;
 
+namespace cgpt {
+// Per-row losses (already divided by total_rows) and, when grad != nullptr, the scaled gradient for
+// `rows` rows. grad may alias logits (every thread rewrites exactly the elements it read).
+int cross_entropy_rows(float* row_loss, void* grad, const void* logits, const std::uint32_t* targets, long long rows,
+                       long long vocab, float inv_total_rows, float gradient_scale, int dtype, cudaStream_t s) {
+    const std::size_t row_bytes = static_cast<std::size_t>(vocab) * dtype_size(dtype);
+    const bool staged = row_bytes <= 200 * 1024;
+    const unsigned grid = static_cast<unsigned>(rows < kNumSMs * 4ll ? rows : kNumSMs * 4ll);
+    CGPT_DISPATCH_DTYPE(dtype, T, {
+        if (staged) {
+            static bool attr_done = false;
+            if (!attr_done) {
+                CGPT_CUDA_TRY(cudaFuncSetAttribute(cross_entropy_kernel<T, true>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+                attr_done = true;
+            }
+            cross_entropy_kernel<T, true><<<grid, kCeThreads, row_bytes, s>>>(
+                row_loss, static_cast<T*>(grad), static_cast<const T*>(logits), targets, rows, static_cast<int>(vocab),
+                inv_total_rows, gradient_scale);
+        } else {
+            cross_entropy_kernel<T, false><<<grid, kCeThreads, 0, s>>>(
+                row_loss, static_cast<T*>(grad), static_cast<const T*>(logits), targets, rows, static_cast<int>(vocab),
+                inv_total_rows, gradient_scale);
+        }
+        count_launch();
+        CGPT_LAUNCH_CHECK();
+    });
+    return CGPT_OK;
+}
+}  // namespace cgpt
+
 extern "C" int cgpt_cross_entropy(float* loss, void* grad, const void* logits, const uint32_t* targets,
                                   size_t rows, size_t vocab, float gradient_scale, int dtype,
                                   cgpt_stream_t stream) {
@@ -118,28 +149,7 @@ extern "C" int cgpt_cross_entropy(float* loss, void* grad, const void* logits, c
     auto s = static_cast<cudaStream_t>(stream);
     void* scratch = nullptr;
     CGPT_TRY(scratch_get(&scratch, rows * sizeof(float), s));
-    const float inv_rows = 1.0f / static_cast<float>(rows);
-    const std::size_t row_bytes = vocab * dtype_size(dtype);
-    const bool staged = row_bytes <= 200 * 1024;
-    const unsigned grid = static_cast<unsigned>(rows < kNumSMs * 4ull ? rows : kNumSMs * 4ull);
-    CGPT_DISPATCH_DTYPE(dtype, T, {
-        if (staged) {
-            static bool attr_done[3] = {false, false, false};
-            if (!attr_done[dtype]) {
-                CGPT_CUDA_TRY(cudaFuncSetAttribute(cross_entropy_kernel<T, true>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-                attr_done[dtype] = true;
-            }
-            cross_entropy_kernel<T, true><<<grid, kCeThreads, row_bytes, s>>>(
-                static_cast<float*>(scratch), static_cast<T*>(grad), static_cast<const T*>(logits), targets,
-                static_cast<long long>(rows), static_cast<int>(vocab), inv_rows, gradient_scale);
-        } else {
-            cross_entropy_kernel<T, false><<<grid, kCeThreads, 0, s>>>(
-                static_cast<float*>(scratch), static_cast<T*>(grad), static_cast<const T*>(logits), targets,
-                static_cast<long long>(rows), static_cast<int>(vocab), inv_rows, gradient_scale);
-        }
-        count_launch();
-        CGPT_LAUNCH_CHECK();
-    });
+    CGPT_TRY(cross_entropy_rows(static_cast<float*>(scratch), grad, logits, targets, static_cast<long long>(rows),
+                                static_cast<long long>(vocab), 1.0f / static_cast<float>(rows), gradient_scale, dtype, s));
     return sum_floats(loss, static_cast<const float*>(scratch), static_cast<long long>(rows), s);
 }

@@ -16,6 +16,7 @@
 // e.g. dW with K = tokens). Algorithmic work: 2*M*N*K flops.
 #include <mutex>
 #include <type_traits>
+#include <vector>
 
 #include "launch_counter.h"
 #include "sm100.cuh"
@@ -81,6 +82,16 @@ template <int BN> struct GemmCfg {
 __device__ unsigned int g_gemm_status = 0;
 
 enum : int { kEpiStore = 0, kEpiAccumulate = 1, kEpiPartial = 2 };
+
+// Optional timing of the tensor-core GEMM launches (eager mode only, never during stream capture):
+// a CUDA event pair around every gemm_tcgen05_kernel launch plus its algorithmic FLOPs.
+struct GemmTiming {
+    bool enabled = false;
+    std::vector<cudaEvent_t> events;   // pairs
+    std::vector<double> flops;
+    std::size_t used = 0;              // events used
+};
+GemmTiming g_timing;
 
 template <typename T, int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -379,9 +390,16 @@ int launch_tc(T* C, const T* A, const T* B, int M, int N, int K, int accumulate,
     }
     const dim3 grid(tiles_m, tiles_n, splits);
     const int epi = splits > 1 ? kEpiPartial : (accumulate ? kEpiAccumulate : kEpiStore);
+    const bool timed = g_timing.enabled && g_timing.used + 2 <= g_timing.events.size();
+    if (timed) CGPT_CUDA_TRY(cudaEventRecord(g_timing.events[g_timing.used], s));
     kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, C, partial, M, N, K, kb_per_split, epi);
     count_launch();
     CGPT_LAUNCH_CHECK();
+    if (timed) {
+        CGPT_CUDA_TRY(cudaEventRecord(g_timing.events[g_timing.used + 1], s));
+        g_timing.used += 2;
+        g_timing.flops.push_back(2.0 * M * N * K);
+    }
     if (splits > 1) {
         const long long mn = static_cast<long long>(M) * N;
         long long blocks = (mn / 4 + 255) / 256;
@@ -502,5 +520,32 @@ extern "C" int cgpt_b200_device_status(unsigned int* status_out, int clear) {
         CGPT_CUDA_TRY(cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(zero)));
     }
     *status_out = v;
+    return CGPT_OK;
+}
+
+extern "C" int cgpt_b200_gemm_timing(int enable) {
+    g_timing.used = 0;
+    g_timing.flops.clear();
+    if (enable && g_timing.events.empty()) {
+        g_timing.events.resize(8192);
+        for (auto& e : g_timing.events) CGPT_CUDA_TRY(cudaEventCreate(&e));
+    }
+    g_timing.enabled = enable != 0;
+    return CGPT_OK;
+}
+
+extern "C" int cgpt_b200_gemm_timing_read(double* total_ms, double* total_flops, uint64_t* launches) {
+    if (!total_ms || !total_flops || !launches) return CGPT_ERR_NULL;
+    CGPT_CUDA_TRY(cudaDeviceSynchronize());
+    double ms = 0.0, fl = 0.0;
+    for (std::size_t i = 0; i + 1 < g_timing.used; i += 2) {
+        float t = 0.f;
+        CGPT_CUDA_TRY(cudaEventElapsedTime(&t, g_timing.events[i], g_timing.events[i + 1]));
+        ms += t;
+        fl += g_timing.flops[i / 2];
+    }
+    *total_ms = ms;
+    *total_flops = fl;
+    *launches = g_timing.used / 2;
     return CGPT_OK;
 }

@@ -1,0 +1,225 @@
+// Host-side orchestration of one transformer block and of the whole model, forward and backward, on
+// top of the kernels of this library. Pure C++ host code: it only sequences launches on the caller's
+// stream, never synchronises and never allocates (scratch comes from the caller's workspace), so a whole
+// step can be captured into a CUDA graph.
+//
+// The operator graph is the reference's (src/core/transformer_block.cu:466-595 forward, :644-748 backward;
+// src/core/transformer_model.cu:170-218, :336-381), with these differences in how it is executed:
+//   * projections are written straight into the tensors that the backward needs (no D2D copies of
+//     query/key into *_pre_norm, no copy of the hidden state into layer_inputs);
+//   * the two residual adds of the forward are one three-input add; the two add_inplace passes and two D2D
+//     copies of the backward are folded into the RMSNorm-backward kernels (residual operands);
+//   * bias gradients are not computed (the model has no biases; the reference reduces them anyway);
+//   * one backward workspace serves all layers (the reference allocates one per layer).
+#include "internal.h"
+
+using namespace cgpt;
+
+namespace {
+
+struct Dims {
+    std::size_t rows, d, inter, hq, hkv, hd, qdim, kvdim, esz;
+};
+
+int check_cfg(const cgpt_model_config* c, std::size_t batch, std::size_t seq, Dims* out) {
+    if (!c) return CGPT_ERR_NULL;
+    if (!valid_float_dtype(c->dtype)) return CGPT_ERR_DTYPE;
+    if (batch == 0 || seq == 0 || c->hidden == 0 || c->intermediate == 0 || c->q_heads == 0 || c->kv_heads == 0 ||
+        c->head_dim == 0 || c->q_heads % c->kv_heads != 0)
+        return CGPT_ERR_SHAPE;
+    if (c->rotary_dim > c->head_dim || (c->rotary_dim & 1) != 0 || !(c->rms_epsilon > 0.f)) return CGPT_ERR_OPTION;
+    // The reference's block requires hidden == q_heads * head_dim (it reshapes the attention output to
+    // [rows, hidden], transformer_block.cu:571).
+    if (c->q_heads * c->head_dim != c->hidden) return CGPT_ERR_SHAPE;
+    *out = Dims{batch * seq, static_cast<std::size_t>(c->hidden), static_cast<std::size_t>(c->intermediate),
+                static_cast<std::size_t>(c->q_heads), static_cast<std::size_t>(c->kv_heads),
+                static_cast<std::size_t>(c->head_dim), static_cast<std::size_t>(c->q_heads * c->head_dim),
+                static_cast<std::size_t>(c->kv_heads * c->head_dim), dtype_size(c->dtype)};
+    return CGPT_OK;
+}
+
+// Bump allocator over the caller's workspace.
+struct Carver {
+    unsigned char* p;
+    std::size_t used = 0;
+    explicit Carver(void* base) : p(static_cast<unsigned char*>(base)) {}
+    void* take(std::size_t bytes) {
+        void* r = p ? p + used : nullptr;
+        used += (bytes + 255) & ~std::size_t{255};
+        return r;
+    }
+};
+
+struct BlockScratch {
+    void *attn_proj, *ffn_out;                       // forward
+    void *d_act, *d_gate, *d_up, *d_ffn_norm_in;     // backward, MLP branch
+    void *d_attn_out, *dq, *dk, *dv, *dq_pre, *dk_pre, *norm_a, *d_attn_norm_in;
+    void *grad_a, *grad_b;                           // model backward ping-pong
+    std::size_t bytes;
+};
+
+BlockScratch carve(void* base, const Dims& m) {
+    Carver c(base);
+    BlockScratch s;
+    const std::size_t rd = m.rows * m.d * m.esz, ri = m.rows * m.inter * m.esz, rq = m.rows * m.qdim * m.esz,
+                      rk = m.rows * m.kvdim * m.esz;
+    // forward and backward scratch never live at the same time, so they overlay each other
+    s.attn_proj = c.take(rd);
+    s.ffn_out = c.take(rd);
+    const std::size_t fwd_used = c.used;
+    c.used = 0;
+    s.d_act = c.take(ri);
+    s.d_gate = c.take(ri);
+    s.d_up = c.take(ri);
+    s.d_ffn_norm_in = c.take(rd);
+    s.d_attn_out = c.take(rq);
+    s.dq = c.take(rq);
+    s.dk = c.take(rk);
+    s.dv = c.take(rk);
+    s.dq_pre = c.take(rq);
+    s.dk_pre = c.take(rk);
+    s.norm_a = c.take(rd);
+    s.d_attn_norm_in = c.take(rd);
+    s.grad_a = c.take(rd);
+    s.grad_b = c.take(rd);
+    s.bytes = c.used > fwd_used ? c.used : fwd_used;
+    return s;
+}
+
+}  // namespace
+
+extern "C" size_t cgpt_block_workspace_bytes(const cgpt_model_config* cfg, size_t batch, size_t seq) {
+    Dims m;
+    if (check_cfg(cfg, batch, seq, &m) != CGPT_OK) return 0;
+    return carve(nullptr, m).bytes;
+}
+
+extern "C" int cgpt_block_forward(void* out, const void* in, const cgpt_block_params* w, const cgpt_block_saved* sv,
+                                  void* workspace, const void* cos_table, const void* sin_table,
+                                  const cgpt_model_config* cfg, size_t batch, size_t seq, size_t position_offset,
+                                  cgpt_stream_t stream) {
+    if (!out || !in || !w || !sv || !workspace || !cos_table || !sin_table) return CGPT_ERR_NULL;
+    Dims m;
+    CGPT_TRY(check_cfg(cfg, batch, seq, &m));
+    const BlockScratch ws = carve(workspace, m);
+    const int dt = cfg->dtype;
+    const float eps = cfg->rms_epsilon;
+    // attention branch
+    CGPT_TRY(cgpt_rmsnorm_forward(sv->norm, in, w->attention_norm, m.rows, m.d, eps, dt, stream));
+    CGPT_TRY(cgpt_linear_forward(sv->query_pre_norm, sv->norm, w->q_projection, m.rows, m.d, m.qdim, dt, stream));
+    CGPT_TRY(cgpt_linear_forward(sv->key_pre_norm, sv->norm, w->k_projection, m.rows, m.d, m.kvdim, dt, stream));
+    CGPT_TRY(cgpt_linear_forward(sv->value, sv->norm, w->v_projection, m.rows, m.d, m.kvdim, dt, stream));
+    CGPT_TRY(cgpt_rmsnorm_forward(sv->query, sv->query_pre_norm, w->q_norm, m.rows * m.hq, m.hd, eps, dt, stream));
+    CGPT_TRY(cgpt_rmsnorm_forward(sv->key, sv->key_pre_norm, w->k_norm, m.rows * m.hkv, m.hd, eps, dt, stream));
+    CGPT_TRY(cgpt_rope_forward(sv->query, sv->key, cos_table, sin_table, batch, seq, m.hq, m.hkv, m.hd, cfg->rotary_dim,
+                               position_offset, cfg->max_seq, dt, stream));
+    CGPT_TRY(cgpt_attention_forward(sv->attention_output, sv->attention_logsumexp, sv->query, sv->key, sv->value, batch,
+                                    seq, seq, m.hq, m.hkv, m.hd, 0.0f, 1, position_offset, dt, 0, stream));
+    CGPT_TRY(cgpt_linear_forward(ws.attn_proj, sv->attention_output, w->o_projection, m.rows, m.qdim, m.d, dt, stream));
+    // MLP branch on the same block input (parallel residual)
+    CGPT_TRY(cgpt_rmsnorm_forward(sv->norm, in, w->ffn_norm, m.rows, m.d, eps, dt, stream));
+    CGPT_TRY(cgpt_linear_forward(sv->gate, sv->norm, w->gate_proj, m.rows, m.d, m.inter, dt, stream));
+    CGPT_TRY(cgpt_linear_forward(sv->up, sv->norm, w->up_proj, m.rows, m.d, m.inter, dt, stream));
+    CGPT_TRY(cgpt_swiglu_forward(sv->activated, sv->gate, sv->up, m.rows * m.inter, dt, stream));
+    CGPT_TRY(cgpt_linear_forward(ws.ffn_out, sv->activated, w->down_proj, m.rows, m.inter, m.d, dt, stream));
+    return cgpt_add(out, in, ws.attn_proj, ws.ffn_out, m.rows * m.d, dt, stream);
+}
+
+extern "C" int cgpt_block_backward(void* grad_in, const void* grad_out, const void* in, const cgpt_block_params* w,
+                                   const cgpt_block_params* g, const cgpt_block_saved* sv, void* workspace,
+                                   const void* cos_table, const void* sin_table, const cgpt_model_config* cfg,
+                                   size_t batch, size_t seq, size_t position_offset, cgpt_stream_t stream) {
+    if (!grad_in || !grad_out || !in || !w || !g || !sv || !workspace || !cos_table || !sin_table) return CGPT_ERR_NULL;
+    Dims m;
+    CGPT_TRY(check_cfg(cfg, batch, seq, &m));
+    const BlockScratch ws = carve(workspace, m);
+    const int dt = cfg->dtype;
+    const float eps = cfg->rms_epsilon;
+    // ---- MLP branch (transformer_block.cu:663-675)
+    CGPT_TRY(cgpt_linear_backward(ws.d_act, g->down_proj, nullptr, grad_out, sv->activated, w->down_proj, m.rows, m.inter,
+                                  m.d, 0, 0, 0, dt, stream));
+    CGPT_TRY(cgpt_swiglu_backward(ws.d_gate, ws.d_up, ws.d_act, sv->gate, sv->up, m.rows * m.inter, 0, 0, dt, stream));
+    CGPT_TRY(cgpt_linear_backward(ws.d_ffn_norm_in, g->gate_proj, nullptr, ws.d_gate, sv->norm, w->gate_proj, m.rows, m.d,
+                                  m.inter, 0, 0, 0, dt, stream));
+    CGPT_TRY(cgpt_linear_backward(ws.d_ffn_norm_in, g->up_proj, nullptr, ws.d_up, sv->norm, w->up_proj, m.rows, m.d,
+                                  m.inter, 1, 0, 0, dt, stream));
+    // grad_in = grad_out + d(ffn_norm)  (the reference's D2D copy + add_inplace, :678-681)
+    CGPT_TRY(cgpt_rmsnorm_backward(grad_in, g->ffn_norm, ws.d_ffn_norm_in, in, w->ffn_norm, grad_out, nullptr, m.rows, m.d,
+                                   eps, dt, stream));
+    // ---- attention branch (:682-747)
+    CGPT_TRY(cgpt_linear_backward(ws.d_attn_out, g->o_projection, nullptr, grad_out, sv->attention_output, w->o_projection,
+                                  m.rows, m.qdim, m.d, 0, 0, 0, dt, stream));
+    CGPT_TRY(cgpt_attention_backward(ws.dq, ws.dk, ws.dv, ws.d_attn_out, sv->attention_output, sv->attention_logsumexp,
+                                     sv->query, sv->key, sv->value, batch, seq, seq, m.hq, m.hkv, m.hd, 0.0f, 1,
+                                     position_offset, 0, dt, 0, stream));
+    CGPT_TRY(cgpt_rope_backward(ws.dq, ws.dk, ws.dq, ws.dk, cos_table, sin_table, batch, seq, m.hq, m.hkv, m.hd,
+                                cfg->rotary_dim, position_offset, cfg->max_seq, dt, stream));
+    CGPT_TRY(cgpt_rmsnorm_backward(ws.dq_pre, g->q_norm, ws.dq, sv->query_pre_norm, w->q_norm, nullptr, nullptr,
+                                   m.rows * m.hq, m.hd, eps, dt, stream));
+    CGPT_TRY(cgpt_rmsnorm_backward(ws.dk_pre, g->k_norm, ws.dk, sv->key_pre_norm, w->k_norm, nullptr, nullptr,
+                                   m.rows * m.hkv, m.hd, eps, dt, stream));
+    // the attention-norm output was overwritten by the FFN norm in the forward: recompute it (:725)
+    CGPT_TRY(cgpt_rmsnorm_forward(ws.norm_a, in, w->attention_norm, m.rows, m.d, eps, dt, stream));
+    CGPT_TRY(cgpt_linear_backward(ws.d_attn_norm_in, g->q_projection, nullptr, ws.dq_pre, ws.norm_a, w->q_projection,
+                                  m.rows, m.d, m.qdim, 0, 0, 0, dt, stream));
+    CGPT_TRY(cgpt_linear_backward(ws.d_attn_norm_in, g->k_projection, nullptr, ws.dk_pre, ws.norm_a, w->k_projection,
+                                  m.rows, m.d, m.kvdim, 1, 0, 0, dt, stream));
+    CGPT_TRY(cgpt_linear_backward(ws.d_attn_norm_in, g->v_projection, nullptr, ws.dv, ws.norm_a, w->v_projection, m.rows,
+                                  m.d, m.kvdim, 1, 0, 0, dt, stream));
+    // grad_in += d(attention_norm)
+    return cgpt_rmsnorm_backward(grad_in, g->attention_norm, ws.d_attn_norm_in, in, w->attention_norm, grad_in, nullptr,
+                                 m.rows, m.d, eps, dt, stream);
+}
+
+extern "C" int cgpt_model_forward(void* logits, const uint32_t* token_ids, const cgpt_model_tensors* w,
+                                  const cgpt_model_saved* sv, void* workspace, const void* cos_table,
+                                  const void* sin_table, const cgpt_model_config* cfg, size_t batch, size_t seq,
+                                  cgpt_stream_t stream) {
+    if (!token_ids || !w || !sv || !workspace || !w->layers || !sv->layers || !sv->layer_inputs) return CGPT_ERR_NULL;
+    Dims m;
+    CGPT_TRY(check_cfg(cfg, batch, seq, &m));
+    if (cfg->layers == 0 || cfg->vocab == 0) return CGPT_ERR_SHAPE;
+    const int dt = cfg->dtype;
+    CGPT_TRY(cgpt_embedding_forward(sv->layer_inputs[0], token_ids, w->token_embedding, m.rows, cfg->vocab, m.d, dt, stream));
+    for (std::size_t l = 0; l < cfg->layers; ++l) {
+        void* out = l + 1 < cfg->layers ? sv->layer_inputs[l + 1] : sv->hidden;
+        CGPT_TRY(cgpt_block_forward(out, sv->layer_inputs[l], &w->layers[l], &sv->layers[l], workspace, cos_table,
+                                    sin_table, cfg, batch, seq, 0, stream));
+    }
+    CGPT_TRY(cgpt_rmsnorm_forward(sv->normalized, sv->hidden, w->final_norm, m.rows, m.d, cfg->rms_epsilon, dt, stream));
+    if (logits != nullptr)
+        CGPT_TRY(cgpt_linear_forward(logits, sv->normalized, w->lm_head, m.rows, m.d, cfg->vocab, dt, stream));
+    return CGPT_OK;
+}
+
+extern "C" int cgpt_model_backward(const void* grad_logits, void* grad_normalized, const uint32_t* token_ids,
+                                   const cgpt_model_tensors* w, const cgpt_model_tensors* g, const cgpt_model_saved* sv,
+                                   void* workspace, const void* cos_table, const void* sin_table,
+                                   const cgpt_model_config* cfg, size_t batch, size_t seq, cgpt_stream_t stream) {
+    if (!grad_normalized || !token_ids || !w || !g || !sv || !workspace || !w->layers || !g->layers || !sv->layers ||
+        !sv->layer_inputs)
+        return CGPT_ERR_NULL;
+    Dims m;
+    CGPT_TRY(check_cfg(cfg, batch, seq, &m));
+    const BlockScratch ws = carve(workspace, m);
+    const int dt = cfg->dtype;
+    if (grad_logits != nullptr) {  // transformer_model.cu:358-361
+        CGPT_TRY(cgpt_linear_backward(grad_normalized, g->lm_head, nullptr, grad_logits, sv->normalized, w->lm_head, m.rows,
+                                      m.d, cfg->vocab, 0, 0, 0, dt, stream));
+    }
+    void* current = ws.grad_a;
+    void* previous = ws.grad_b;
+    CGPT_TRY(cgpt_rmsnorm_backward(current, g->final_norm, grad_normalized, sv->hidden, w->final_norm, nullptr, nullptr,
+                                   m.rows, m.d, cfg->rms_epsilon, dt, stream));
+    for (std::size_t l = cfg->layers; l-- > 0;) {
+        CGPT_TRY(cgpt_block_backward(previous, current, sv->layer_inputs[l], &w->layers[l], &g->layers[l], &sv->layers[l],
+                                     workspace, cos_table, sin_table, cfg, batch, seq, 0, stream));
+        void* t = current;
+        current = previous;
+        previous = t;
+    }
+    // transformer_model.cu:375-380: tied embeddings add the lookup gradient into the LM-head gradient
+    const bool tied = cfg->tied_embeddings != 0;
+    return cgpt_embedding_backward(tied ? g->lm_head : g->token_embedding, current, token_ids, m.rows, cfg->vocab, m.d, 1,
+                                   tied ? 1 : 0, dt, stream);
+}

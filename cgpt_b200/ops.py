@@ -110,6 +110,81 @@ def gemm(c, a, b, m, n, k, a_layout=0, b_layout=0, accumulate=False, force_simt=
                         int(force_simt), stream_ptr(stream)), "gemm")
 
 
+# ------------------------------------------------------------------------------------------- Attention
+@dataclass
+class FlashAttentionOptions:
+    """include/ops/attention.h:8-32 (key_tile_size, block_size and use_tensor_cores are accepted and
+    ignored by the backward, as in the reference)."""
+    num_query_heads: int = 0
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    attention_scale: float = 0.0
+    causal: bool = True
+    query_position_offset: int = 0
+    key_tile_size: int = 16
+    block_size: int = 128
+    use_tensor_cores: bool = True
+
+
+def _attn_check(name, q, k, v, o: FlashAttentionOptions, *same_as_q, same_as_k=()):
+    _same_cuda_dtype(name, q, k, v, *same_as_q, *same_as_k)
+    _require(q.dim() == 4 and k.dim() == 4 and v.shape == k.shape and all(t.shape == q.shape for t in same_as_q)
+             and all(t.shape == k.shape for t in same_as_k), f"{name}: invalid gradient or operand shape")
+    _require(o.num_query_heads > 0 and o.num_kv_heads > 0 and o.head_dim > 0
+             and o.num_query_heads % o.num_kv_heads == 0 and q.shape[2] == o.num_query_heads
+             and k.shape[2] == o.num_kv_heads and q.shape[3] == o.head_dim and k.shape[3] == o.head_dim
+             and q.shape[0] == k.shape[0], f"{name}: invalid attention configuration")
+    _require(o.attention_scale >= 0 and o.attention_scale == o.attention_scale
+             and not (o.causal and o.query_position_offset + q.shape[1] > k.shape[1]),
+             f"{name}: invalid scale or causal range")
+
+
+def flash_gqa_attention_forward_with_lse(output, logsumexp, query, key, value, stream=None,
+                                         options: FlashAttentionOptions | None = None, force_generic=False):
+    """flash_gqa_attention_forward_with_lse (include/ops/attention.h:60-81)."""
+    o = options or FlashAttentionOptions()
+    _attn_check("flash_gqa_attention_forward", query, key, value, o, output)
+    _require(logsumexp is None or (logsumexp.dtype == torch.float32 and logsumexp.is_cuda
+                                   and tuple(logsumexp.shape) == tuple(query.shape[:3])),
+             "flash_gqa_attention_forward: logsumexp must be F32 [batch, seq, heads]")
+    b, sq, hq, d = query.shape
+    check(lib.cgpt_attention_forward(ptr(output), ptr(logsumexp), ptr(query), ptr(key), ptr(value), b, sq, key.shape[1],
+                                     hq, key.shape[2], d, float(o.attention_scale), int(o.causal),
+                                     o.query_position_offset, dtype_code(query), int(force_generic),
+                                     stream_ptr(stream)), "flash_gqa_attention_forward_with_lse")
+
+
+def flash_gqa_attention_backward_with_lse(grad_query, grad_key, grad_value, grad_output, output, logsumexp, query,
+                                          key, value, stream=None, options: FlashAttentionOptions | None = None,
+                                          accumulate_grads=False, force_generic=False):
+    """flash_gqa_attention_backward_with_lse (include/ops/backward/attention_backward.h:57-70)."""
+    o = options or FlashAttentionOptions()
+    _attn_check("flash_gqa_attention_backward", query, key, value, o, grad_query, grad_output, output,
+                same_as_k=(grad_key, grad_value))
+    _require(logsumexp.dtype == torch.float32 and tuple(logsumexp.shape) == tuple(query.shape[:3]),
+             "flash_gqa_attention_backward: logsumexp must be F32 [batch, seq, heads]")
+    b, sq, hq, d = query.shape
+    check(lib.cgpt_attention_backward(ptr(grad_query), ptr(grad_key), ptr(grad_value), ptr(grad_output), ptr(output),
+                                      ptr(logsumexp), ptr(query), ptr(key), ptr(value), b, sq, key.shape[1], hq,
+                                      key.shape[2], d, float(o.attention_scale), int(o.causal),
+                                      o.query_position_offset, int(accumulate_grads), dtype_code(query),
+                                      int(force_generic), stream_ptr(stream)), "flash_gqa_attention_backward_with_lse")
+
+
+def flash_gqa_attention_backward(grad_query, grad_key, grad_value, grad_output, query, key, value, stream=None,
+                                 options: FlashAttentionOptions | None = None, accumulate_grads=False):
+    """flash_gqa_attention_backward without saved statistics (attention_backward.h:24-35)."""
+    o = options or FlashAttentionOptions()
+    _attn_check("flash_gqa_attention_backward", query, key, value, o, grad_query, grad_output,
+                same_as_k=(grad_key, grad_value))
+    b, sq, hq, d = query.shape
+    check(lib.cgpt_attention_backward(ptr(grad_query), ptr(grad_key), ptr(grad_value), ptr(grad_output), None, None,
+                                      ptr(query), ptr(key), ptr(value), b, sq, key.shape[1], hq, key.shape[2], d,
+                                      float(o.attention_scale), int(o.causal), o.query_position_offset,
+                                      int(accumulate_grads), dtype_code(query), 1, stream_ptr(stream)),
+          "flash_gqa_attention_backward")
+
+
 # --------------------------------------------------------------------------------------------- RMSNorm
 def rmsnorm_forward(output, input, weight, epsilon, stream=None):
     """rmsnorm_forward(Tensor& output, const Tensor& input, const Tensor& weight, float eps, stream)."""

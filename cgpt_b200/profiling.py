@@ -1,0 +1,42 @@
+"""Live measurement helpers used by bench.py (CUDA events recorded by the library around its own launches)."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ._lib import check, lib
+
+
+def model_flops_per_token(options) -> float:
+    """Model FLOPs per token of one training step: 6 x matmul weights (forward + two backward products, LM head
+    counted once per use, embedding lookup 0) + causal attention forward (4*S*d/2) and backward (2.5x forward)."""
+    b = options.block_options
+    qd, kvd = b.num_query_heads * b.head_dim, b.num_kv_heads * b.head_dim
+    per_layer = b.hidden_size * (qd + 2 * kvd) + qd * b.hidden_size + 3 * b.hidden_size * b.intermediate_size
+    n_mm = options.num_layers * per_layer + options.vocabulary_size * b.hidden_size
+    return 6.0 * n_mm
+
+
+def attention_flops_per_token(options, seq: int) -> float:
+    b = options.block_options
+    fwd = 4.0 * seq * b.num_query_heads * b.head_dim / 2.0          # QK^T and PV, causal half
+    return options.num_layers * (fwd + 2.5 * fwd)
+
+
+def time_gemms(train_step, steps: int = 2) -> dict:
+    """Runs `steps` eager (non-graph) model steps with event pairs around every tensor-core GEMM launch and returns
+    the per-step totals: ms inside the kernel, algorithmic TFLOP/s, launches, and the model FLOPs of a step."""
+    ts = train_step
+    check(lib.cgpt_b200_gemm_timing(1), "gemm_timing")
+    with torch.cuda.stream(ts.stream):
+        for _ in range(steps):
+            ts.enqueue_model_step()
+    ts.stream.synchronize()
+    ms, fl, n = C.c_double(0), C.c_double(0), C.c_uint64(0)
+    check(lib.cgpt_b200_gemm_timing_read(C.byref(ms), C.byref(fl), C.byref(n)), "gemm_timing_read")
+    check(lib.cgpt_b200_gemm_timing(0), "gemm_timing")
+    tokens = ts.batch * ts.seq
+    model = (model_flops_per_token(ts.options) + attention_flops_per_token(ts.options, ts.seq)) * tokens
+    return {"ms": ms.value / steps, "tflops": fl.value / ms.value / 1e9 if ms.value > 0 else 0.0,
+            "launches": int(n.value) // steps, "gemm_flops": fl.value / steps, "model_flops": model}

@@ -1,0 +1,104 @@
+"""One training step (forward + cut-cross-entropy loss + backward + AdamW), optionally data-parallel.
+
+Follows the reference trainer's step (train/train.cpp:427-457, 532-556): fp16 weights and activations,
+fp32 master weights, static loss scale, forward+loss+backward captured once into a CUDA graph and
+replayed, AdamW launched after it with the step's learning rate. Differences: the loss layer is the
+cut-cross-entropy op (no [tokens, vocab] logits), and with more than one rank the gradients are
+averaged with bucketed NCCL all-reduces between the backward and the optimizer.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import model as M
+from . import optim as O
+
+
+class TrainStep:
+    def __init__(self, options: M.TransformerModelOptions, batch: int, seq: int, *, dtype=torch.float16, seed: int = 0,
+                 loss_scale: float = 1024.0, adamw: O.AdamWOptions | None = None, process_group=None,
+                 bucket_bytes: int = 48 << 20, use_graph: bool = True, cce_chunk_rows: int = 0, device="cuda"):
+        self.options, self.batch, self.seq, self.dtype = options, batch, seq, dtype
+        self.rows = batch * seq
+        self.pg = process_group
+        self.world = process_group.size() if process_group is not None else 1
+        self.loss_scale = loss_scale
+        self.adamw_options = adamw or O.AdamWOptions(3e-4, 0.9, 0.95, 1e-8, 0.1, loss_scale, 1.0)
+        self.adamw_options.loss_scale = loss_scale
+        self.cce_chunk_rows = cce_chunk_rows
+        b = options.block_options
+        self.storage = M.ModelStorage(options, dtype, seed, device=device)
+        self.workspace = M.TransformerModelWorkspace(options, batch, seq, dtype, device)
+        self.backward_workspace = M.TransformerModelBackwardWorkspace(options, batch, seq, dtype, device, max_seq=seq)
+        self.cos, self.sin = M.rotary_cache(seq, b.rotary_dim or b.head_dim, dtype, device)
+        self.token_ids = torch.zeros(self.rows, dtype=torch.int32, device=device)
+        self.targets = torch.zeros(self.rows, dtype=torch.int32, device=device)
+        self.loss = torch.zeros(1, dtype=torch.float32, device=device)
+        pairs = self.storage.parameters_and_gradients()
+        self.states = [O.AdamWState.for_parameter(p) for p, _ in pairs]
+        self.entries = [O.AdamWBatchEntry(p, g, s) for (p, g), s in zip(pairs, self.states)]
+        self.adamw_workspace = O.AdamWWorkspace()
+        self.stream = torch.cuda.Stream(device=device)
+        self.graph = None
+        self.use_graph = use_graph
+        self._buckets = self._make_buckets(bucket_bytes)
+        self._keep = None
+
+    # ------------------------------------------------------------------------------------------ pieces
+    def _make_buckets(self, bucket_bytes: int):
+        """Contiguous slices of the flat gradient buffer of about bucket_bytes each, in backward order."""
+        flat = self.storage.flat_gradients
+        per = max(1, bucket_bytes // flat.element_size())
+        return [flat[i:i + per] for i in range(0, flat.numel(), per)]
+
+    def upload_batch(self, host_ids: torch.Tensor, host_targets: torch.Tensor) -> None:
+        """Host (pinned) -> device copy of the step's token ids and targets on the step's stream."""
+        with torch.cuda.stream(self.stream):
+            self.token_ids.copy_(host_ids.view(-1), non_blocking=True)
+            self.targets.copy_(host_targets.view(-1), non_blocking=True)
+
+    def enqueue_model_step(self) -> None:
+        """forward -> loss (+ LM-head gradients) -> backward on the current stream (capturable)."""
+        st, ws, bw, o = self.storage, self.workspace, self.backward_workspace, self.options
+        k1 = M.transformer_model_forward(None, self.token_ids, self.batch, self.seq, st, ws, self.cos, self.sin, None,
+                                         None, o, scratch=bw)
+        M.cut_cross_entropy_forward_backward(self.loss, bw.grad_normalized, st.g_lm_head, ws.normalized, st.lm_head,
+                                             self.targets, self.rows, None, self.loss_scale / self.world,
+                                             chunk_rows=self.cce_chunk_rows)
+        k2 = M.transformer_model_backward(None, self.token_ids, self.batch, self.seq, st, ws, bw, self.cos, self.sin,
+                                          None, None, o)
+        self._keep = (k1, k2)
+
+    def _allreduce_gradients(self) -> None:
+        if self.world == 1:
+            return
+        import torch.distributed as dist
+        for bucket in self._buckets:
+            dist.all_reduce(bucket, op=dist.ReduceOp.SUM, group=self.pg)
+
+    def step(self, learning_rate: float | None = None) -> None:
+        """One optimizer step on the batch currently in token_ids/targets. Asynchronous."""
+        if learning_rate is not None:
+            self.adamw_options.learning_rate = learning_rate
+        with torch.cuda.stream(self.stream):
+            if self.use_graph:
+                if self.graph is None:
+                    self.enqueue_model_step()          # eager warm-up sizes the library's scratch arena
+                    self.stream.synchronize()
+                    self.graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(self.graph, stream=self.stream):
+                        self.enqueue_model_step()
+                self.graph.replay()
+            else:
+                self.enqueue_model_step()
+            self._allreduce_gradients()
+            O.adamw_step_many_async(self.entries, self.adamw_options, self.adamw_workspace)
+
+    def read_loss(self) -> float:
+        """Device -> host read of the last step's loss (synchronises the step's stream)."""
+        self.stream.synchronize()
+        return float(self.loss.item())
+
+    def check(self) -> bool:
+        with torch.cuda.stream(self.stream):
+            return O.adamw_check(self.adamw_workspace)

@@ -55,6 +55,12 @@ uint64_t cgpt_b200_launch_count(void);
  * those kernels (on an mbarrier fed by TMA or by tcgen05.commit) is bounded; a kernel whose wait ran out
  * sets the word to non-zero and returns. Synchronises the device. */
 int cgpt_b200_device_status(unsigned int* status_out, int clear);
+/* Measurement aid for benchmarks: with enable != 0 the library records a CUDA event pair around every
+ * tensor-core GEMM launch (eager mode only; do not enable while capturing a graph) together with the
+ * launch's algorithmic FLOPs (2*m*n*k); cgpt_b200_gemm_timing_read synchronises the device and returns the
+ * summed kernel milliseconds, FLOPs and launch count since enabling. */
+int cgpt_b200_gemm_timing(int enable);
+int cgpt_b200_gemm_timing_read(double* total_ms, double* total_flops, uint64_t* launches);
 /* Pre-sizes the per-device scratch arena so that later ops (and CUDA graphs that captured them) never
  * see it move. Call outside stream capture. */
 int cgpt_b200_reserve_scratch(size_t bytes);
@@ -81,6 +87,32 @@ int cgpt_linear_forward(void* y, const void* x, const void* w, size_t rows, size
 int cgpt_linear_backward(void* dx, void* dw, void* db, const void* dy, const void* x, const void* w,
                          size_t rows, size_t in_features, size_t out_features, int accumulate_input,
                          int accumulate_weight, int accumulate_bias, int dtype, cgpt_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Grouped-query softmax attention, forward with saved log-sum-exp and backward.
+ * Replaces flash_gqa_attention_forward_with_lse (reference include/ops/attention.h:60-81,
+ * src/ops/attention.cu), flash_gqa_attention_backward_with_lse and flash_gqa_attention_backward
+ * (reference include/ops/backward/attention_backward.h:24-35,57-70,
+ * src/ops/backward/attention_backward.cu:1914-2069).
+ * q, out, dout, dq: [batch, sq, hq, head_dim]; k, v, dk, dv: [batch, sk, hkv, head_dim];
+ * lse: fp32 [batch, sq, hq] = log sum exp of the scaled scores (natural log). hq % hkv == 0.
+ * Key k is visible to query q iff !causal or k <= offset + q (causal requires offset + sq <= sk).
+ * scale <= 0 selects 1/sqrt(head_dim).
+ *   P = exp(scale QK^T - lse); delta = rowsum(dout*out); dS = P (dout V^T - delta);
+ *   dq = scale dS K; dk = scale dS^T Q; dv = P^T dout.   accumulate != 0 adds into dq, dk, dv.
+ * Backward with out == NULL or lse == NULL recomputes the forward statistics first (the reference's
+ * flash_gqa_attention_backward). 16-bit tensors with head_dim 64 or 128 run on the tensor cores;
+ * everything else (and force_generic != 0) runs a warp-per-row kernel. No atomics: bit-reproducible.
+ * ---------------------------------------------------------------------------------------------- */
+int cgpt_attention_forward(void* out, float* lse, const void* q, const void* k, const void* v,
+                           size_t batch, size_t sq, size_t sk, size_t hq, size_t hkv, size_t head_dim,
+                           float scale, int causal, size_t offset, int dtype, int force_generic,
+                           cgpt_stream_t stream);
+int cgpt_attention_backward(void* dq, void* dk, void* dv, const void* dout, const void* out,
+                            const float* lse, const void* q, const void* k, const void* v, size_t batch,
+                            size_t sq, size_t sk, size_t hq, size_t hkv, size_t head_dim, float scale,
+                            int causal, size_t offset, int accumulate, int dtype, int force_generic,
+                            cgpt_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
  * RMSNorm  y = x * rsqrt(mean(x^2) + eps) * w
@@ -216,6 +248,114 @@ int cgpt_adamw_check(cgpt_adamw_workspace* ws, uint64_t* step_out, int* non_fini
  * Synchronises the stream. For tests and logging. */
 int cgpt_adamw_last_stats(cgpt_adamw_workspace* ws, float* squared_norm, float* clip,
                           cgpt_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Cut cross-entropy: mean CE of X C^T against targets, with dX and dC, without a [rows, vocab] logits
+ * tensor. Replaces cut_cross_entropy_forward_backward (reference include/ops/cut_cross_entropy.h:25-33,
+ * src/ops/cut_cross_entropy.cu:97-221, F32 only there) and, in the training step, the composition
+ * linear_forward -> cross_entropy_forward_backward -> linear_backward that CGPT's trainer runs on
+ * materialised fp16 logits (train/train.cpp:536-544).
+ * x, dx: [rows, hidden]; c (classifier), dc: [vocab, hidden]; targets: uint32 [rows]; loss: fp32 [1].
+ *   loss = mean_rows(log sum exp(x C^T) - (x C^T)[target]);  G = (softmax - onehot) / rows * gradient_scale
+ *   dx = G C;  dc (+)= G^T x.   Rows whose target >= vocab add no loss and no -1 (as cross_entropy).
+ * Rows are processed in chunks of at most chunk_rows (0 = library default): logits of one chunk live in
+ * scratch ([chunk_rows, vocab]), are turned into G in place and feed the two gradient GEMMs.
+ * accumulate_dc != 0 adds into dc instead of overwriting it.
+ * ---------------------------------------------------------------------------------------------- */
+int cgpt_cut_cross_entropy(float* loss, void* dx, void* dc, const void* x, const void* c,
+                           const uint32_t* targets, size_t rows, size_t vocab, size_t hidden,
+                           float gradient_scale, int accumulate_dc, size_t chunk_rows, int dtype,
+                           cgpt_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Transformer block / model forward and backward (host orchestration in C++ inside the library).
+ * Replaces transformer_block_forward / transformer_block_backward (reference
+ * include/core/transformer_block.h:10-242, src/core/transformer_block.cu:405-748) and
+ * transformer_model_forward / transformer_model_backward (reference include/core/transformer_model.h,
+ * src/core/transformer_model.cu:170-381). Block graph (parallel residual, per-head QK-RMSNorm before
+ * RoPE):   out = x + W_o Attn(RoPE(qnorm(W_q n_a)), RoPE(knorm(W_k n_a)), W_v n_a) + W_down SwiGLU(W_gate n_f, W_up n_f)
+ * with n_a = RMSNorm(x; attention_norm), n_f = RMSNorm(x; ffn_norm).
+ * Every struct member is a device pointer to a contiguous tensor in `dtype`
+ * (attention_logsumexp: fp32). The same struct type describes weights and their gradients.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct cgpt_block_params {
+    void* attention_norm; /* [hidden] */
+    void* q_projection;   /* [q_heads*head_dim, hidden] */
+    void* k_projection;   /* [kv_heads*head_dim, hidden] */
+    void* q_norm;         /* [head_dim] */
+    void* k_norm;         /* [head_dim] */
+    void* v_projection;   /* [kv_heads*head_dim, hidden] */
+    void* o_projection;   /* [hidden, q_heads*head_dim] */
+    void* ffn_norm;       /* [hidden] */
+    void* gate_proj;      /* [intermediate, hidden] */
+    void* up_proj;        /* [intermediate, hidden] */
+    void* down_proj;      /* [hidden, intermediate] */
+} cgpt_block_params;
+
+/* Activations saved by the forward for the backward (TransformerBlockWorkspace in the reference,
+ * include/core/transformer_block.h:65-93), rows = batch*seq. */
+typedef struct cgpt_block_saved {
+    void* norm;                  /* [rows, hidden] output of the FFN RMSNorm */
+    void* query;                 /* [batch, seq, q_heads, head_dim] after QK-norm and RoPE */
+    void* key;                   /* [batch, seq, kv_heads, head_dim] after QK-norm and RoPE */
+    void* value;                 /* [batch, seq, kv_heads, head_dim] */
+    void* query_pre_norm;        /* [batch, seq, q_heads, head_dim] */
+    void* key_pre_norm;          /* [batch, seq, kv_heads, head_dim] */
+    void* attention_output;      /* [batch, seq, q_heads, head_dim] */
+    float* attention_logsumexp;  /* [batch, seq, q_heads] fp32 */
+    void* gate;                  /* [rows, intermediate] */
+    void* up;                    /* [rows, intermediate] */
+    void* activated;             /* [rows, intermediate] */
+} cgpt_block_saved;
+
+typedef struct cgpt_model_config {
+    uint64_t vocab, layers, hidden, intermediate, q_heads, kv_heads, head_dim, rotary_dim;
+    uint64_t max_seq;        /* rows of the cos/sin tables */
+    float rms_epsilon;
+    int32_t dtype;           /* CGPT_DTYPE_* of every weight / activation */
+    int32_t tied_embeddings; /* != 0: lm_head and token_embedding share weight and gradient */
+    int32_t reserved;
+} cgpt_model_config;
+
+/* Bytes of scratch the block / model calls need for (batch, seq); pass a buffer of at least this size. */
+size_t cgpt_block_workspace_bytes(const cgpt_model_config* cfg, size_t batch, size_t seq);
+
+int cgpt_block_forward(void* out, const void* in, const cgpt_block_params* weights, const cgpt_block_saved* saved,
+                       void* workspace, const void* cos_table, const void* sin_table, const cgpt_model_config* cfg,
+                       size_t batch, size_t seq, size_t position_offset, cgpt_stream_t stream);
+int cgpt_block_backward(void* grad_in, const void* grad_out, const void* in, const cgpt_block_params* weights,
+                        const cgpt_block_params* grads, const cgpt_block_saved* saved, void* workspace,
+                        const void* cos_table, const void* sin_table, const cgpt_model_config* cfg, size_t batch,
+                        size_t seq, size_t position_offset, cgpt_stream_t stream);
+
+typedef struct cgpt_model_tensors {
+    void* token_embedding;          /* [vocab, hidden] */
+    const cgpt_block_params* layers; /* host array of `layers` entries */
+    void* final_norm;               /* [hidden] */
+    void* lm_head;                  /* [vocab, hidden] (== token_embedding when tied) */
+} cgpt_model_tensors;
+
+typedef struct cgpt_model_saved {
+    const cgpt_block_saved* layers; /* host array of `layers` entries */
+    void* const* layer_inputs;      /* host array of `layers` device pointers, each [rows, hidden] */
+    void* hidden;                   /* [rows, hidden] output of the last block */
+    void* normalized;               /* [rows, hidden] output of the final RMSNorm */
+} cgpt_model_saved;
+
+/* Forward: embedding -> blocks -> final RMSNorm (saved->normalized); with logits != NULL also the LM head
+ * into logits [rows, vocab] (the reference's transformer_model_forward). */
+int cgpt_model_forward(void* logits, const uint32_t* token_ids, const cgpt_model_tensors* weights,
+                       const cgpt_model_saved* saved, void* workspace, const void* cos_table, const void* sin_table,
+                       const cgpt_model_config* cfg, size_t batch, size_t seq, cgpt_stream_t stream);
+/* Backward. Either grad_logits [rows, vocab] is given (the reference's transformer_model_backward: LM-head
+ * backward first, grads->lm_head overwritten), or grad_logits == NULL and grad_normalized [rows, hidden]
+ * already holds the gradient of the final-norm output with grads->lm_head already written (the cut
+ * cross-entropy path). grad_normalized is scratch of [rows, hidden] in the first case. With tied embeddings
+ * the lookup gradient is added into grads->lm_head, else grads->token_embedding is overwritten. */
+int cgpt_model_backward(const void* grad_logits, void* grad_normalized, const uint32_t* token_ids,
+                        const cgpt_model_tensors* weights, const cgpt_model_tensors* grads,
+                        const cgpt_model_saved* saved, void* workspace, const void* cos_table, const void* sin_table,
+                        const cgpt_model_config* cfg, size_t batch, size_t seq, cgpt_stream_t stream);
 
 #ifdef __cplusplus
 } /* extern "C" */

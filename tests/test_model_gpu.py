@@ -1,0 +1,210 @@
+"""GPU parity of cut cross-entropy, transformer block and whole-model forward/backward (through the C ABI)
+against the numpy oracle, on the reference's tiny CPU-runnable configuration (2 layers, d 256, 4 Q / 2 KV
+heads, head_dim 64, SwiGLU 688, vocab 32000, batch 2 x seq 128) and smaller variants.
+
+Gradients are compared with the pure-fp32 oracle chain evaluated on the activations the GPU saved
+(round_intermediates=False), bar 1e-2 norm-scaled; the loss after 50 identical steps is compared with the
+oracle's fp16-storage emulation of the same training loop, bar 1e-3 absolute.
+"""
+import numpy as np
+import pytest
+import torch
+
+import known_answers as KA
+from gpu_util import assert_close, dev, host, ids_dev
+from oracle import cgpt_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def M():
+    from cgpt_b200 import model as m
+    return m
+
+
+def np_weights(storage):
+    layers = [{n: host(t) for n, t in layer.items()} for layer in storage.layers]
+    return {"token_embedding": host(storage.token_embedding), "layers": layers, "final_norm": host(storage.final_norm),
+            "lm_head": host(storage.lm_head)}
+
+
+def cfg_dict(o, batch, seq):
+    b = o.block_options
+    return dict(batch=batch, seq=seq, hidden=b.hidden_size, intermediate=b.intermediate_size, q_heads=b.num_query_heads,
+                kv_heads=b.num_kv_heads, head_dim=b.head_dim, rotary_dim=b.rotary_dim, eps=b.rms_epsilon)
+
+
+# ----------------------------------------------------------------------------------------------- CCE
+def test_cce_known_answer_f32(M):
+    c = KA.CCE
+    x, cl = dev(c["input"]), dev(c["classifier"])
+    loss = torch.zeros(1, device="cuda"); dx, dc = torch.empty_like(x), torch.empty_like(cl)
+    M.cut_cross_entropy_forward_backward(loss, dx, dc, x, cl, ids_dev(c["targets"]), 2)
+    el, edx, edc = O.cut_cross_entropy(c["input"], c["classifier"], c["targets"])
+    np.testing.assert_allclose(host(loss), [c["loss"]], atol=2e-5)
+    np.testing.assert_allclose(host(dx)[0], c["grad_input"][0], atol=2e-5)
+    np.testing.assert_allclose(host(dc)[:2], c["grad_classifier"][:2], atol=2e-3)
+    np.testing.assert_allclose(host(dx), edx, atol=2e-6); np.testing.assert_allclose(host(dc), edc, atol=2e-6)
+
+
+@pytest.mark.parametrize("rows,vocab,hidden,chunk,dt", [(256, 32000, 256, 0, "f16"), (1000, 4096, 768, 384, "f16"), (300, 1000, 64, 128, "bf16"),
+                                                        (64, 100, 24, 0, "f32")])
+def test_cce_against_oracle(M, rows, vocab, hidden, chunk, dt):
+    r = np.random.default_rng(rows)
+    x, cl = dev(r.standard_normal((rows, hidden)), dt), dev(0.05 * r.standard_normal((vocab, hidden)), dt)
+    t = r.integers(0, vocab, rows); t[5] = vocab + 3
+    loss = torch.zeros(1, device="cuda"); dx, dc = torch.full_like(x, float("nan")), torch.full_like(cl, float("nan"))
+    M.cut_cross_entropy_forward_backward(loss, dx, dc, x, cl, ids_dev(t), rows, None, 1024.0, chunk_rows=chunk)
+    el, edx, edc = O.cut_cross_entropy(host(x), host(cl), t, 1024.0)
+    assert abs(float(loss.item()) - float(el)) <= 1e-3
+    tol = {"f16": 1e-2, "bf16": 5e-2, "f32": 1e-4}[dt]
+    assert_close(host(dx), edx, tol, "dx"); assert_close(host(dc), edc, tol, "dc")
+    dc2 = dc.clone()
+    M.cut_cross_entropy_forward_backward(loss, dx, dc2, x, cl, ids_dev(t), rows, None, 1024.0, accumulate_classifier_gradient=True, chunk_rows=chunk)
+    assert_close(host(dc2), 2 * host(dc), tol, "dc accumulate")
+
+
+# --------------------------------------------------------------------------------------------- block
+@pytest.mark.parametrize("batch,seq,opts", [(2, 128, (256, 688, 4, 2, 64, 64)), (1, 96, (64, 64, 2, 1, 32, 32)), (2, 64, (256, 512, 2, 1, 128, 128))])
+def test_block_forward_backward(M, batch, seq, opts):
+    o = M.TransformerBlockOptions(*opts)
+    rows = batch * seq
+    r = np.random.default_rng(seq)
+    shapes = M.block_param_shapes(o)
+    w = {n: dev((1 + 0.05 * r.standard_normal(s)) if n.endswith("norm") else 0.05 * r.standard_normal(s), "f16") for n, s in shapes.items()}
+    g = {n: torch.full_like(t, float("nan")) for n, t in w.items()}
+    x, dout = dev(r.standard_normal((rows, o.hidden_size)), "f16"), dev(r.standard_normal((rows, o.hidden_size)), "f16")
+    cos, sin = M.rotary_cache(seq, o.rotary_dim)
+    ws = M.TransformerBlockWorkspace(o, batch, seq)
+    cfg = M._config(M.TransformerModelOptions(1, 1, o), torch.float16, seq, False)
+    bw = M.TransformerBlockBackwardWorkspace(cfg, batch, seq)
+    out, gin = torch.full_like(x, float("nan")), torch.full_like(x, float("nan"))
+    M.transformer_block_forward(out, x, w, ws, cos, sin, None, None, o, scratch=bw)
+    wn = {n: host(t) for n, t in w.items()}
+    c = cfg_dict(M.TransformerModelOptions(1, 1, o), batch, seq)
+    eout, esv = O.block_forward(host(x), wn, c, host(cos), host(sin), "f16")
+    assert_close(host(out), eout, 1e-2, "block out")
+    for name in ("query", "key", "value", "attention_output", "gate", "up", "activated", "norm"):
+        assert_close(host(getattr(ws, name)), esv[name], 1.5e-2, name)
+    M.transformer_block_backward(gin, dout, x, w, g, ws, bw, cos, sin, None, None, o)
+    saved = {n: host(getattr(ws, n)) for n in ("norm", "query", "key", "value", "query_pre_norm", "key_pre_norm", "attention_output",
+                                               "attention_logsumexp", "gate", "up", "activated")}
+    egin, eg = O.block_backward(host(dout), host(x), wn, saved, c, host(cos), host(sin), "f16", 0, round_intermediates=False)
+    assert_close(host(gin), egin, 1e-2, "grad_input")
+    for n in shapes:
+        assert_close(host(g[n]), eg[n], 1e-2, f"grad {n}")
+
+
+# --------------------------------------------------------------------------------------------- model
+def _tiny(M, vocab=32000):
+    o = M.preset("tiny")
+    o.vocabulary_size = vocab
+    return o
+
+
+def test_model_forward_backward_tiny(M):
+    """BASELINE config 1: tiny model, batch 2 x seq 128, full backward through the CCE loss."""
+    from cgpt_b200.train import TrainStep
+    o = _tiny(M)
+    batch, seq = 2, 128
+    ts = TrainStep(o, batch, seq, seed=0, use_graph=False)
+    r = np.random.default_rng(1)
+    tokens = r.integers(0, o.vocabulary_size, (batch, seq + 1))
+    ids, targets = tokens[:, :-1].copy(), tokens[:, 1:].copy()
+    ts.token_ids.copy_(ids_dev(ids.reshape(-1))); ts.targets.copy_(ids_dev(targets.reshape(-1)))
+    with torch.cuda.stream(ts.stream):
+        ts.enqueue_model_step()
+    ts.stream.synchronize()
+    w = np_weights(ts.storage)
+    c = cfg_dict(o, batch, seq)
+    cos, sin = host(ts.cos), host(ts.sin)
+    normalized, saved = O.model_forward(ids, w, c, cos, sin, "f16")
+    assert_close(host(ts.workspace.normalized), normalized, 1.5e-2, "normalized")
+    # loss + gradients from the activations the GPU saved (fp32 oracle chain)
+    gpu_saved = {"layer_inputs": [host(t) for t in ts.workspace.layer_inputs], "hidden": host(ts.workspace.hidden),
+                 "layers": [{n: host(getattr(l, n)) for n in ("norm", "query", "key", "value", "query_pre_norm", "key_pre_norm",
+                                                              "attention_output", "attention_logsumexp", "gate", "up", "activated")}
+                            for l in ts.workspace.layers]}
+    el, ed_norm, eg_head = O.cut_cross_entropy(host(ts.workspace.normalized), w["lm_head"], targets.reshape(-1), 1024.0)
+    assert abs(ts.read_loss() - float(el)) <= 1e-3
+    assert abs(float(el) - np.log(o.vocabulary_size)) < 0.2, "random-init loss should sit near ln(vocab)"
+    assert_close(host(ts.backward_workspace.grad_normalized), ed_norm, 1e-2, "grad_normalized")
+    eg = O.model_backward(ed_norm, eg_head, ids, w, gpu_saved, c, cos, sin, "f16", tied=True, round_intermediates=False)
+    assert_close(host(ts.storage.g_token_embedding), eg["token_embedding"], 1e-2, "g_embedding (tied)")
+    assert_close(host(ts.storage.g_final_norm), eg["final_norm"], 1e-2, "g_final_norm")
+    for li in range(o.num_layers):
+        for n, t in ts.storage.g_layers[li].items():
+            assert_close(host(t), eg["layers"][li][n], 1e-2, f"layer {li} {n}")
+
+
+def test_reference_api_with_materialised_logits(M):
+    """transformer_model_forward(logits) + cross_entropy_forward_backward + transformer_model_backward(grad_logits),
+    the composition CGPT's trainer runs, gives the same gradients as the cut-cross-entropy path."""
+    from cgpt_b200 import ops
+    from cgpt_b200.train import TrainStep
+    o = _tiny(M, vocab=2048)
+    batch, seq = 2, 64
+    ts = TrainStep(o, batch, seq, seed=3, use_graph=False)
+    r = np.random.default_rng(2)
+    ids = r.integers(0, 2048, batch * seq); tg = r.integers(0, 2048, batch * seq)
+    ts.token_ids.copy_(ids_dev(ids)); ts.targets.copy_(ids_dev(tg))
+    with torch.cuda.stream(ts.stream):
+        ts.enqueue_model_step()
+    ts.stream.synchronize()
+    g_cce = ts.storage.flat_gradients.clone(); loss_cce = ts.read_loss()
+    logits = torch.empty(batch * seq, 2048, device="cuda", dtype=torch.float16); grad_logits = torch.empty_like(logits)
+    loss = torch.zeros(1, device="cuda")
+    M.transformer_model_forward(logits, ts.token_ids, batch, seq, ts.storage, ts.workspace, ts.cos, ts.sin, None, None, o, scratch=ts.backward_workspace)
+    ops.cross_entropy_forward_backward(loss, grad_logits, logits, ts.targets, batch * seq, None, 1024.0)
+    M.transformer_model_backward(grad_logits, ts.token_ids, batch, seq, ts.storage, ts.workspace, ts.backward_workspace, ts.cos, ts.sin, None, None, o)
+    torch.cuda.synchronize()
+    assert abs(float(loss.item()) - loss_cce) <= 2e-3
+    assert_close(host(ts.storage.flat_gradients), host(g_cce), 1e-2, "gradients: materialised logits vs CCE")
+
+
+def test_loss_after_50_identical_steps(M):
+    """Parity bar: loss after 50 identical steps within 1e-3 absolute of the oracle's emulation of the same
+    loop (fp16 storage roundings, fp32 master weights, AdamW lr 3e-4, betas .9/.95, wd .1, loss scale 1024)."""
+    from cgpt_b200.train import TrainStep
+    from cgpt_b200 import optim
+    o = M.TransformerModelOptions(512, 2, M.TransformerBlockOptions(64, 176, 2, 1, 32, 32))
+    batch, seq, steps = 2, 32, 50
+    adam = optim.AdamWOptions(3e-4, 0.9, 0.95, 1e-8, 0.1, 1024.0, float("inf"))
+    ts = TrainStep(o, batch, seq, seed=5, adamw=adam, use_graph=True)
+    r = np.random.default_rng(9)
+    tokens = r.integers(0, 512, (batch, seq + 1))
+    ids, targets = tokens[:, :-1].copy(), tokens[:, 1:].copy()
+    ts.token_ids.copy_(ids_dev(ids.reshape(-1))); ts.targets.copy_(ids_dev(targets.reshape(-1)))
+    w = np_weights(ts.storage)
+    cos, sin = host(ts.cos), host(ts.sin)
+    c = cfg_dict(o, batch, seq)
+    gpu_losses = []
+    for _ in range(steps):
+        ts.step()
+        gpu_losses.append(ts.read_loss())
+    assert ts.check()
+    # oracle loop
+    names = [("token_embedding", None), ("final_norm", None)] + [(n, li) for li in range(o.num_layers) for n in O.BLOCK_WEIGHTS]
+    get = lambda d, n, li: d[n] if li is None else d["layers"][li][n]
+    masters = [get(w, n, li).astype(np.float32) for n, li in names]
+    ms = [np.zeros_like(m_) for m_ in masters]; vs = [np.zeros_like(m_) for m_ in masters]
+    step = 0
+    cpu_losses = []
+    for _ in range(steps):
+        normalized, saved = O.model_forward(ids, w, c, cos, sin, "f16")
+        loss, d_norm, g_head = O.cut_cross_entropy(normalized, w["lm_head"], targets.reshape(-1), 1024.0)
+        cpu_losses.append(float(loss))
+        grads = O.model_backward(O.rnd(d_norm), O.rnd(g_head), ids, w, saved, c, cos, sin, "f16", tied=True)
+        glist = [get(grads, n, li) for n, li in names]
+        params, masters, ms, vs, step, skipped = O.adamw_step("f16", glist, masters, ms, vs, step, 3e-4, 0.9, 0.95, 1e-8, 0.1, 1024.0)
+        assert not skipped
+        for (n, li), p in zip(names, params):
+            if li is None:
+                w[n] = p
+            else:
+                w["layers"][li][n] = p
+        w["lm_head"] = w["token_embedding"]
+    assert gpu_losses[-1] < gpu_losses[0] - 0.05, "training must reduce the loss"
+    assert abs(gpu_losses[0] - cpu_losses[0]) <= 1e-3
+    assert abs(gpu_losses[-1] - cpu_losses[-1]) <= 1e-3, (gpu_losses[-1], cpu_losses[-1])
