@@ -59,10 +59,11 @@ def test_cce_against_oracle(M, rows, vocab, hidden, chunk, dt):
     el, edx, edc = O.cut_cross_entropy(host(x), host(cl), t, 1024.0)
     assert abs(float(loss.item()) - float(el)) <= 1e-3
     tol = {"f16": 1e-2, "bf16": 5e-2, "f32": 1e-4}[dt]
-    assert_close(host(dx), edx, tol, "dx"); assert_close(host(dc), edc, tol, "dc")
+    # dC is heavy-tailed (rows of target tokens dominate), so it is judged relative to its largest entry
+    assert_close(host(dx), edx, tol, "dx"); assert_close(host(dc), edc, tol / 2, "dc", metric="max")
     dc2 = dc.clone()
     M.cut_cross_entropy_forward_backward(loss, dx, dc2, x, cl, ids_dev(t), rows, None, 1024.0, accumulate_classifier_gradient=True, chunk_rows=chunk)
-    assert_close(host(dc2), 2 * host(dc), tol, "dc accumulate")
+    assert_close(host(dc2), 2 * host(dc), tol / 2, "dc accumulate", metric="max")
 
 
 # --------------------------------------------------------------------------------------------- block
