@@ -26,9 +26,12 @@ def rounded(t):
 
 
 def scaled_err(got, want):
+    """The harness's norm-scaled error: max_i |a_i - b_i| / (|b_i| + rms(b)). An element may be off by `tol` of its
+    own magnitude plus `tol` of the tensor's RMS. A plain max|a-b| / rms(b) would flag correctly rounded outputs of
+    heavy-tailed tensors (one fp16 ulp of a 5-sigma element is several 1e-3 of the RMS)."""
     got = np.asarray(got, np.float64); want = np.asarray(want, np.float64)
     rms = np.sqrt(np.mean(want ** 2))
-    return float(np.max(np.abs(got - want)) / max(rms, 1e-30))
+    return float(np.max(np.abs(got - want) / (np.abs(want) + max(rms, 1e-30))))
 
 
 def max_err(got, want):
