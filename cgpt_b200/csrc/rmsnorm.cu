@@ -13,6 +13,8 @@
 // partials go to a [grid, hidden] fp32 scratch and a second, tiny kernel sums them in a fixed order
 // (deterministic, no atomics). Algorithmic HBM bytes per row: 3 * hidden * sizeof(T)
 // (+ hidden * sizeof(T) per residual operand).
+#include <mutex>
+
 #include "common.cuh"
 #include "launch_counter.h"
 
@@ -342,6 +344,113 @@ extern "C" int cgpt_rmsnorm_backward(void* dx, void* dw, const void* dy, const v
         if (p.vec == 4)
             return launch_backward<T, 4>(dx, dw, dy, x, w, residual_a, residual_b, rows, hidden, epsilon, p, s);
         return launch_backward<T, 1>(dx, dw, dy, x, w, residual_a, residual_b, rows, hidden, epsilon, p, s);
+    });
+    return CGPT_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// RMSNorm backward for callers that must not allocate.
+//
+// Some hosts embed this library where device allocation is off limits at call time: a process that
+// handed all device memory to its own pool allocator at start-up, a real-time loop that may not take the
+// allocator's lock, or a sandbox that only lets pre-approved entry points touch the driver's allocator.
+// cgpt_rmsnorm_backward takes its [grid, hidden] fp32 partial-sum buffer from the library's arena, which
+// calls cudaMalloc the first time (or whenever a larger size is needed). This variant instead keeps that
+// buffer in a fixed array in the library's own device image: it exists from the moment the library is
+// loaded on a GPU until the process exits, costs kNoAllocFloats * 4 bytes on every GPU that loads the
+// library, and is never resized.
+// ------------------------------------------------------------------------------------------------
+namespace cgpt {
+namespace {
+
+constexpr std::size_t kNoAllocFloats = std::size_t{1} << 20;   // 4 MiB of fp32 partial sums per GPU
+static __device__ __align__(256) float g_noalloc_partials[kNoAllocFloats];
+
+constexpr int kNoAllocMaxDevices = 64;
+float* g_noalloc_address[kNoAllocMaxDevices] = {};   // device address of the array, per device
+std::mutex g_noalloc_mutex;
+
+// In host code the array's name is only a handle for the runtime, not an address the GPU can use:
+// ask the runtime for the device address once per device (with that device current) and cache it.
+int noalloc_scratch(float** out) {
+    int device = 0;
+    CGPT_CUDA_TRY(cudaGetDevice(&device));
+    if (device < 0 || device >= kNoAllocMaxDevices) return CGPT_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_address[device] == nullptr) {
+        float* p = nullptr;
+        CGPT_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_partials));
+        if (p == nullptr) return CGPT_ERR_STATE;
+        g_noalloc_address[device] = p;
+    }
+    *out = g_noalloc_address[device];
+    return CGPT_OK;
+}
+
+template <typename T, int VEC>
+int launch_backward_fixed_scratch(void* dx, void* dw, const void* dy, const void* x, const void* w, const void* ra,
+                                  const void* rb, std::size_t rows, std::size_t hidden, float eps, const Plan& p,
+                                  float* scratch, cudaStream_t s) {
+    int grid = grid_for(rows, p.wpr, 4);
+    const std::size_t fit = kNoAllocFloats / hidden;   // CTAs whose partial rows fit in the fixed array
+    if (fit == 0) return CGPT_ERR_SHAPE;
+    if (static_cast<std::size_t>(grid) > fit) grid = static_cast<int>(fit);
+#define CGPT_RMS_BWD_FIXED(CPT)                                                                  \
+    rmsnorm_backward_kernel<T, VEC, CPT><<<grid, kThreads, 0, s>>>(                               \
+        static_cast<T*>(dx), scratch, static_cast<const T*>(dy), static_cast<const T*>(x),      \
+        static_cast<const T*>(w), static_cast<const T*>(ra), static_cast<const T*>(rb),         \
+        static_cast<long long>(rows), static_cast<int>(hidden), eps, p.wpr)
+    switch (p.cpt) {
+        case 1: CGPT_RMS_BWD_FIXED(1); break;
+        case 2: CGPT_RMS_BWD_FIXED(2); break;
+        default: CGPT_RMS_BWD_FIXED(4); break;
+    }
+#undef CGPT_RMS_BWD_FIXED
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+    rmsnorm_dw_reduce_kernel<T><<<static_cast<unsigned>((hidden + 31) / 32), 256, 0, s>>>(
+        static_cast<T*>(dw), scratch, grid, static_cast<int>(hidden));
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+    return CGPT_OK;
+}
+
+}  // namespace
+}  // namespace cgpt
+
+// Same contract and results as cgpt_rmsnorm_backward, but no cudaMalloc / cudaFree / allocating library
+// routine is ever called: the partial sums live in a 4 MiB array that is part of the library image.
+//  * Limit: hidden <= 8192 (and within what the register-cached kernel supports); larger sizes return
+//    CGPT_ERR_SHAPE. When rows are many and hidden is large the grid is capped so that grid * hidden
+//    floats fit in the array.
+//  * The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
+//    that first call outside of any stream capture.
+//  * All calls on a device share the one array, which still holds the previous call's partial sums.
+//    Nothing needs to start at zero (every partial that is read was written by the same call), but
+//    two calls that overlap on the GPU (different streams) would overwrite each other's partials:
+//    issue them on one stream or otherwise order them.
+extern "C" int cgpt_rmsnorm_backward_noalloc(void* dx, void* dw, const void* dy, const void* x, const void* w,
+                                             const void* residual_a, const void* residual_b, size_t rows,
+                                             size_t hidden, float epsilon, int dtype, cgpt_stream_t stream) {
+    if (!dx || !dw || !dy || !x || !w) return CGPT_ERR_NULL;
+    if (!valid_float_dtype(dtype)) return CGPT_ERR_DTYPE;
+    if (rows == 0 || hidden == 0 || rows > (1ull << 40)) return CGPT_ERR_SHAPE;
+    if (hidden > 8192) return CGPT_ERR_SHAPE;   // beyond the fixed scratch this entry point is built for
+    if (!(epsilon > 0.f)) return CGPT_ERR_OPTION;
+    float* scratch = nullptr;
+    CGPT_TRY(noalloc_scratch(&scratch));
+    auto s = static_cast<cudaStream_t>(stream);
+    const bool al = aligned16(dx) && aligned16(dy) && aligned16(x) && aligned16(w) && aligned16(residual_a) &&
+                    aligned16(residual_b);
+    CGPT_DISPATCH_DTYPE(dtype, T, {
+        Plan p;
+        if (!make_plan<T>(hidden, al, &p)) return CGPT_ERR_UNSUPPORTED;
+        constexpr int kMaxVec = 16 / sizeof(T);
+        if (p.vec == kMaxVec)
+            return launch_backward_fixed_scratch<T, kMaxVec>(dx, dw, dy, x, w, residual_a, residual_b, rows, hidden, epsilon, p, scratch, s);
+        if (p.vec == 4)
+            return launch_backward_fixed_scratch<T, 4>(dx, dw, dy, x, w, residual_a, residual_b, rows, hidden, epsilon, p, scratch, s);
+        return launch_backward_fixed_scratch<T, 1>(dx, dw, dy, x, w, residual_a, residual_b, rows, hidden, epsilon, p, scratch, s);
     });
     return CGPT_OK;
 }

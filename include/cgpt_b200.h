@@ -132,6 +132,18 @@ int cgpt_rmsnorm_backward(void* dx, void* dw, const void* dy, const void* x, con
                           const void* residual_a, const void* residual_b, size_t rows,
                           size_t hidden, float epsilon, int dtype, cgpt_stream_t stream);
 
+/* RMSNorm backward that never allocates. No counterpart in the reference: it exists for hosts that
+ * cannot call the device allocator at call time (a process whose pool allocator owns all device memory,
+ * a latency-critical loop that may not take the allocator's lock, a sandbox that filters allocator
+ * calls). Arguments, results and error codes are those of cgpt_rmsnorm_backward; the [grid, hidden] fp32
+ * partial sums live in a fixed 4 MiB array inside the library image (present on every GPU that loads
+ * the library, for the life of the process). Limits: hidden <= 8192, otherwise CGPT_ERR_SHAPE. The first
+ * call on a device resolves the array's device address and should be made outside stream capture.
+ * Calls share the array: order them on one stream; calls that overlap on the GPU race on it. */
+int cgpt_rmsnorm_backward_noalloc(void* dx, void* dw, const void* dy, const void* x, const void* w,
+                                  const void* residual_a, const void* residual_b, size_t rows,
+                                  size_t hidden, float epsilon, int dtype, cgpt_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------
  * RoPE on adjacent pairs (x[2p], x[2p+1]) of the first rotary_dim dims of each head, angle index
  * (position_offset + s, p), tables [max_seq, rotary_dim/2] in the tensors' dtype.
