@@ -464,6 +464,15 @@ int gemm_dispatch(void* C, const void* A, const void* B, long long M, long long 
     return CGPT_OK;
 }
 
+unsigned int* tc_status_device_ptr() {
+    static unsigned int* p = nullptr;   // one device per process
+    if (p == nullptr) {
+        void* addr = nullptr;
+        if (cudaGetSymbolAddress(&addr, g_gemm_status) == cudaSuccess) p = static_cast<unsigned int*>(addr);
+    }
+    return p;
+}
+
 int column_sum(void* out, const void* in, long long rows, long long cols, int accumulate, int dtype, cudaStream_t s) {
     CGPT_DISPATCH_DTYPE(dtype, T, {
         column_sum_kernel<T><<<static_cast<unsigned>((cols + 31) / 32), 256, 0, s>>>(
