@@ -1,0 +1,136 @@
+// Compute role (warps 0-3) of attention_bwd_tc_kernel: thread t owns stationary row t = TMEM lane t.
+// Included by attention_bwd_tc.cu only.
+#pragma once
+
+template <typename T, int D, int MODE>
+__device__ __forceinline__ bool bwd_compute(unsigned char* smem, const BwdBars& bars, const BwdGeom& g, const AttnDims& dm,
+                                            std::uint32_t tmem, const float* __restrict__ lse2_t,
+                                            const float* __restrict__ delta_t, T* __restrict__ out1, T* __restrict__ out2,
+                                            int accumulate) {
+    using L = BwdSmem<D>;
+    const int row = threadIdx.x;                       // 0..127
+    const int warp = row >> 5;
+    const std::uint32_t lane_base = static_cast<std::uint32_t>(warp * 32) << 16;
+    const float scale2 = dm.scale * kLog2e;
+    const int x_idx = g.x0 + row;                      // query index (dQ) or key index (dKV) of this thread
+
+    // MODE_DQ: this thread's own statistics; rows past the end get lse2 = +1e30 so that P = 0.
+    float my_lse2 = 1.0e30f, my_delta = 0.f;
+    int limit = 0;                                     // MODE_DQ: last visible key of this query
+    if (MODE == MODE_DQ) {
+        if (x_idx < dm.sq) {
+            const long long t = (static_cast<long long>(g.b) * dm.hq + g.h) * dm.sq + x_idx;
+            my_lse2 = lse2_t[t];
+            my_delta = delta_t[t];
+        }
+        limit = dm.causal ? dm.offset + x_idx : dm.sk - 1;
+        if (limit > dm.sk - 1) limit = dm.sk - 1;
+    }
+    bool failed = false;
+
+    for (int it = 0; it < g.n_it; ++it) {
+        const int s = it & 1;
+        const std::uint32_t par = (it >> 1) & 1;
+        int head, y0;
+        bwd_stream_coords<MODE>(g, it, &head, &y0);
+        // U/W buffer s was last read by the accumulating MMAs of tile it-2
+        if (!mbar_wait(&bars.stage_free[s], par ^ 1u)) failed = true;
+        if (!failed && !mbar_wait(&bars.t_full[s], par)) failed = true;
+        if (MODE == MODE_DKV && !failed && !mbar_wait(&bars.stat_full[s], par)) failed = true;
+        failed = __any_sync(0xffffffffu, failed);
+        if (failed) break;
+        tc_fence_after_sync();
+        const float* st = reinterpret_cast<const float*>(smem + L::kStats) + s * 2 * kCols;
+        unsigned char* u_row = smem + L::kU + s * kRows * 128 + row * 128;
+        unsigned char* w_row = smem + L::kW + s * kRows * 128 + row * 128;
+        // does any element of this tile need the visibility test?
+        bool need_mask;
+        if (MODE == MODE_DQ) need_mask = (y0 + kCols > dm.sk) || (dm.causal && y0 + kCols - 1 > dm.offset + g.x0);
+        else need_mask = dm.causal && (g.x0 + kRows - 1 > dm.offset + y0);
+#pragma unroll
+        for (int c0 = 0; c0 < kCols; c0 += 32) {
+            std::uint32_t t1[32], t2[32];
+            tmem_ld_32x32_x2(tmem + s * kCols + lane_base + c0, t1, tmem + 128 + s * kCols + lane_base + c0, t2);
+            std::uint32_t pu[16], pw[16];
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+                float p[2], ds[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int col = y0 + c0 + j + e;
+                    float lse2, delta;
+                    bool visible = true;
+                    if (MODE == MODE_DQ) {
+                        lse2 = my_lse2; delta = my_delta;
+                        if (need_mask) visible = col <= limit;
+                    } else {
+                        lse2 = st[c0 + j + e]; delta = st[kCols + c0 + j + e];
+                        if (need_mask) visible = x_idx <= dm.offset + col;
+                    }
+                    const float sc = __uint_as_float(t1[j + e]) * scale2;
+                    p[e] = visible ? fast_exp2(sc - lse2) : 0.f;
+                    ds[e] = p[e] * (__uint_as_float(t2[j + e]) - delta) * dm.scale;
+                }
+                pu[j >> 1] = pack2<T>(p[0], p[1]);
+                pw[j >> 1] = pack2<T>(ds[0], ds[1]);
+            }
+            const int c16 = c0 >> 3;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                const std::uint32_t off = static_cast<std::uint32_t>(((c16 + q4) ^ (row & 7)) << 4);
+                if (MODE == MODE_DKV)
+                    *reinterpret_cast<uint4*>(u_row + off) = make_uint4(pu[4 * q4], pu[4 * q4 + 1], pu[4 * q4 + 2], pu[4 * q4 + 3]);
+                *reinterpret_cast<uint4*>(w_row + off) = make_uint4(pw[4 * q4], pw[4 * q4 + 1], pw[4 * q4 + 2], pw[4 * q4 + 3]);
+            }
+        }
+        tc_fence_before_sync();
+        fence_proxy_async_smem();
+        mbar_arrive(&bars.w_full[s]);
+    }
+
+    // ---- epilogue: accumulators -> global
+    if (g.n_it > 0) {
+        if (!failed && !mbar_wait(bars.acc_done, 0)) failed = true;
+        failed = __any_sync(0xffffffffu, failed);
+        if (failed) return false;
+        tc_fence_after_sync();
+    }
+    const int x_limit = MODE == MODE_DQ ? dm.sq : dm.sk;
+    const int heads = MODE == MODE_DQ ? dm.hq : dm.hkv;
+    const int xh = MODE == MODE_DQ ? g.h : g.kvh;
+    const long long dst_off = ((static_cast<long long>(g.b) * x_limit + x_idx) * heads + xh) * D;
+    constexpr int kOuts = MODE == MODE_DKV ? 2 : 1;
+#pragma unroll
+    for (int o = 0; o < kOuts; ++o) {
+        // dKV: acc1 = dV -> out2 (grad_value), acc2 = dK -> out1 (grad_key); dQ: acc1 -> out1
+        T* dst = (MODE == MODE_DKV ? (o == 0 ? out2 : out1) : out1) + dst_off;
+        const std::uint32_t acc = tmem + 256 + o * D;
+#pragma unroll
+        for (int c0 = 0; c0 < D; c0 += 32) {
+            std::uint32_t r[32];
+            if (g.n_it > 0) {
+                tmem_ld_32x32(acc + lane_base + c0, r);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = 0u;
+            }
+            if (x_idx < x_limit) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    float v8[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v8[e] = __uint_as_float(r[j + e]);
+                    if (accumulate) {
+                        float old[8];
+                        load_vec<T, 8>(old, dst + c0 + j);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) v8[e] += old[e];
+                    }
+                    store_vec<T, 8>(dst + c0 + j, v8);
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    return true;
+}

@@ -1,0 +1,148 @@
+// Kernel body and host launch of the tensor-core attention backward. Included by attention_bwd_tc.cu only.
+#pragma once
+
+template <typename T, int D, int MODE>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attention_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_constant__ CUtensorMap map_x2,
+                        const __grid_constant__ CUtensorMap map_y1, const __grid_constant__ CUtensorMap map_y2,
+                        T* __restrict__ out1, T* __restrict__ out2, const float* __restrict__ lse2_t,
+                        const float* __restrict__ delta_t, AttnDims dm, int accumulate, unsigned int* __restrict__ status) {
+    using L = BwdSmem<D>;
+    extern __shared__ unsigned char bwd_smem_raw[];
+    const std::uint32_t raw = smem_u32(bwd_smem_raw);
+    unsigned char* smem = bwd_smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+    std::uint64_t* bar = reinterpret_cast<std::uint64_t*>(smem + L::kBars);
+    BwdBars bars;
+    bars.x_full = bar + 0;
+    bars.y_full = bar + 1;       // [2]
+    bars.stat_full = bar + 3;    // [2]
+    bars.stage_free = bar + 5;   // [2]
+    bars.t_full = bar + 7;       // [2]
+    bars.w_full = bar + 9;       // [2]
+    bars.acc_done = bar + 11;
+    std::uint32_t* tmem_slot = reinterpret_cast<std::uint32_t*>(bar + 12);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    BwdGeom g;
+    g.b = blockIdx.z;
+    g.ratio = dm.hq / dm.hkv;
+    g.i0 = 0;
+    g.n_q = 0;
+    if (MODE == MODE_DQ) {
+        const int q_tiles = (dm.sq + kRows - 1) / kRows;
+        g.x0 = (q_tiles - 1 - static_cast<int>(blockIdx.x)) * kRows;   // longest rows first
+        g.h = blockIdx.y;
+        g.kvh = g.h / g.ratio;
+        int q_last = g.x0 + kRows - 1;
+        if (q_last > dm.sq - 1) q_last = dm.sq - 1;
+        int last_key = dm.causal ? dm.offset + q_last : dm.sk - 1;
+        if (last_key > dm.sk - 1) last_key = dm.sk - 1;
+        g.n_it = last_key / kCols + 1;
+    } else {
+        g.x0 = static_cast<int>(blockIdx.x) * kRows;
+        g.kvh = blockIdx.y;
+        g.h = g.kvh * g.ratio;
+        int first_q = dm.causal ? g.x0 - dm.offset : 0;
+        if (first_q < 0) first_q = 0;
+        g.i0 = first_q / kCols;
+        g.n_q = (dm.sq - 1) / kCols - g.i0 + 1;
+        if (g.n_q < 0) g.n_q = 0;
+        g.n_it = g.ratio * g.n_q;
+    }
+
+    if (threadIdx.x == 0) {
+        mbar_init(bars.x_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars.y_full[s], 1);
+            mbar_init(&bars.stat_full[s], 32);
+            mbar_init(&bars.stage_free[s], 1);
+            mbar_init(&bars.t_full[s], 1);
+            mbar_init(&bars.w_full[s], kRows);
+        }
+        mbar_init(bars.acc_done, 1);
+        mbar_init_fence();
+        tma_prefetch_desc(&map_x1); tma_prefetch_desc(&map_x2); tma_prefetch_desc(&map_y1); tma_prefetch_desc(&map_y2);
+    }
+    if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const std::uint32_t tmem = *tmem_slot;
+
+    bool ok = true;
+    if (warp == 4) {
+        if (g.n_it > 0) ok = bwd_producer<D, MODE>(smem, bars, g, dm, &map_x1, &map_x2, &map_y1, &map_y2, lse2_t, delta_t, lane);
+    } else if (warp == 5) {
+        if (lane == 0 && g.n_it > 0) ok = bwd_mma_issuer<T, D, MODE>(smem, bars, g, tmem);
+    } else {
+        ok = bwd_compute<T, D, MODE>(smem, bars, g, dm, tmem, lse2_t, delta_t, out1, out2, accumulate);
+    }
+    if (!ok) {
+        atomicExch(status, 2u);
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) { }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+// 4D tensor map over a [batch, seq, heads, D] tensor: box = 64 columns x 1 head x `rows` positions.
+inline int make_bshd_map_rows(CUtensorMap* map, const void* base, int dtype, int batch, int seq, int heads, int d, int rows) {
+    const std::uint64_t dims[4] = {static_cast<std::uint64_t>(d), static_cast<std::uint64_t>(heads), static_cast<std::uint64_t>(seq),
+                                   static_cast<std::uint64_t>(batch)};
+    const std::uint64_t strides[3] = {static_cast<std::uint64_t>(d) * 2, static_cast<std::uint64_t>(heads) * d * 2,
+                                      static_cast<std::uint64_t>(seq) * heads * d * 2};
+    const std::uint32_t box[4] = {64, 1, static_cast<std::uint32_t>(rows), 1};
+    return make_tensor_map(map, dtype, base, 4, dims, strides, box);
+}
+
+template <typename T, int D>
+int launch_backward(void* dq, void* dk, void* dv, const void* dout, const void* out, const float* lse, const void* q,
+                    const void* k, const void* v, const AttnDims& dm, int accumulate, int dtype, cudaStream_t s) {
+    using L = BwdSmem<D>;
+    const long long qrows = static_cast<long long>(dm.batch) * dm.sq * dm.hq;
+    void* scratch = nullptr;
+    CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(qrows) * 2 * sizeof(float), s));
+    float* delta_t = static_cast<float*>(scratch);
+    float* lse2_t = delta_t + qrows;
+    attention_bwd_prep_kernel<T><<<static_cast<unsigned>((qrows + 3) / 4), 128, 0, s>>>(
+        delta_t, lse2_t, static_cast<const T*>(dout), static_cast<const T*>(out), lse, dm.batch, dm.sq, dm.hq, D);
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+
+    CUtensorMap q128, do128, k64, v64, k128, v128, q64, do64;
+    CGPT_TRY(make_bshd_map_rows(&q128, q, dtype, dm.batch, dm.sq, dm.hq, D, kRows));
+    CGPT_TRY(make_bshd_map_rows(&do128, dout, dtype, dm.batch, dm.sq, dm.hq, D, kRows));
+    CGPT_TRY(make_bshd_map_rows(&k64, k, dtype, dm.batch, dm.sk, dm.hkv, D, kCols));
+    CGPT_TRY(make_bshd_map_rows(&v64, v, dtype, dm.batch, dm.sk, dm.hkv, D, kCols));
+    CGPT_TRY(make_bshd_map_rows(&k128, k, dtype, dm.batch, dm.sk, dm.hkv, D, kRows));
+    CGPT_TRY(make_bshd_map_rows(&v128, v, dtype, dm.batch, dm.sk, dm.hkv, D, kRows));
+    CGPT_TRY(make_bshd_map_rows(&q64, q, dtype, dm.batch, dm.sq, dm.hq, D, kCols));
+    CGPT_TRY(make_bshd_map_rows(&do64, dout, dtype, dm.batch, dm.sq, dm.hq, D, kCols));
+
+    auto kq = attention_bwd_tc_kernel<T, D, MODE_DQ>;
+    auto kkv = attention_bwd_tc_kernel<T, D, MODE_DKV>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        CGPT_CUDA_TRY(cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
+        CGPT_CUDA_TRY(cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
+        attr_done = true;
+    }
+    unsigned int* status = tc_status_device_ptr();
+    if (status == nullptr) return CGPT_ERR_STATE;
+    const dim3 grid_q((dm.sq + kRows - 1) / kRows, dm.hq, dm.batch);
+    kq<<<grid_q, kBwdThreads, L::kBytes, s>>>(q128, do128, k64, v64, static_cast<T*>(dq), static_cast<T*>(nullptr), lse2_t, delta_t, dm,
+                                              accumulate, status);
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+    const dim3 grid_kv((dm.sk + kRows - 1) / kRows, dm.hkv, dm.batch);
+    kkv<<<grid_kv, kBwdThreads, L::kBytes, s>>>(k128, v128, q64, do64, static_cast<T*>(dk), static_cast<T*>(dv), lse2_t, delta_t, dm,
+                                                accumulate, status);
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+    return CGPT_OK;
+}

@@ -1,0 +1,133 @@
+// Producer (TMA) and MMA-issuer roles of attention_bwd_tc_kernel. Included by attention_bwd_tc.cu only.
+#pragma once
+
+// Geometry of one CTA's work, computed identically by every thread.
+struct BwdGeom {
+    int b;        // batch index
+    int h;        // MODE_DQ: query head of this CTA
+    int kvh;      // kv head
+    int x0;       // first stationary row: query index (dQ) or key index (dKV)
+    int n_it;     // streaming tiles to process
+    int i0;       // MODE_DKV: first 64-query tile that can see this key tile
+    int n_q;      // MODE_DKV: 64-query tiles per query head
+    int ratio;    // query heads per kv head
+};
+
+struct BwdBars {
+    std::uint64_t *x_full, *y_full, *stat_full, *stage_free, *t_full, *w_full, *acc_done;
+};
+
+// Streaming tile `it` -> (head, first row of the streaming tile).
+template <int MODE>
+__device__ __forceinline__ void bwd_stream_coords(const BwdGeom& g, int it, int* head, int* row0) {
+    if (MODE == MODE_DQ) {
+        *head = g.kvh;             // K / V tiles of the kv head
+        *row0 = it * kCols;
+    } else {
+        *head = g.kvh * g.ratio + it / g.n_q;
+        *row0 = (g.i0 + it % g.n_q) * kCols;
+    }
+}
+
+template <int D, int MODE>
+__device__ __forceinline__ bool bwd_producer(unsigned char* smem, const BwdBars& bars, const BwdGeom& g, const AttnDims& dm,
+                                             const CUtensorMap* map_x1, const CUtensorMap* map_x2, const CUtensorMap* map_y1,
+                                             const CUtensorMap* map_y2, const float* __restrict__ lse2_t,
+                                             const float* __restrict__ delta_t, int lane) {
+    using L = BwdSmem<D>;
+    if (lane == 0) {
+        const int xh = MODE == MODE_DQ ? g.h : g.kvh;
+        mbar_expect_tx(bars.x_full, 2 * L::kXBytes);
+#pragma unroll
+        for (int c = 0; c < L::kChunks; ++c) {
+            tma_load_4d(smem + L::kX1 + c * kRows * 128, map_x1, bars.x_full, c * 64, xh, g.x0, g.b);
+            tma_load_4d(smem + L::kX2 + c * kRows * 128, map_x2, bars.x_full, c * 64, xh, g.x0, g.b);
+        }
+    }
+    for (int it = 0; it < g.n_it; ++it) {
+        const int s = it & 1;
+        if (!mbar_wait(&bars.stage_free[s], ((it >> 1) & 1) ^ 1u)) return false;
+        int head, row0;
+        bwd_stream_coords<MODE>(g, it, &head, &row0);
+        if (lane == 0) {
+            unsigned char* y1 = smem + L::kY + s * 2 * L::kYBytes;
+            unsigned char* y2 = y1 + L::kYBytes;
+            mbar_expect_tx(&bars.y_full[s], 2 * L::kYBytes);
+#pragma unroll
+            for (int c = 0; c < L::kChunks; ++c) {
+                tma_load_4d(y1 + c * kCols * 128, map_y1, &bars.y_full[s], c * 64, head, row0, g.b);
+                tma_load_4d(y2 + c * kCols * 128, map_y2, &bars.y_full[s], c * 64, head, row0, g.b);
+            }
+        }
+        if (MODE == MODE_DKV) {
+            // per-query statistics of the streaming tile: lse2 (+1e30 for rows past the end -> P = 0) and delta
+            float* st = reinterpret_cast<float*>(smem + L::kStats) + s * 2 * kCols;
+            const long long base = (static_cast<long long>(g.b) * dm.hq + head) * dm.sq;
+#pragma unroll
+            for (int j = lane; j < kCols; j += 32) {
+                const int q = row0 + j;
+                st[j] = q < dm.sq ? lse2_t[base + q] : 1.0e30f;
+                st[kCols + j] = q < dm.sq ? delta_t[base + q] : 0.f;
+            }
+            mbar_arrive(&bars.stat_full[s]);
+        }
+    }
+    return true;
+}
+
+template <typename T, int D, int MODE>
+__device__ __forceinline__ bool bwd_mma_issuer(unsigned char* smem, const BwdBars& bars, const BwdGeom& g, std::uint32_t tmem) {
+    using L = BwdSmem<D>;
+    constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+    constexpr std::uint32_t idesc_t = idesc_f16(fmt, 0, 0, kRows, kCols);   // T = X Y^T: both K-major
+    constexpr std::uint32_t idesc_acc = idesc_f16(fmt, 0, 1, kRows, D);     // acc += U/W (K-major) * Y (N-major)
+    const std::uint32_t x1 = smem_u32(smem + L::kX1), x2 = smem_u32(smem + L::kX2);
+    const std::uint32_t tmem_acc1 = tmem + 256, tmem_acc2 = tmem + 256 + D;
+
+    auto issue_t = [&](int it) -> bool {
+        const int s = it & 1;
+        if (!mbar_wait(&bars.y_full[s], (it >> 1) & 1)) return false;
+        tc_fence_after_sync();
+        const std::uint32_t y1 = smem_u32(smem + L::kY + s * 2 * L::kYBytes), y2 = y1 + L::kYBytes;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+            const std::uint32_t xo = (k >> 2) * (kRows * 128) + (k & 3) * 32, yo = (k >> 2) * (kCols * 128) + (k & 3) * 32;
+            mma_f16_ss(tmem + s * kCols, smem_desc_sw128(x1 + xo, 16, 1024), smem_desc_sw128(y1 + yo, 16, 1024), idesc_t, k > 0);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+            const std::uint32_t xo = (k >> 2) * (kRows * 128) + (k & 3) * 32, yo = (k >> 2) * (kCols * 128) + (k & 3) * 32;
+            mma_f16_ss(tmem + 128 + s * kCols, smem_desc_sw128(x2 + xo, 16, 1024), smem_desc_sw128(y2 + yo, 16, 1024), idesc_t, k > 0);
+        }
+        tc_commit(&bars.t_full[s]);
+        return true;
+    };
+
+    if (!mbar_wait(bars.x_full, 0)) return false;
+    if (!issue_t(0)) return false;
+    for (int it = 0; it < g.n_it; ++it) {
+        const int s = it & 1;
+        if (it + 1 < g.n_it && !issue_t(it + 1)) return false;
+        if (!mbar_wait(&bars.w_full[s], (it >> 1) & 1)) return false;
+        tc_fence_after_sync();
+        const std::uint32_t y1 = smem_u32(smem + L::kY + s * 2 * L::kYBytes), y2 = y1 + L::kYBytes;
+        const std::uint32_t u = smem_u32(smem + L::kU + s * kRows * 128), w = smem_u32(smem + L::kW + s * kRows * 128);
+#pragma unroll
+        for (int k = 0; k < kCols / 16; ++k) {
+            // A: [128 rows][64] K-major, one swizzle atom wide; B: streaming tile as N-major: 16 rows of 128 B per K step,
+            // 64-column chunks of D kCols*128 bytes apart.
+            if (MODE == MODE_DKV) {
+                mma_f16_ss(tmem_acc1, smem_desc_sw128(u + k * 32, 16, 1024), smem_desc_sw128(y2 + k * (16 * 128), kCols * 128, 1024),
+                           idesc_acc, (it > 0 || k > 0) ? 1u : 0u);                  // dV += P^T dO
+                mma_f16_ss(tmem_acc2, smem_desc_sw128(w + k * 32, 16, 1024), smem_desc_sw128(y1 + k * (16 * 128), kCols * 128, 1024),
+                           idesc_acc, (it > 0 || k > 0) ? 1u : 0u);                  // dK += dS^T Q
+            } else {
+                mma_f16_ss(tmem_acc1, smem_desc_sw128(w + k * 32, 16, 1024), smem_desc_sw128(y1 + k * (16 * 128), kCols * 128, 1024),
+                           idesc_acc, (it > 0 || k > 0) ? 1u : 0u);                  // dQ += dS K
+            }
+        }
+        tc_commit(&bars.stage_free[s]);
+    }
+    tc_commit(bars.acc_done);
+    return true;
+}

@@ -1,11 +1,126 @@
-// Tensor-core attention backward (stub until the kernels below are filled in).
+// Tensor-core (tcgen05 / TMEM / TMA) attention backward for sm_100a: 16-bit tensors, head_dim 64 or 128,
+// any GQA ratio, causal (with query_position_offset) or full. Three launches, no atomics, no fp32
+// gradient scratch, bit-reproducible:
+//
+//   1. attention_bwd_prep_kernel   delta[b,h,q] = sum_d dO*O and lse2[b,h,q] = LSE * log2(e), both stored
+//                                  [batch, heads, seq] so that a tile's 64 or 128 values are contiguous.
+//   2. attention_bwd_tc_kernel<MODE_DQ>   one CTA per (128-query tile, query head, batch); streams 64-key
+//                                  tiles: S = Q K^T, dP = dO V^T -> dS -> dQ += dS K          (3 MMAs / tile)
+//   3. attention_bwd_tc_kernel<MODE_DKV>  one CTA per (128-key tile, kv head, batch); streams 64-query
+//                                  tiles of every query head of the group: S^T = K Q^T, dP^T = V dO^T ->
+//                                  P^T, dS^T -> dV += P^T dO, dK += dS^T Q                     (4 MMAs / tile)
+// Like the reference's tensor-core backward (src/ops/backward/attention_backward.cu:1167-1677) S and dP are
+// recomputed in both kernels (7 GEMM-equivalents for the 5 algorithmic ones) in exchange for having exactly
+// one writer per output element. Rounding points are the reference's: P and scale*dS are rounded to the
+// storage dtype before the second products (:1336-1343, :1567-1586); everything else is fp32.
+//
+// Both kernels are one template. A "stationary" pair of [128, D] tiles (X1, X2) stays in shared memory,
+// a "streaming" pair of [64, D] tiles (Y1, Y2) runs through a 2-stage TMA ring:
+//     T1 = X1 Y1^T, T2 = X2 Y2^T            two 128x64 fp32 tiles in TMEM (double-buffered)
+//     threads (one per TMEM lane = stationary row) turn T1/T2 into 16-bit tiles U (P^T) and W (dS or dS^T)
+//     in 128B-swizzled shared memory (K-major A operands)
+//     acc1 += U Y2, acc2 += W Y1 (dKV)   or   acc1 += W Y1 (dQ)      accumulators stay in TMEM
+// The streaming tiles serve twice from the same bytes: as K-major B operands of T1/T2 and as N-major
+// ("MN-major") B operands of the accumulating products.
+#include <type_traits>
+
 #include "attention.h"
+#include "launch_counter.h"
+#include "sm100.cuh"
 
 namespace cgpt {
 
-int attention_backward_tc_launch(void*, void*, void*, const void*, const void*, const float*, const void*, const void*,
-                                 const void*, const AttnDims&, int, int, cudaStream_t) {
-    return CGPT_ERR_UNSUPPORTED;
+unsigned int* tc_status_device_ptr();   // gemm.cu
+
+namespace {
+
+using namespace sm100;
+
+constexpr int kRows = 128;   // stationary tile rows = TMEM lanes
+constexpr int kCols = 64;    // streaming tile rows = columns of T1/T2
+constexpr int kBwdThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int MODE_DQ = 0, MODE_DKV = 1;
+
+template <int D> struct BwdSmem {
+    static constexpr int kChunks = D / 64;
+    static constexpr int kXBytes = kChunks * kRows * 128;     // one stationary tile
+    static constexpr int kYBytes = kChunks * kCols * 128;     // one streaming tile
+    static constexpr int kX1 = 0;
+    static constexpr int kX2 = kX1 + kXBytes;
+    static constexpr int kY = kX2 + kXBytes;                  // [2 stages][Y1 | Y2]
+    static constexpr int kU = kY + 4 * kYBytes;               // [2] x [128 rows][128 B]
+    static constexpr int kW = kU + 2 * kRows * 128;           // [2] x [128 rows][128 B]
+    static constexpr int kStats = kW + 2 * kRows * 128;       // [2 stages][2][64] fp32
+    static constexpr int kBars = kStats + 2 * 2 * kCols * 4;
+    static constexpr int kBytes = kBars + 256 + 1024;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <typename T> __device__ __forceinline__ std::uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ std::uint32_t pack2<__half>(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<std::uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ std::uint32_t pack2<__nv_bfloat16>(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<std::uint32_t*>(&h);
+}
+
+// delta and lse2 in [batch, heads, seq] order. One warp per (b, q, h) row of dO / O.
+template <typename T>
+__global__ void __launch_bounds__(128)
+attention_bwd_prep_kernel(float* __restrict__ delta_t, float* __restrict__ lse2_t, const T* __restrict__ dout,
+                          const T* __restrict__ out, const float* __restrict__ lse, int batch, int sq, int hq, int d) {
+    const long long row = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    const long long rows = static_cast<long long>(batch) * sq * hq;
+    if (row >= rows) return;
+    float s = 0.f;
+    const T* a = dout + row * d;
+    const T* o = out + row * d;
+    for (int c = lane * 8; c < d; c += 256) {
+        float x[8], y[8];
+        load_vec<T, 8>(x, a + c);
+        load_vec<T, 8>(y, o + c);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s = fmaf(x[e], y[e], s);
+    }
+    s = warp_sum(s);
+    if (lane == 0) {
+        const int h = static_cast<int>(row % hq);
+        const int q = static_cast<int>((row / hq) % sq);
+        const long long b = row / (static_cast<long long>(hq) * sq);
+        const long long t = (b * hq + h) * sq + q;
+        delta_t[t] = s;
+        lse2_t[t] = lse[row] * kLog2e;
+    }
+}
+
+#include "attention_bwd_roles.cuh"
+#include "attention_bwd_compute.cuh"
+#include "attention_bwd_main.cuh"
+
+}  // namespace
+
+int attention_backward_tc_launch(void* dq, void* dk, void* dv, const void* dout, const void* out, const float* lse,
+                                 const void* q, const void* k, const void* v, const AttnDims& dm, int accumulate, int dtype,
+                                 cudaStream_t s) {
+    if (dtype == CGPT_DTYPE_F32 || (dm.d != 64 && dm.d != 128)) return CGPT_ERR_UNSUPPORTED;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !aligned16(dout) || !aligned16(dq) ||
+        !aligned16(dk) || !aligned16(dv))
+        return CGPT_ERR_UNSUPPORTED;
+    if (dm.hq > 65535 || dm.batch > 65535) return CGPT_ERR_UNSUPPORTED;
+    if (dtype == CGPT_DTYPE_F16)
+        return dm.d == 64 ? launch_backward<__half, 64>(dq, dk, dv, dout, out, lse, q, k, v, dm, accumulate, dtype, s)
+                          : launch_backward<__half, 128>(dq, dk, dv, dout, out, lse, q, k, v, dm, accumulate, dtype, s);
+    return dm.d == 64 ? launch_backward<__nv_bfloat16, 64>(dq, dk, dv, dout, out, lse, q, k, v, dm, accumulate, dtype, s)
+                      : launch_backward<__nv_bfloat16, 128>(dq, dk, dv, dout, out, lse, q, k, v, dm, accumulate, dtype, s);
 }
 
 }  // namespace cgpt
