@@ -40,3 +40,41 @@ def time_gemms(train_step, steps: int = 2) -> dict:
     model = (model_flops_per_token(ts.options) + attention_flops_per_token(ts.options, ts.seq)) * tokens
     return {"ms": ms.value / steps, "tflops": fl.value / ms.value / 1e9 if ms.value > 0 else 0.0,
             "launches": int(n.value) // steps, "gemm_flops": fl.value / steps, "model_flops": model}
+
+
+def main() -> None:
+    """`python -m cgpt_b200.profiling [--steps K] [--warmup W] [--preset 104m] [--batch 32] [--seq 1024]`:
+    runs eager (no CUDA graph) training steps so that a profiler sees every kernel launch of a step; prints the
+    mean step time. Used for the launch lists and ncu captures summarised under profiles/."""
+    import argparse
+
+    from . import model as M
+    from .train import TrainStep
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=1)
+    ap.add_argument("--warmup", type=int, default=1)
+    ap.add_argument("--preset", default="104m")
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--seq", type=int, default=1024)
+    args = ap.parse_args()
+    opts = M.preset(args.preset)
+    ts = TrainStep(opts, args.batch, args.seq, seed=0, use_graph=False)
+    ts.token_ids.copy_(torch.randint(0, opts.vocabulary_size, (args.batch * args.seq,), dtype=torch.int32))
+    ts.targets.copy_(torch.randint(0, opts.vocabulary_size, (args.batch * args.seq,), dtype=torch.int32))
+    for _ in range(args.warmup):
+        ts.step()
+    ts.stream.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(ts.stream):
+        e0.record()
+    for _ in range(args.steps):
+        ts.step()
+    with torch.cuda.stream(ts.stream):
+        e1.record()
+    ts.stream.synchronize()
+    print(f"eager step: {e0.elapsed_time(e1) / args.steps:.3f} ms, loss {ts.read_loss():.4f}")
+
+
+if __name__ == "__main__":
+    main()
