@@ -14,6 +14,7 @@
 // accumulator from TMEM (tcgen05.ld), convert and store. Split-K writes fp32 partials that a small
 // kernel sums in a fixed order (deterministic; used when the tile count alone cannot fill 148 SMs,
 // e.g. dW with K = tokens). Algorithmic work: 2*M*N*K flops.
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 #include <vector>
@@ -343,6 +344,14 @@ column_sum_kernel(T* __restrict__ out, const T* __restrict__ in, long long rows,
     }
 }
 
+#include "gemm_persistent.cuh"
+
+// CGPT_B200_GEMM_V1=1 selects the one-tile-per-CTA kernel instead of the persistent one (for A/B timing).
+inline bool use_v1_gemm() {
+    static const bool v1 = [] { const char* e = std::getenv("CGPT_B200_GEMM_V1"); return e != nullptr && e[0] == '1'; }();
+    return v1;
+}
+
 template <typename T, int BN, bool A_MN, bool B_MN>
 int launch_tc(T* C, const T* A, const T* B, int M, int N, int K, int accumulate, int dtype, cudaStream_t s) {
     using Cfg = GemmCfg<BN>;
@@ -383,16 +392,24 @@ int launch_tc(T* C, const T* A, const T* B, int M, int N, int K, int accumulate,
         partial = static_cast<float*>(scratch);
     }
     auto kernel = gemm_tcgen05_kernel<T, BN, A_MN, B_MN>;
+    auto pkernel = gemm_tcgen05_persistent_kernel<T, BN, A_MN, B_MN>;
     static bool attr_done = false;
     if (!attr_done) {
         CGPT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        CGPT_CUDA_TRY(cudaFuncSetAttribute(pkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         attr_done = true;
     }
-    const dim3 grid(tiles_m, tiles_n, splits);
     const int epi = splits > 1 ? kEpiPartial : (accumulate ? kEpiAccumulate : kEpiStore);
     const bool timed = g_timing.enabled && g_timing.used + 2 <= g_timing.events.size();
     if (timed) CGPT_CUDA_TRY(cudaEventRecord(g_timing.events[g_timing.used], s));
-    kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, C, partial, M, N, K, kb_per_split, epi);
+    if (use_v1_gemm()) {
+        const dim3 grid(tiles_m, tiles_n, splits);
+        kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, C, partial, M, N, K, kb_per_split, epi);
+    } else {
+        const long long units = static_cast<long long>(tiles) * splits;
+        const unsigned grid = static_cast<unsigned>(units < kNumSMs ? units : kNumSMs);
+        pkernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, C, partial, M, N, K, tiles_m, tiles_n, splits, kb_per_split, epi);
+    }
     count_launch();
     CGPT_LAUNCH_CHECK();
     if (timed) {
@@ -415,9 +432,9 @@ int launch_tc(T* C, const T* A, const T* B, int M, int N, int K, int accumulate,
 template <typename T>
 int launch_tc_layout(T* C, const T* A, const T* B, int M, int N, int K, int a_mn, int b_mn, int accumulate, int dtype,
                      cudaStream_t s) {
-    // 128x256 tiles when that still gives every SM a tile; 128x128 otherwise.
-    const long long tiles256 = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256);
-    const bool wide = N >= 256 && tiles256 >= kNumSMs;
+    // 128x256 tiles whenever N allows: a 128x128 tile needs as many shared-memory operand bytes per MMA as the
+    // tensor core can consume, 128x256 needs 3/4 of that per FLOP. Few tiles are compensated by split-K.
+    const bool wide = N >= 256;
 #define CGPT_GEMM_CASE(AM, BMN)                                                                  \
     if (a_mn == AM && b_mn == BMN)                                                               \
         return wide ? launch_tc<T, 256, AM != 0, BMN != 0>(C, A, B, M, N, K, accumulate, dtype, s) \

@@ -1,0 +1,197 @@
+// Persistent variant of the tcgen05 GEMM. Included by gemm.cu only (inside its anonymous namespace).
+//
+// One CTA per SM walks a list of work units (output tile x K split). The TMA ring and its phase counters
+// run on across units; the fp32 accumulator is double-buffered in TMEM (2 x BN columns) so that the four
+// epilogue warps drain tile j (tcgen05.ld -> convert -> global stores) while the MMA warp already
+// accumulates tile j+1. Units are ordered tile_n fastest so that CTAs running at the same time share the
+// same rows of A through L2.
+#pragma once
+
+// One 32-column chunk of an accumulator row -> global memory.
+template <typename T>
+__device__ __forceinline__ void gemm_store_chunk(const std::uint32_t (&r)[32], T* __restrict__ C, float* __restrict__ partial,
+                                                 int row, int col0, int M, int N, int split, int epilogue) {
+    if (row >= M || col0 >= N) return;
+    if (epilogue == kEpiPartial) {
+        float* dst = partial + (static_cast<long long>(split) * M + row) * N + col0;
+        if (col0 + 32 <= N && (N & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                                  __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) dst[j] = __uint_as_float(r[j]);
+        }
+        return;
+    }
+    T* dst = C + static_cast<long long>(row) * N + col0;
+    if (col0 + 32 <= N && (N & 7) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+            if (epilogue == kEpiAccumulate) {
+                float old[8];
+                load_vec<T, 8>(old, dst + j);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] += old[e];
+            }
+            store_vec<T, 8>(dst + j, v);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (col0 + j < N) {
+                float v = __uint_as_float(r[j]);
+                if (epilogue == kEpiAccumulate) v += to_f32<T>(dst[j]);
+                dst[j] = from_f32<T>(v);
+            }
+        }
+    }
+}
+
+template <typename T, int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                               T* __restrict__ C, float* __restrict__ partial, int M, int N, int K, int tiles_m, int tiles_n,
+                               int splits, int kb_per_split, int epilogue) {
+    using Cfg = GemmCfg<BN>;
+    extern __shared__ unsigned char gemm_smem_raw[];
+    const std::uint32_t raw = smem_u32(gemm_smem_raw);
+    unsigned char* smem = gemm_smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+    std::uint64_t* bars = reinterpret_cast<std::uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+    std::uint64_t* full = bars;
+    std::uint64_t* empty = bars + Cfg::kStages;
+    std::uint64_t* acc_full = bars + 2 * Cfg::kStages;       // [2]
+    std::uint64_t* acc_empty = bars + 2 * Cfg::kStages + 2;  // [2]
+    std::uint32_t* tmem_slot = reinterpret_cast<std::uint32_t*>(bars + 2 * Cfg::kStages + 4);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int total_kb = (K + BK - 1) / BK;
+    const int tiles = tiles_m * tiles_n;
+    const int units = tiles * splits;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        mbar_init_fence();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 2 * BN);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const std::uint32_t tmem_base = *tmem_slot;
+    bool failed = false;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            for (int u = blockIdx.x; u < units && !failed; u += gridDim.x) {
+                const int split = u / tiles, t = u % tiles;
+                const int tile_m = t / tiles_n, tile_n = t % tiles_n;
+                const int kb_begin = split * kb_per_split;
+                int nkb = total_kb - kb_begin;
+                if (nkb > kb_per_split) nkb = kb_per_split;
+                for (int i = 0; i < nkb; ++i, ++it) {
+                    const int s = it % Cfg::kStages;
+                    const std::uint32_t ph = (it / Cfg::kStages) & 1;
+                    if (!mbar_wait(&empty[s], ph ^ 1u)) { failed = true; break; }
+                    mbar_expect_tx(&full[s], Cfg::kStageBytes);
+                    unsigned char* a_dst = smem + s * Cfg::kStageBytes;
+                    unsigned char* b_dst = a_dst + Cfg::kABytes;
+                    const int k0 = (kb_begin + i) * BK;
+                    if (!A_MN) {
+                        tma_load_2d(a_dst, &tmap_a, &full[s], k0, tile_m * BM);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * (BK * 128), &tmap_a, &full[s], tile_m * BM + j * 64, k0);
+                    }
+                    if (!B_MN) {
+                        tma_load_2d(b_dst, &tmap_b, &full[s], k0, tile_n * BN);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * (BK * 128), &tmap_b, &full[s], tile_n * BN + j * 64, k0);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr std::uint32_t idesc = idesc_f16(std::is_same<T, __nv_bfloat16>::value ? 1 : 0, A_MN ? 1 : 0, B_MN ? 1 : 0, BM, BN);
+            int it = 0, j = 0;
+            for (int u = blockIdx.x; u < units && !failed; u += gridDim.x, ++j) {
+                const int split = u / tiles;
+                const int kb_begin = split * kb_per_split;
+                int nkb = total_kb - kb_begin;
+                if (nkb > kb_per_split) nkb = kb_per_split;
+                const int buf = j & 1;
+                if (!mbar_wait(&acc_empty[buf], ((j >> 1) & 1) ^ 1u)) { failed = true; break; }
+                tc_fence_after_sync();
+                const std::uint32_t tmem_acc = tmem_base + buf * BN;
+                for (int i = 0; i < nkb; ++i, ++it) {
+                    const int s = it % Cfg::kStages;
+                    const std::uint32_t ph = (it / Cfg::kStages) & 1;
+                    if (!mbar_wait(&full[s], ph)) { failed = true; break; }
+                    tc_fence_after_sync();
+                    const std::uint32_t a_base = smem_u32(smem + s * Cfg::kStageBytes);
+                    const std::uint32_t b_base = a_base + Cfg::kABytes;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const std::uint64_t adesc = A_MN ? smem_desc_sw128(a_base + k * (UMMA_K * 128), BK * 128, 1024)
+                                                         : smem_desc_sw128(a_base + k * (UMMA_K * 2), 16, 1024);
+                        const std::uint64_t bdesc = B_MN ? smem_desc_sw128(b_base + k * (UMMA_K * 128), BK * 128, 1024)
+                                                         : smem_desc_sw128(b_base + k * (UMMA_K * 2), 16, 1024);
+                        mma_f16_ss(tmem_acc, adesc, bdesc, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tc_commit(&empty[s]);
+                }
+                tc_commit(&acc_full[buf]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int j = 0;
+        for (int u = blockIdx.x; u < units; u += gridDim.x, ++j) {
+            const int split = u / tiles, t = u % tiles;
+            const int tile_m = t / tiles_n, tile_n = t % tiles_n;
+            const int buf = j & 1;
+            if (!mbar_wait(&acc_full[buf], (j >> 1) & 1)) failed = true;
+            failed = __any_sync(0xffffffffu, failed);
+            if (failed) break;
+            tc_fence_after_sync();
+            const int row = tile_m * BM + quarter * 32 + lane;
+            const std::uint32_t tmem_acc = tmem_base + buf * BN + (static_cast<std::uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 64) {
+                std::uint32_t r0[32], r1[32];
+                tmem_ld_32x32_x2(tmem_acc + c0, r0, tmem_acc + c0 + 32, r1);
+                gemm_store_chunk<T>(r0, C, partial, row, tile_n * BN + c0, M, N, split, epilogue);
+                gemm_store_chunk<T>(r1, C, partial, row, tile_n * BN + c0 + 32, M, N, split, epilogue);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+    }
+
+    if (failed) {
+        atomicExch(&g_gemm_status, 1u);
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) { }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 2 * BN);
+    }
+}
