@@ -1,0 +1,88 @@
+"""`python -m cgpt_b200.profile_ops <op> [--iters N]`: launches one operator a few times on inputs larger
+than L2 but a few hundred MB at most, so that `ncu -k regex:<kernel>` captures of it end by themselves.
+Ops: gemm_fwd, gemm_dx, gemm_dw, attention_fwd, attention_bwd, rmsnorm_bwd, swiglu_bwd, adamw, cross_entropy.
+Prints the CUDA-event time per launch (taken without a profiler attached it is the number to quote)."""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from . import ops, optim
+
+
+def _run(fn, iters):
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op")
+    ap.add_argument("--iters", type=int, default=3)
+    a = ap.parse_args()
+    h = lambda *s: torch.randn(*s, device="cuda").half()
+    T, d, I = 32768, 1024, 2048
+    if a.op in ("gemm_fwd", "gemm_dx", "gemm_dw"):
+        x, w, dy = h(T, d), h(I, d) * 0.02, h(T, I)
+        y, dx, dw = torch.empty(T, I, device="cuda", dtype=torch.float16), torch.empty_like(x), torch.empty_like(w)
+        fn = {"gemm_fwd": lambda: ops.linear_forward(y, x, w),
+              "gemm_dx": lambda: ops.linear_backward(dx, None, None, dy, x, w),
+              "gemm_dw": lambda: ops.linear_backward(None, dw, None, dy, x, w)}[a.op]
+        ms = _run(fn, a.iters)
+        print(f"{a.op} {T}x{I}x{d}: {ms * 1e3:.1f} us, {2.0 * T * d * I / ms / 1e9:.1f} TFLOP/s")
+    elif a.op in ("attention_fwd", "attention_bwd"):
+        B, S, Hq, Hkv, D = 32, 1024, 8, 2, 128
+        q, k, v, do = h(B, S, Hq, D), h(B, S, Hkv, D), h(B, S, Hkv, D), h(B, S, Hq, D)
+        o, lse = torch.empty_like(q), torch.empty(B, S, Hq, device="cuda")
+        opts = ops.FlashAttentionOptions(Hq, Hkv, D)
+        ops.flash_gqa_attention_forward_with_lse(o, lse, q, k, v, None, opts)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        fwd = 4.0 * S * S * D * Hq * B / 2
+        if a.op == "attention_fwd":
+            ms = _run(lambda: ops.flash_gqa_attention_forward_with_lse(o, lse, q, k, v, None, opts), a.iters)
+            print(f"attention_fwd B{B} S{S} {Hq}/{Hkv} D{D}: {ms * 1e3:.1f} us, {fwd / ms / 1e9:.1f} TFLOP/s")
+        else:
+            ms = _run(lambda: ops.flash_gqa_attention_backward_with_lse(dq, dk, dv, do, o, lse, q, k, v, None, opts), a.iters)
+            print(f"attention_bwd B{B} S{S} {Hq}/{Hkv} D{D}: {ms * 1e3:.1f} us, {2.5 * fwd / ms / 1e9:.1f} TFLOP/s (5 GEMMs, causal half)")
+    elif a.op == "rmsnorm_bwd":
+        x, dy, w = h(T, d), h(T, d), torch.ones(d, device="cuda", dtype=torch.float16)
+        dx, dw = torch.empty_like(x), torch.empty_like(w)
+        ms = _run(lambda: ops.rmsnorm_backward(dx, dw, dy, x, w, 1e-5), a.iters)
+        print(f"rmsnorm_bwd {T}x{d}: {ms * 1e3:.1f} us, {3.0 * T * d * 2 / ms / 1e6:.0f} GB/s algorithmic")
+    elif a.op == "swiglu_bwd":
+        g, u, dy = h(T, I), h(T, I), h(T, I)
+        dg, du = torch.empty_like(g), torch.empty_like(g)
+        ms = _run(lambda: ops.swiglu_backward(dg, du, dy, g, u), a.iters)
+        print(f"swiglu_bwd {T}x{I}: {ms * 1e3:.1f} us, {5.0 * T * I * 2 / ms / 1e6:.0f} GB/s algorithmic")
+    elif a.op == "cross_entropy":
+        rows, V = 8192, 32000
+        z, t = h(rows, V), torch.randint(0, V, (rows,), device="cuda", dtype=torch.int32)
+        loss = torch.zeros(1, device="cuda")
+        ms = _run(lambda: ops.cross_entropy_forward_backward(loss, z, z, t, rows, None, 1024.0), a.iters)
+        print(f"cross_entropy {rows}x{V} in place: {ms * 1e3:.1f} us, {2.0 * rows * V * 2 / ms / 1e6:.0f} GB/s algorithmic")
+    elif a.op == "adamw":
+        sizes = [32000 * 1024] + [1024 * 1024, 2048 * 1024, 2048 * 1024, 1024 * 2048] * 8
+        ps = [h(n) * 0.02 for n in sizes]
+        gs = [h(n) for n in sizes]
+        sts = [optim.AdamWState.for_parameter(p) for p in ps]
+        ws = optim.AdamWWorkspace()
+        ent = [optim.AdamWBatchEntry(p, g, s) for p, g, s in zip(ps, gs, sts)]
+        o = optim.AdamWOptions(3e-4, 0.9, 0.95, 1e-8, 0.1, 1024.0, 1.0)
+        ms = _run(lambda: optim.adamw_step_many_async(ent, o, ws), a.iters)
+        n = sum(sizes)
+        print(f"adamw {n / 1e6:.1f}M params: {ms * 1e3:.1f} us, {30.0 * n / ms / 1e6:.0f} GB/s algorithmic (2+28 B/param)")
+    else:
+        raise SystemExit(f"unknown op {a.op}")
+
+
+if __name__ == "__main__":
+    main()
