@@ -241,7 +241,7 @@ def run_ours(args) -> None:
             if peak is None:
                 peak, which = 1400.0, "fallback (1.4 PFLOP/s sustained)"
             line["roofline"] = {"bound": "tensor", "achieved": gemm["tflops"], "peak": peak, "unit": "TFLOP/s",
-                                "frac": gemm["tflops"] / peak, "traffic": None, "kernel": "gemm_tcgen05_kernel",
+                                "frac": gemm["tflops"] / peak, "traffic": None, "kernel": "gemm_tcgen05_persistent_kernel",
                                 "launches_per_step": gemm["launches"], "ms_per_step_in_kernel": gemm["ms"],
                                 "share_of_step": gemm["ms"] / ms_step, "peak_source": which,
                                 "model_flops_per_step": gemm["model_flops"], "model_tflops": gemm["model_flops"] / ms_step / 1e9}

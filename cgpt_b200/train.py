@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import torch
 
+from . import dp
 from . import model as M
 from . import optim as O
 
@@ -47,9 +48,7 @@ class TrainStep:
     # ------------------------------------------------------------------------------------------ pieces
     def _make_buckets(self, bucket_bytes: int):
         """Contiguous slices of the flat gradient buffer of about bucket_bytes each, in backward order."""
-        flat = self.storage.flat_gradients
-        per = max(1, bucket_bytes // flat.element_size())
-        return [flat[i:i + per] for i in range(0, flat.numel(), per)]
+        return dp.make_buckets(self.storage.flat_gradients, bucket_bytes)
 
     def upload_batch(self, host_ids: torch.Tensor, host_targets: torch.Tensor) -> None:
         """Host (pinned) -> device copy of the step's token ids and targets on the step's stream."""
@@ -63,7 +62,7 @@ class TrainStep:
         k1 = M.transformer_model_forward(None, self.token_ids, self.batch, self.seq, st, ws, self.cos, self.sin, None,
                                          None, o, scratch=bw)
         M.cut_cross_entropy_forward_backward(self.loss, bw.grad_normalized, st.g_lm_head, ws.normalized, st.lm_head,
-                                             self.targets, self.rows, None, self.loss_scale / self.world,
+                                             self.targets, self.rows, None, dp.gradient_scale(self.loss_scale, self.world),
                                              chunk_rows=self.cce_chunk_rows)
         k2 = M.transformer_model_backward(None, self.token_ids, self.batch, self.seq, st, ws, bw, self.cos, self.sin,
                                           None, None, o)
@@ -72,9 +71,7 @@ class TrainStep:
     def _allreduce_gradients(self) -> None:
         if self.world == 1:
             return
-        import torch.distributed as dist
-        for bucket in self._buckets:
-            dist.all_reduce(bucket, op=dist.ReduceOp.SUM, group=self.pg)
+        dp.allreduce_buckets(self._buckets, group=self.pg)
 
     def step(self, learning_rate: float | None = None) -> None:
         """One optimizer step on the batch currently in token_ids/targets. Asynchronous."""
