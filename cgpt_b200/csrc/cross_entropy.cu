@@ -40,7 +40,8 @@ __device__ __forceinline__ float block_sum_512(float v, float* red) {
     return r;
 }
 
-template <typename T, bool STAGED>
+// VEC = elements moved per access (16 bytes when the row pitch and pointers allow it, else 1).
+template <typename T, bool STAGED, int VEC>
 __global__ void __launch_bounds__(kCeThreads)
 cross_entropy_kernel(float* __restrict__ row_loss, T* grad, const T* logits,
                      const std::uint32_t* __restrict__ targets, long long rows, int vocab, float inv_rows,
@@ -48,18 +49,29 @@ cross_entropy_kernel(float* __restrict__ row_loss, T* grad, const T* logits,
     extern __shared__ __align__(16) unsigned char ce_smem[];
     __shared__ float red[kCeWarps];
     T* staged = reinterpret_cast<T*>(ce_smem);
+    const int chunks = vocab / VEC;   // VEC > 1 only when vocab % VEC == 0
     for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
         const T* src = logits + row * vocab;
         float local_max = -CUDART_INF_F;
-        for (int c = threadIdx.x; c < vocab; c += kCeThreads) {
-            const T raw = src[c];
-            if (STAGED) staged[c] = raw;
-            local_max = fmaxf(local_max, to_f32<T>(raw));
+        for (int c = threadIdx.x; c < chunks; c += kCeThreads) {
+            float v[VEC];
+            load_vec_stream<T, VEC>(v, src + c * VEC);
+            if (STAGED) {
+                using Raw = typename RawVec<sizeof(T) * VEC>::type;
+                *reinterpret_cast<Raw*>(staged + c * VEC) = *reinterpret_cast<const Raw*>(src + c * VEC);
+            }
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) local_max = fmaxf(local_max, v[i]);
         }
         const float maximum = block_max_512(local_max, red);  // also orders the staging writes
         const T* cached = STAGED ? staged : src;
         float local_sum = 0.f;
-        for (int c = threadIdx.x; c < vocab; c += kCeThreads) local_sum += __expf(to_f32<T>(cached[c]) - maximum);
+        for (int c = threadIdx.x; c < chunks; c += kCeThreads) {
+            float v[VEC];
+            load_vec<T, VEC>(v, cached + c * VEC);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) local_sum += __expf(v[i] - maximum);
+        }
         const float denominator = block_sum_512(local_sum, red);
         const float inv_denominator = __frcp_rn(denominator);
         const std::uint32_t target = targets[row];
@@ -69,10 +81,17 @@ cross_entropy_kernel(float* __restrict__ row_loss, T* grad, const T* logits,
         }
         if (grad != nullptr) {
             T* dst = grad + row * vocab;
-            for (int c = threadIdx.x; c < vocab; c += kCeThreads) {
-                float v = __expf(to_f32<T>(cached[c]) - maximum) * inv_denominator;
-                if (valid && static_cast<std::uint32_t>(c) == target) v -= 1.0f;
-                dst[c] = from_f32<T>(v * inv_rows * gradient_scale);
+            const float out_scale = inv_rows * gradient_scale;
+            for (int c = threadIdx.x; c < chunks; c += kCeThreads) {
+                float v[VEC];
+                load_vec<T, VEC>(v, cached + c * VEC);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) {
+                    float p = __expf(v[i] - maximum) * inv_denominator;
+                    if (valid && static_cast<std::uint32_t>(c * VEC + i) == target) p -= 1.0f;
+                    v[i] = p * out_scale;
+                }
+                store_vec<T, VEC>(dst + c * VEC, v);
             }
         }
         __syncthreads();  // staged row is reused by the next iteration
@@ -112,29 +131,39 @@ using namespace cgpt;
 namespace cgpt {
 // Per-row losses (already divided by total_rows) and, when grad != nullptr, the scaled gradient for
 // `rows` rows. grad may alias logits (every thread rewrites exactly the elements it read).
+namespace {
+template <typename T, bool STAGED, int VEC>
+int ce_launch(float* row_loss, void* grad, const void* logits, const std::uint32_t* targets, long long rows, long long vocab,
+              float inv_total_rows, float gradient_scale, unsigned grid, std::size_t smem, cudaStream_t s) {
+    if (STAGED) {
+        static bool attr_done = false;
+        if (!attr_done) {
+            CGPT_CUDA_TRY(cudaFuncSetAttribute(cross_entropy_kernel<T, STAGED, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               200 * 1024));
+            attr_done = true;
+        }
+    }
+    cross_entropy_kernel<T, STAGED, VEC><<<grid, kCeThreads, smem, s>>>(row_loss, static_cast<T*>(grad), static_cast<const T*>(logits),
+                                                                        targets, rows, static_cast<int>(vocab), inv_total_rows,
+                                                                        gradient_scale);
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+    return CGPT_OK;
+}
+}  // namespace
+
 int cross_entropy_rows(float* row_loss, void* grad, const void* logits, const std::uint32_t* targets, long long rows,
                        long long vocab, float inv_total_rows, float gradient_scale, int dtype, cudaStream_t s) {
     const std::size_t row_bytes = static_cast<std::size_t>(vocab) * dtype_size(dtype);
     const bool staged = row_bytes <= 200 * 1024;
     const unsigned grid = static_cast<unsigned>(rows < kNumSMs * 4ll ? rows : kNumSMs * 4ll);
     CGPT_DISPATCH_DTYPE(dtype, T, {
-        if (staged) {
-            static bool attr_done = false;
-            if (!attr_done) {
-                CGPT_CUDA_TRY(cudaFuncSetAttribute(cross_entropy_kernel<T, true>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-                attr_done = true;
-            }
-            cross_entropy_kernel<T, true><<<grid, kCeThreads, row_bytes, s>>>(
-                row_loss, static_cast<T*>(grad), static_cast<const T*>(logits), targets, rows, static_cast<int>(vocab),
-                inv_total_rows, gradient_scale);
-        } else {
-            cross_entropy_kernel<T, false><<<grid, kCeThreads, 0, s>>>(
-                row_loss, static_cast<T*>(grad), static_cast<const T*>(logits), targets, rows, static_cast<int>(vocab),
-                inv_total_rows, gradient_scale);
-        }
-        count_launch();
-        CGPT_LAUNCH_CHECK();
+        constexpr int V = 16 / sizeof(T);
+        const bool vec = vocab % V == 0 && aligned16(logits) && aligned16(grad);
+        if (staged && vec) return ce_launch<T, true, V>(row_loss, grad, logits, targets, rows, vocab, inv_total_rows, gradient_scale, grid, row_bytes, s);
+        if (staged) return ce_launch<T, true, 1>(row_loss, grad, logits, targets, rows, vocab, inv_total_rows, gradient_scale, grid, row_bytes, s);
+        if (vec) return ce_launch<T, false, V>(row_loss, grad, logits, targets, rows, vocab, inv_total_rows, gradient_scale, grid, 0, s);
+        return ce_launch<T, false, 1>(row_loss, grad, logits, targets, rows, vocab, inv_total_rows, gradient_scale, grid, 0, s);
     });
     return CGPT_OK;
 }

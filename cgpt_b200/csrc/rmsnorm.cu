@@ -13,6 +13,7 @@
 // partials go to a [grid, hidden] fp32 scratch and a second, tiny kernel sums them in a fixed order
 // (deterministic, no atomics). Algorithmic HBM bytes per row: 3 * hidden * sizeof(T)
 // (+ hidden * sizeof(T) per residual operand).
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -230,6 +231,17 @@ struct Plan {
     int vec, cpt, wpr;
 };
 
+// 16-byte chunks a thread should hold before a row is spread over more warps (CGPT_B200_RMS_CPT = 1, 2 or 4 overrides).
+// More chunks per thread = more loads in flight per thread but more registers (fewer resident CTAs).
+inline int chunks_per_thread_target() {
+    static const int v = [] {
+        const char* e = std::getenv("CGPT_B200_RMS_CPT");
+        const int x = e ? std::atoi(e) : 2;
+        return (x == 1 || x == 2 || x == 4) ? x : 2;
+    }();
+    return v;
+}
+
 // Chooses vector width, chunks per thread and warps per row. Returns false if hidden is too large
 // for the register-cached layout.
 template <typename T>
@@ -238,8 +250,10 @@ bool make_plan(std::size_t hidden, bool all_aligned16, Plan* plan) {
     int vec = (all_aligned16 && hidden % kMaxVec == 0) ? kMaxVec : 1;
     if (vec == 8 && hidden <= 128 && hidden % 4 == 0) vec = 4;  // keep all 32 lanes busy on head_dim rows
     const std::size_t chunks = (hidden + vec - 1) / vec;
+    // Prefer up to four 16-byte chunks per thread before spreading a row over more warps: a row owned by one
+    // warp needs no block-level synchronisation and keeps more loads in flight per thread.
     int wpr = 1;
-    while (wpr < kWarps && chunks > static_cast<std::size_t>(wpr) * 32) wpr *= 2;
+    while (wpr < kWarps && chunks > static_cast<std::size_t>(wpr) * 32 * chunks_per_thread_target()) wpr *= 2;
     const std::size_t per_thread = (chunks + wpr * 32 - 1) / (wpr * 32);
     int cpt = 1;
     while (cpt < static_cast<int>(per_thread)) cpt *= 2;
