@@ -110,6 +110,8 @@ SIGNATURES = {
     "cgpt_rmsnorm_forward": (_i, [_vp, _vp, _vp, _sz, _sz, _f, _i, _vp]),
     "cgpt_rmsnorm_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _f, _i, _vp]),
     "cgpt_rmsnorm_backward_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _f, _i, _vp]),
+    "cgpt_qknorm_rope_forward": (_i, [_vp] * 8 + [_sz] * 8 + [_f, _i, _vp]),
+    "cgpt_qknorm_rope_backward": (_i, [_vp] * 12 + [_sz] * 8 + [_f, _i, _vp]),
     "cgpt_rope_forward": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _i, _vp]),
     "cgpt_rope_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _i, _vp]),
     "cgpt_swiglu_forward": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),

@@ -109,10 +109,18 @@ extern "C" int cgpt_block_forward(void* out, const void* in, const cgpt_block_pa
     CGPT_TRY(cgpt_linear_forward(sv->query_pre_norm, sv->norm, w->q_projection, m.rows, m.d, m.qdim, dt, stream));
     CGPT_TRY(cgpt_linear_forward(sv->key_pre_norm, sv->norm, w->k_projection, m.rows, m.d, m.kvdim, dt, stream));
     CGPT_TRY(cgpt_linear_forward(sv->value, sv->norm, w->v_projection, m.rows, m.d, m.kvdim, dt, stream));
-    CGPT_TRY(cgpt_rmsnorm_forward(sv->query, sv->query_pre_norm, w->q_norm, m.rows * m.hq, m.hd, eps, dt, stream));
-    CGPT_TRY(cgpt_rmsnorm_forward(sv->key, sv->key_pre_norm, w->k_norm, m.rows * m.hkv, m.hd, eps, dt, stream));
-    CGPT_TRY(cgpt_rope_forward(sv->query, sv->key, cos_table, sin_table, batch, seq, m.hq, m.hkv, m.hd, cfg->rotary_dim,
-                               position_offset, cfg->max_seq, dt, stream));
+    {   // per-head QK-norm then RoPE: one fused pass when the shape allows it, else the three separate ops
+        int rc = cgpt_qknorm_rope_forward(sv->query, sv->key, sv->query_pre_norm, sv->key_pre_norm, w->q_norm, w->k_norm,
+                                          cos_table, sin_table, batch, seq, m.hq, m.hkv, m.hd, cfg->rotary_dim,
+                                          position_offset, cfg->max_seq, eps, dt, stream);
+        if (rc == CGPT_ERR_UNSUPPORTED) {
+            CGPT_TRY(cgpt_rmsnorm_forward(sv->query, sv->query_pre_norm, w->q_norm, m.rows * m.hq, m.hd, eps, dt, stream));
+            CGPT_TRY(cgpt_rmsnorm_forward(sv->key, sv->key_pre_norm, w->k_norm, m.rows * m.hkv, m.hd, eps, dt, stream));
+            rc = cgpt_rope_forward(sv->query, sv->key, cos_table, sin_table, batch, seq, m.hq, m.hkv, m.hd, cfg->rotary_dim,
+                                   position_offset, cfg->max_seq, dt, stream);
+        }
+        CGPT_TRY(rc);
+    }
     CGPT_TRY(cgpt_attention_forward(sv->attention_output, sv->attention_logsumexp, sv->query, sv->key, sv->value, batch,
                                     seq, seq, m.hq, m.hkv, m.hd, 0.0f, 1, position_offset, dt, 0, stream));
     CGPT_TRY(cgpt_linear_forward(ws.attn_proj, sv->attention_output, w->o_projection, m.rows, m.qdim, m.d, dt, stream));
@@ -152,12 +160,20 @@ extern "C" int cgpt_block_backward(void* grad_in, const void* grad_out, const vo
     CGPT_TRY(cgpt_attention_backward(ws.dq, ws.dk, ws.dv, ws.d_attn_out, sv->attention_output, sv->attention_logsumexp,
                                      sv->query, sv->key, sv->value, batch, seq, seq, m.hq, m.hkv, m.hd, 0.0f, 1,
                                      position_offset, 0, dt, 0, stream));
-    CGPT_TRY(cgpt_rope_backward(ws.dq, ws.dk, ws.dq, ws.dk, cos_table, sin_table, batch, seq, m.hq, m.hkv, m.hd,
-                                cfg->rotary_dim, position_offset, cfg->max_seq, dt, stream));
-    CGPT_TRY(cgpt_rmsnorm_backward(ws.dq_pre, g->q_norm, ws.dq, sv->query_pre_norm, w->q_norm, nullptr, nullptr,
-                                   m.rows * m.hq, m.hd, eps, dt, stream));
-    CGPT_TRY(cgpt_rmsnorm_backward(ws.dk_pre, g->k_norm, ws.dk, sv->key_pre_norm, w->k_norm, nullptr, nullptr,
-                                   m.rows * m.hkv, m.hd, eps, dt, stream));
+    {   // inverse RoPE then QK-norm backward: fused when possible
+        int rc = cgpt_qknorm_rope_backward(ws.dq_pre, ws.dk_pre, g->q_norm, g->k_norm, ws.dq, ws.dk, sv->query_pre_norm,
+                                           sv->key_pre_norm, w->q_norm, w->k_norm, cos_table, sin_table, batch, seq, m.hq,
+                                           m.hkv, m.hd, cfg->rotary_dim, position_offset, cfg->max_seq, eps, dt, stream);
+        if (rc == CGPT_ERR_UNSUPPORTED) {
+            CGPT_TRY(cgpt_rope_backward(ws.dq, ws.dk, ws.dq, ws.dk, cos_table, sin_table, batch, seq, m.hq, m.hkv, m.hd,
+                                        cfg->rotary_dim, position_offset, cfg->max_seq, dt, stream));
+            CGPT_TRY(cgpt_rmsnorm_backward(ws.dq_pre, g->q_norm, ws.dq, sv->query_pre_norm, w->q_norm, nullptr, nullptr,
+                                           m.rows * m.hq, m.hd, eps, dt, stream));
+            rc = cgpt_rmsnorm_backward(ws.dk_pre, g->k_norm, ws.dk, sv->key_pre_norm, w->k_norm, nullptr, nullptr,
+                                       m.rows * m.hkv, m.hd, eps, dt, stream);
+        }
+        CGPT_TRY(rc);
+    }
     // the attention-norm output was overwritten by the FFN norm in the forward: recompute it (:725)
     CGPT_TRY(cgpt_rmsnorm_forward(ws.norm_a, in, w->attention_norm, m.rows, m.d, eps, dt, stream));
     CGPT_TRY(cgpt_linear_backward(ws.d_attn_norm_in, g->q_projection, nullptr, ws.dq_pre, ws.norm_a, w->q_projection,

@@ -236,8 +236,8 @@ struct Plan {
 inline int chunks_per_thread_target() {
     static const int v = [] {
         const char* e = std::getenv("CGPT_B200_RMS_CPT");
-        const int x = e ? std::atoi(e) : 2;
-        return (x == 1 || x == 2 || x == 4) ? x : 2;
+        const int x = e ? std::atoi(e) : 1;
+        return (x == 1 || x == 2 || x == 4) ? x : 1;
     }();
     return v;
 }

@@ -162,6 +162,22 @@ int cgpt_rope_backward(void* dq, void* dk, const void* dq_rot, const void* dk_ro
                        size_t q_heads, size_t kv_heads, size_t head_dim, size_t rotary_dim,
                        size_t position_offset, size_t max_seq, int dtype, cgpt_stream_t stream);
 
+/* Fused per-head QK-RMSNorm + RoPE: one pass instead of the reference's rmsnorm_forward(q), rmsnorm_forward(k),
+ * rope_forward sequence (src/core/transformer_block.cu:496-521) and, backward, rope_backward, rmsnorm_backward(q),
+ * rmsnorm_backward(k) (:705-720). q_pre/k_pre are the projections before the norm ([batch, seq, heads, head_dim]),
+ * q_norm/k_norm the [head_dim] weights; rounding points are the reference's (the normalised value / the un-rotated
+ * gradient are rounded to the storage dtype between the two stages). 16-bit dtypes, head_dim a power of two in
+ * [8, 256], rotary_dim a multiple of 8; otherwise CGPT_ERR_UNSUPPORTED (callers then use the separate ops). */
+int cgpt_qknorm_rope_forward(void* q, void* k, const void* q_pre, const void* k_pre, const void* q_norm,
+                             const void* k_norm, const void* cos_table, const void* sin_table, size_t batch, size_t seq,
+                             size_t q_heads, size_t kv_heads, size_t head_dim, size_t rotary_dim,
+                             size_t position_offset, size_t max_seq, float epsilon, int dtype, cgpt_stream_t stream);
+int cgpt_qknorm_rope_backward(void* dq_pre, void* dk_pre, void* dq_norm, void* dk_norm, const void* dq_rot,
+                              const void* dk_rot, const void* q_pre, const void* k_pre, const void* q_norm,
+                              const void* k_norm, const void* cos_table, const void* sin_table, size_t batch,
+                              size_t seq, size_t q_heads, size_t kv_heads, size_t head_dim, size_t rotary_dim,
+                              size_t position_offset, size_t max_seq, float epsilon, int dtype, cgpt_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------
  * SwiGLU  y = silu(gate) * up.
  * Replaces swiglu_forward (reference include/ops/swiglu.h) and swiglu_backward
