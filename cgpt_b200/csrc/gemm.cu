@@ -76,13 +76,13 @@ template <int BN> struct GemmCfg {
     static constexpr int kABytes = BM * BK * 2;
     static constexpr int kBBytes = BN * BK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + 2 * BM * 128 /*store staging*/;
 };
 
 // Device status word shared by the contraction kernels: non-zero means a bounded wait ran out.
 __device__ unsigned int g_gemm_status = 0;
 
-enum : int { kEpiStore = 0, kEpiAccumulate = 1, kEpiPartial = 2 };
+enum : int { kEpiStore = 0, kEpiAccumulate = 1, kEpiPartial = 2, kEpiNone = 3, kEpiStoreTma = 4 };
 
 // Optional timing of the tensor-core GEMM launches (eager mode only, never during stream capture):
 // a CUDA event pair around every gemm_tcgen05_kernel launch plus its algorithmic FLOPs.
@@ -399,7 +399,11 @@ int launch_tc(T* C, const T* A, const T* B, int M, int N, int K, int accumulate,
         CGPT_CUDA_TRY(cudaFuncSetAttribute(pkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         attr_done = true;
     }
-    const int epi = splits > 1 ? kEpiPartial : (accumulate ? kEpiAccumulate : kEpiStore);
+    int epi = splits > 1 ? kEpiPartial : (accumulate ? kEpiAccumulate : kEpiStore);
+    {   // diagnosis only: CGPT_B200_GEMM_NOSTORE=1 drains the accumulator but skips the global stores
+        static const bool nostore = [] { const char* e = std::getenv("CGPT_B200_GEMM_NOSTORE"); return e && e[0] == '1'; }();
+        if (nostore) epi = 3;
+    }
     const bool timed = g_timing.enabled && g_timing.used + 2 <= g_timing.events.size();
     if (timed) CGPT_CUDA_TRY(cudaEventRecord(g_timing.events[g_timing.used], s));
     if (use_v1_gemm()) {
@@ -408,7 +412,16 @@ int launch_tc(T* C, const T* A, const T* B, int M, int N, int K, int accumulate,
     } else {
         const long long units = static_cast<long long>(tiles) * splits;
         const unsigned grid = static_cast<unsigned>(units < kNumSMs ? units : kNumSMs);
-        pkernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, C, partial, M, N, K, tiles_m, tiles_n, splits, kb_per_split, epi);
+        // Plain stores of 16-bit output go through shared memory and TMA (needs a 16-byte aligned C and N % 8 == 0).
+        CUtensorMap tc = ta;
+        if (epi == kEpiStore && aligned16(C) && N % 8 == 0) {
+            const std::uint64_t dims_c[2] = {static_cast<std::uint64_t>(N), static_cast<std::uint64_t>(M)};
+            const std::uint64_t st_c[1] = {static_cast<std::uint64_t>(N) * 2};
+            const std::uint32_t box_c[2] = {64, BM};
+            CGPT_TRY(make_tensor_map(&tc, dtype, C, 2, dims_c, st_c, box_c));
+            epi = kEpiStoreTma;
+        }
+        pkernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, tc, C, partial, M, N, K, tiles_m, tiles_n, splits, kb_per_split, epi);
     }
     count_launch();
     CGPT_LAUNCH_CHECK();

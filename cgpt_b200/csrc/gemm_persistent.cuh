@@ -11,7 +11,7 @@
 template <typename T>
 __device__ __forceinline__ void gemm_store_chunk(const std::uint32_t (&r)[32], T* __restrict__ C, float* __restrict__ partial,
                                                  int row, int col0, int M, int N, int split, int epilogue) {
-    if (row >= M || col0 >= N) return;
+    if (row >= M || col0 >= N || epilogue == 3) return;
     if (epilogue == kEpiPartial) {
         float* dst = partial + (static_cast<long long>(split) * M + row) * N + col0;
         if (col0 + 32 <= N && (N & 3) == 0) {
@@ -56,13 +56,14 @@ __device__ __forceinline__ void gemm_store_chunk(const std::uint32_t (&r)[32], T
 template <typename T, int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                               T* __restrict__ C, float* __restrict__ partial, int M, int N, int K, int tiles_m, int tiles_n,
+                               const __grid_constant__ CUtensorMap tmap_c, T* __restrict__ C, float* __restrict__ partial, int M, int N, int K, int tiles_m, int tiles_n,
                                int splits, int kb_per_split, int epilogue) {
     using Cfg = GemmCfg<BN>;
     extern __shared__ unsigned char gemm_smem_raw[];
     const std::uint32_t raw = smem_u32(gemm_smem_raw);
     unsigned char* smem = gemm_smem_raw + ((1024u - (raw & 1023u)) & 1023u);
-    std::uint64_t* bars = reinterpret_cast<std::uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+    unsigned char* staging = smem + Cfg::kStages * Cfg::kStageBytes;   // 2 x [128 rows][128 B], 1024-byte aligned
+    std::uint64_t* bars = reinterpret_cast<std::uint64_t*>(staging + 2 * BM * 128);
     std::uint64_t* full = bars;
     std::uint64_t* empty = bars + Cfg::kStages;
     std::uint64_t* acc_full = bars + 2 * Cfg::kStages;       // [2]
@@ -160,6 +161,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const
     } else {
         const int quarter = warp & 3;
         int j = 0;
+        int stage_buf = 0;
         for (int u = blockIdx.x; u < units; u += gridDim.x, ++j) {
             const int split = u / tiles, t = u % tiles;
             const int tile_m = t / tiles_n, tile_n = t % tiles_n;
@@ -170,12 +172,45 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const
             tc_fence_after_sync();
             const int row = tile_m * BM + quarter * 32 + lane;
             const std::uint32_t tmem_acc = tmem_base + buf * BN + (static_cast<std::uint32_t>(quarter * 32) << 16);
+            if (epilogue == kEpiStoreTma) {
+                // Stage 64 columns of the tile as 16-bit values in 128B-swizzled shared memory and let TMA write
+                // them out as full lines (a direct store would give every lane a different row: 16-byte pieces).
+                const int et = threadIdx.x - 64;              // 0..127 within the epilogue warps
+                const int trow = quarter * 32 + lane;         // row inside the tile
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 64) {
-                std::uint32_t r0[32], r1[32];
-                tmem_ld_32x32_x2(tmem_acc + c0, r0, tmem_acc + c0 + 32, r1);
-                gemm_store_chunk<T>(r0, C, partial, row, tile_n * BN + c0, M, N, split, epilogue);
-                gemm_store_chunk<T>(r1, C, partial, row, tile_n * BN + c0 + 32, M, N, split, epilogue);
+                for (int c0 = 0; c0 < BN; c0 += 64) {
+                    unsigned char* buf_s = staging + stage_buf * (BM * 128);
+                    if (et == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // buffer used 2 stores ago is free
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    std::uint32_t r0[32], r1[32];
+                    tmem_ld_32x32_x2(tmem_acc + c0, r0, tmem_acc + c0 + 32, r1);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const std::uint32_t* src = j < 4 ? &r0[8 * j] : &r1[8 * (j - 4)];
+                        float v[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(src[e]);
+                        store_vec<T, 8>(reinterpret_cast<T*>(buf_s + trow * 128 + ((j ^ (trow & 7)) << 4)), v);
+                    }
+                    fence_proxy_async_smem();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (et == 0) {
+                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                                     ::"l"(reinterpret_cast<std::uint64_t>(&tmap_c)), "r"(smem_u32(buf_s)), "r"(tile_n * BN + c0),
+                                       "r"(tile_m * BM)
+                                     : "memory");
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                    stage_buf ^= 1;
+                }
+            } else {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 64) {
+                    std::uint32_t r0[32], r1[32];
+                    tmem_ld_32x32_x2(tmem_acc + c0, r0, tmem_acc + c0 + 32, r1);
+                    gemm_store_chunk<T>(r0, C, partial, row, tile_n * BN + c0, M, N, split, epilogue);
+                    gemm_store_chunk<T>(r1, C, partial, row, tile_n * BN + c0 + 32, M, N, split, epilogue);
+                }
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -183,6 +218,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const
         }
     }
 
+    if (threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // TMA stores of this CTA are complete
     if (failed) {
         atomicExch(&g_gemm_status, 1u);
         const unsigned long long t0 = globaltimer_ns();

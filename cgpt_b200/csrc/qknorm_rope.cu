@@ -150,15 +150,25 @@ qknorm_rope_kernel(T* __restrict__ out_q, T* __restrict__ out_k, const T* __rest
     }
 }
 
+// dw[col] = sum of the per-CTA partials in a fixed order: 8 row lanes per column, then a shared-memory combine.
 template <typename T>
 __global__ void __launch_bounds__(256)
 qknorm_dw_reduce_kernel(T* __restrict__ dw_q, T* __restrict__ dw_k, const float* __restrict__ partial, int parts, int head_dim) {
-    const int col = blockIdx.x * 256 + threadIdx.x;      // 0 .. 2*head_dim
-    if (col >= 2 * head_dim) return;
+    __shared__ float tile[8][33];
+    const int col = blockIdx.x * 32 + (threadIdx.x & 31);      // 0 .. 2*head_dim
+    const int rl = threadIdx.x >> 5;
     float acc = 0.f;
-    for (int p = 0; p < parts; ++p) acc += partial[static_cast<long long>(p) * 2 * head_dim + col];
-    if (col < head_dim) dw_q[col] = from_f32<T>(acc);
-    else dw_k[col - head_dim] = from_f32<T>(acc);
+    if (col < 2 * head_dim)
+        for (int p = rl; p < parts; p += 8) acc += partial[static_cast<long long>(p) * 2 * head_dim + col];
+    tile[rl][threadIdx.x & 31] = acc;
+    __syncthreads();
+    if (rl == 0 && col < 2 * head_dim) {
+        float total = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) total += tile[r][threadIdx.x & 31];
+        if (col < head_dim) dw_q[col] = from_f32<T>(total);
+        else dw_k[col - head_dim] = from_f32<T>(total);
+    }
 }
 
 bool fast_path_ok(size_t head_dim, size_t rotary_dim, int dtype, std::initializer_list<const void*> ptrs) {
@@ -232,7 +242,7 @@ extern "C" int cgpt_qknorm_rope_backward(void* dq_pre, void* dk_pre, void* dq_no
     void* scratch = nullptr;
     CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(grid) * 2 * head_dim * sizeof(float), s));
     float* partial = static_cast<float*>(scratch);
-    const unsigned rgrid = static_cast<unsigned>((2 * head_dim + 255) / 256);
+    const unsigned rgrid = static_cast<unsigned>((2 * head_dim + 31) / 32);
     if (dtype == CGPT_DTYPE_F16) {
         qknorm_rope_kernel<__half, true><<<grid, kQkThreads, 0, s>>>(
             static_cast<__half*>(dq_pre), static_cast<__half*>(dk_pre), static_cast<const __half*>(dq_rot),
