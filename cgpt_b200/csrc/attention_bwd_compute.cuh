@@ -8,8 +8,9 @@ __device__ __forceinline__ bool bwd_compute(unsigned char* smem, const BwdBars& 
                                             const float* __restrict__ delta_t, T* __restrict__ out1, T* __restrict__ out2,
                                             int accumulate) {
     using L = BwdSmem<D>;
-    const int row = threadIdx.x;                       // 0..127
-    const int warp = row >> 5;
+    const int row = threadIdx.x & (kRows - 1);         // 0..127: TMEM lane; two threads (one per warpgroup) share a row
+    const int half = threadIdx.x >> 7;                 // which 32 of the tile's 64 columns this thread handles
+    const int warp = (threadIdx.x >> 5) & 3;           // lane quarter of this warp
     const std::uint32_t lane_base = static_cast<std::uint32_t>(warp * 32) << 16;
     const float scale2 = dm.scale * kLog2e;
     const int x_idx = g.x0 + row;                      // query index (dQ) or key index (dKV) of this thread
@@ -28,27 +29,30 @@ __device__ __forceinline__ bool bwd_compute(unsigned char* smem, const BwdBars& 
     }
     bool failed = false;
 
+    int ys = 0;                 // ring stage of the streaming tile = it % kYStages
+    std::uint32_t ypar = 0;     // its phase = (it / kYStages) & 1
     for (int it = 0; it < g.n_it; ++it) {
         const int s = it & 1;
         const std::uint32_t par = (it >> 1) & 1;
         int head, y0;
         bwd_stream_coords<MODE>(g, it, &head, &y0);
         // U/W buffer s was last read by the accumulating MMAs of tile it-2
-        if (!mbar_wait(&bars.stage_free[s], par ^ 1u)) failed = true;
+        if (!mbar_wait(&bars.uw_free[s], par ^ 1u)) failed = true;
         if (!failed && !mbar_wait(&bars.t_full[s], par)) failed = true;
-        if (MODE == MODE_DKV && !failed && !mbar_wait(&bars.stat_full[s], par)) failed = true;
+        if (MODE == MODE_DKV && !failed && !mbar_wait(&bars.stat_full[ys], ypar)) failed = true;
         failed = __any_sync(0xffffffffu, failed);
         if (failed) break;
+        if (threadIdx.x == 0) bwd_trace(bars, it, 3);
         tc_fence_after_sync();
-        const float* st = reinterpret_cast<const float*>(smem + L::kStats) + s * 2 * kCols;
+        const float* st = reinterpret_cast<const float*>(smem + L::kStats) + ys * 2 * kCols;
         unsigned char* u_row = smem + L::kU + s * kRows * 128 + row * 128;
         unsigned char* w_row = smem + L::kW + s * kRows * 128 + row * 128;
         // does any element of this tile need the visibility test?
         bool need_mask;
         if (MODE == MODE_DQ) need_mask = (y0 + kCols > dm.sk) || (dm.causal && y0 + kCols - 1 > dm.offset + g.x0);
         else need_mask = dm.causal && (g.x0 + kRows - 1 > dm.offset + y0);
-#pragma unroll
-        for (int c0 = 0; c0 < kCols; c0 += 32) {
+        {
+            const int c0 = half * 32;
             std::uint32_t t1[32], t2[32];
             tmem_ld_32x32_x2(tmem + s * kCols + lane_base + c0, t1, tmem + 128 + s * kCols + lane_base + c0, t2);
             std::uint32_t pu[16], pw[16];
@@ -86,6 +90,8 @@ __device__ __forceinline__ bool bwd_compute(unsigned char* smem, const BwdBars& 
         tc_fence_before_sync();
         fence_proxy_async_smem();
         mbar_arrive(&bars.w_full[s]);
+        if (threadIdx.x == 0) bwd_trace(bars, it, 4);
+        if (++ys == kYStages) { ys = 0; ypar ^= 1u; }
     }
 
     // ---- epilogue: accumulators -> global
@@ -106,7 +112,8 @@ __device__ __forceinline__ bool bwd_compute(unsigned char* smem, const BwdBars& 
         T* dst = (MODE == MODE_DKV ? (o == 0 ? out2 : out1) : out1) + dst_off;
         const std::uint32_t acc = tmem + 256 + o * D;
 #pragma unroll
-        for (int c0 = 0; c0 < D; c0 += 32) {
+        for (int cc = 0; cc < D / 2; cc += 32) {
+            const int c0 = half * (D / 2) + cc;
             std::uint32_t r[32];
             if (g.n_it > 0) {
                 tmem_ld_32x32(acc + lane_base + c0, r);

@@ -6,7 +6,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 attention_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_constant__ CUtensorMap map_x2,
                         const __grid_constant__ CUtensorMap map_y1, const __grid_constant__ CUtensorMap map_y2,
                         T* __restrict__ out1, T* __restrict__ out2, const float* __restrict__ lse2_t,
-                        const float* __restrict__ delta_t, AttnDims dm, int accumulate, unsigned int* __restrict__ status) {
+                        const float* __restrict__ delta_t, AttnDims dm, int accumulate, unsigned int* __restrict__ status,
+                        unsigned long long* trace) {
     using L = BwdSmem<D>;
     extern __shared__ unsigned char bwd_smem_raw[];
     const std::uint32_t raw = smem_u32(bwd_smem_raw);
@@ -14,13 +15,15 @@ attention_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid
     std::uint64_t* bar = reinterpret_cast<std::uint64_t*>(smem + L::kBars);
     BwdBars bars;
     bars.x_full = bar + 0;
-    bars.y_full = bar + 1;       // [2]
-    bars.stat_full = bar + 3;    // [2]
-    bars.stage_free = bar + 5;   // [2]
-    bars.t_full = bar + 7;       // [2]
-    bars.w_full = bar + 9;       // [2]
-    bars.acc_done = bar + 11;
-    std::uint32_t* tmem_slot = reinterpret_cast<std::uint32_t*>(bar + 12);
+    bars.y_full = bar + 1;                      // [kYStages]
+    bars.stat_full = bar + 1 + kYStages;        // [kYStages]
+    bars.y_free = bar + 1 + 2 * kYStages;       // [kYStages]
+    bars.uw_free = bar + 1 + 3 * kYStages;      // [2]
+    bars.t_full = bars.uw_free + 2;             // [2]
+    bars.w_full = bars.uw_free + 4;             // [2]
+    bars.acc_done = bars.uw_free + 6;
+    bars.trace = (trace != nullptr && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && blockIdx.z == gridDim.z / 2) ? trace : nullptr;
+    std::uint32_t* tmem_slot = reinterpret_cast<std::uint32_t*>(bars.acc_done + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     BwdGeom g;
@@ -52,27 +55,30 @@ attention_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid
 
     if (threadIdx.x == 0) {
         mbar_init(bars.x_full, 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < kYStages; ++s) {
             mbar_init(&bars.y_full[s], 1);
             mbar_init(&bars.stat_full[s], 32);
-            mbar_init(&bars.stage_free[s], 1);
+            mbar_init(&bars.y_free[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars.uw_free[s], 1);
             mbar_init(&bars.t_full[s], 1);
-            mbar_init(&bars.w_full[s], kRows);
+            mbar_init(&bars.w_full[s], 2 * kRows);
         }
         mbar_init(bars.acc_done, 1);
         mbar_init_fence();
         tma_prefetch_desc(&map_x1); tma_prefetch_desc(&map_x2); tma_prefetch_desc(&map_y1); tma_prefetch_desc(&map_y2);
     }
-    if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    if (warp == 9) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const std::uint32_t tmem = *tmem_slot;
 
     bool ok = true;
-    if (warp == 4) {
+    if (warp == 8) {
         if (g.n_it > 0) ok = bwd_producer<D, MODE>(smem, bars, g, dm, &map_x1, &map_x2, &map_y1, &map_y2, lse2_t, delta_t, lane);
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         if (lane == 0 && g.n_it > 0) ok = bwd_mma_issuer<T, D, MODE>(smem, bars, g, tmem);
     } else {
         ok = bwd_compute<T, D, MODE>(smem, bars, g, dm, tmem, lse2_t, delta_t, out1, out2, accumulate);
@@ -84,7 +90,7 @@ attention_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, 512);
     }
@@ -135,13 +141,16 @@ int launch_backward(void* dq, void* dk, void* dv, const void* dout, const void* 
     unsigned int* status = tc_status_device_ptr();
     if (status == nullptr) return CGPT_ERR_STATE;
     const dim3 grid_q((dm.sq + kRows - 1) / kRows, dm.hq, dm.batch);
+    // CGPT_B200_ATTN_TRACE=<device pointer of 2*64*8 uint64> records per-iteration timestamps of one CTA per kernel (diagnosis)
+    unsigned long long* trace = nullptr;
+    if (const char* e = std::getenv("CGPT_B200_ATTN_TRACE")) trace = reinterpret_cast<unsigned long long*>(std::strtoull(e, nullptr, 0));
     kq<<<grid_q, kBwdThreads, L::kBytes, s>>>(q128, do128, k64, v64, static_cast<T*>(dq), static_cast<T*>(nullptr), lse2_t, delta_t, dm,
-                                              accumulate, status);
+                                              accumulate, status, trace);
     count_launch();
     CGPT_LAUNCH_CHECK();
     const dim3 grid_kv((dm.sk + kRows - 1) / kRows, dm.hkv, dm.batch);
     kkv<<<grid_kv, kBwdThreads, L::kBytes, s>>>(k128, v128, q64, do64, static_cast<T*>(dk), static_cast<T*>(dv), lse2_t, delta_t, dm,
-                                                accumulate, status);
+                                                accumulate, status, trace ? trace + 64 * 8 : nullptr);
     count_launch();
     CGPT_LAUNCH_CHECK();
     return CGPT_OK;

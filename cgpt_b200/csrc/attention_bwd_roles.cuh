@@ -14,8 +14,13 @@ struct BwdGeom {
 };
 
 struct BwdBars {
-    std::uint64_t *x_full, *y_full, *stat_full, *stage_free, *t_full, *w_full, *acc_done;
+    std::uint64_t *x_full, *y_full, *stat_full, *y_free, *uw_free, *t_full, *w_full, *acc_done;
+    unsigned long long* trace;   // diagnosis: per-iteration timestamps of one CTA (nullptr = off)
 };
+
+__device__ __forceinline__ void bwd_trace(const BwdBars& b, int it, int slot) {
+    if (b.trace != nullptr && it < 64) b.trace[it * 8 + slot] = globaltimer_ns();
+}
 
 // Streaming tile `it` -> (head, first row of the streaming tile).
 template <int MODE>
@@ -44,9 +49,11 @@ __device__ __forceinline__ bool bwd_producer(unsigned char* smem, const BwdBars&
             tma_load_4d(smem + L::kX2 + c * kRows * 128, map_x2, bars.x_full, c * 64, xh, g.x0, g.b);
         }
     }
+    int s = 0;                  // ring stage = it % kYStages
+    std::uint32_t par = 0;      // its phase = (it / kYStages) & 1
     for (int it = 0; it < g.n_it; ++it) {
-        const int s = it & 1;
-        if (!mbar_wait(&bars.stage_free[s], ((it >> 1) & 1) ^ 1u)) return false;
+        if (!mbar_wait(&bars.y_free[s], par ^ 1u)) return false;
+        if (lane == 0) bwd_trace(bars, it, 0);
         int head, row0;
         bwd_stream_coords<MODE>(g, it, &head, &row0);
         if (lane == 0) {
@@ -71,9 +78,15 @@ __device__ __forceinline__ bool bwd_producer(unsigned char* smem, const BwdBars&
             }
             mbar_arrive(&bars.stat_full[s]);
         }
+        if (++s == kYStages) { s = 0; par ^= 1u; }
     }
     return true;
 }
+
+// The MMA-issuing thread is a single scalar instruction stream, so every instruction between two tcgen05.mma
+// counts: all shared-memory descriptors are loop-invariant per ring stage and are built once; a K step only adds
+// a constant to the 14-bit address field.
+__device__ __forceinline__ std::uint64_t desc_advance(std::uint64_t desc, std::uint32_t bytes) { return desc + (bytes >> 4); }
 
 template <typename T, int D, int MODE>
 __device__ __forceinline__ bool bwd_mma_issuer(unsigned char* smem, const BwdBars& bars, const BwdGeom& g, std::uint32_t tmem) {
@@ -81,52 +94,75 @@ __device__ __forceinline__ bool bwd_mma_issuer(unsigned char* smem, const BwdBar
     constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
     constexpr std::uint32_t idesc_t = idesc_f16(fmt, 0, 0, kRows, kCols);   // T = X Y^T: both K-major
     constexpr std::uint32_t idesc_acc = idesc_f16(fmt, 0, 1, kRows, D);     // acc += U/W (K-major) * Y (N-major)
-    const std::uint32_t x1 = smem_u32(smem + L::kX1), x2 = smem_u32(smem + L::kX2);
+    constexpr std::uint32_t kYStage16 = (2 * L::kYBytes) >> 4;              // ring stage stride in descriptor units
+    constexpr std::uint32_t kUW16 = (kRows * 128) >> 4;
     const std::uint32_t tmem_acc1 = tmem + 256, tmem_acc2 = tmem + 256 + D;
+    const std::uint64_t dx1 = smem_desc_sw128(smem_u32(smem + L::kX1), 16, 1024);
+    const std::uint64_t dx2 = smem_desc_sw128(smem_u32(smem + L::kX2), 16, 1024);
+    const std::uint32_t y_base = smem_u32(smem + L::kY);
+    const std::uint64_t dy1k = smem_desc_sw128(y_base, 16, 1024);                       // as K-major B of T1
+    const std::uint64_t dy2k = smem_desc_sw128(y_base + L::kYBytes, 16, 1024);
+    const std::uint64_t dy1n = smem_desc_sw128(y_base, kCols * 128, 1024);              // as N-major B of the accumulations
+    const std::uint64_t dy2n = smem_desc_sw128(y_base + L::kYBytes, kCols * 128, 1024);
+    const std::uint64_t du0 = smem_desc_sw128(smem_u32(smem + L::kU), 16, 1024);
+    const std::uint64_t dw0 = smem_desc_sw128(smem_u32(smem + L::kW), 16, 1024);
 
-    auto issue_t = [&](int it) -> bool {
-        const int s = it & 1;
-        if (!mbar_wait(&bars.y_full[s], (it >> 1) & 1)) return false;
+    // T1/T2 of tile `it` whose streaming pair sits in ring stage ys (phase ypar)
+    auto issue_t = [&](int it, int ys, std::uint32_t ypar) -> bool {
+        if (!mbar_wait(&bars.y_full[ys], ypar)) return false;
+        bwd_trace(bars, it, 1);
         tc_fence_after_sync();
-        const std::uint32_t y1 = smem_u32(smem + L::kY + s * 2 * L::kYBytes), y2 = y1 + L::kYBytes;
+        const int s = it & 1;
+        const std::uint32_t t1 = tmem + s * kCols, t2 = tmem + 128 + s * kCols;
+        const std::uint64_t y1 = dy1k + ys * kYStage16, y2 = dy2k + ys * kYStage16;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
             const std::uint32_t xo = (k >> 2) * (kRows * 128) + (k & 3) * 32, yo = (k >> 2) * (kCols * 128) + (k & 3) * 32;
-            mma_f16_ss(tmem + s * kCols, smem_desc_sw128(x1 + xo, 16, 1024), smem_desc_sw128(y1 + yo, 16, 1024), idesc_t, k > 0);
+            mma_f16_ss(t1, desc_advance(dx1, xo), desc_advance(y1, yo), idesc_t, k > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
             const std::uint32_t xo = (k >> 2) * (kRows * 128) + (k & 3) * 32, yo = (k >> 2) * (kCols * 128) + (k & 3) * 32;
-            mma_f16_ss(tmem + 128 + s * kCols, smem_desc_sw128(x2 + xo, 16, 1024), smem_desc_sw128(y2 + yo, 16, 1024), idesc_t, k > 0);
+            mma_f16_ss(t2, desc_advance(dx2, xo), desc_advance(y2, yo), idesc_t, k > 0 ? 1u : 0u);
         }
         tc_commit(&bars.t_full[s]);
         return true;
     };
 
     if (!mbar_wait(bars.x_full, 0)) return false;
-    if (!issue_t(0)) return false;
+    if (!issue_t(0, 0, 0u)) return false;
+    int ys = 0;                  // ring stage of tile `it`
+    std::uint32_t ypar = 0;
     for (int it = 0; it < g.n_it; ++it) {
         const int s = it & 1;
-        if (it + 1 < g.n_it && !issue_t(it + 1)) return false;
+        int ys_next = ys + 1;
+        std::uint32_t ypar_next = ypar;
+        if (ys_next == kYStages) { ys_next = 0; ypar_next ^= 1u; }
+        if (it + 1 < g.n_it && !issue_t(it + 1, ys_next, ypar_next)) return false;
         if (!mbar_wait(&bars.w_full[s], (it >> 1) & 1)) return false;
+        bwd_trace(bars, it, 2);
         tc_fence_after_sync();
-        const std::uint32_t y1 = smem_u32(smem + L::kY + s * 2 * L::kYBytes), y2 = y1 + L::kYBytes;
-        const std::uint32_t u = smem_u32(smem + L::kU + s * kRows * 128), w = smem_u32(smem + L::kW + s * kRows * 128);
+        const std::uint32_t acc = it > 0 ? 1u : 0u;
+        const std::uint64_t y1 = dy1n + ys * kYStage16, y2 = dy2n + ys * kYStage16;
+        const std::uint64_t du = du0 + s * kUW16, dw = dw0 + s * kUW16;
 #pragma unroll
         for (int k = 0; k < kCols / 16; ++k) {
-            // A: [128 rows][64] K-major, one swizzle atom wide; B: streaming tile as N-major: 16 rows of 128 B per K step,
-            // 64-column chunks of D kCols*128 bytes apart.
+            // A: [128 rows][64] K-major, one swizzle atom wide (32 B per K step); B: streaming tile as N-major:
+            // 16 rows of 128 B per K step, 64-column chunks of D kCols*128 bytes apart.
             if (MODE == MODE_DKV) {
-                mma_f16_ss(tmem_acc1, smem_desc_sw128(u + k * 32, 16, 1024), smem_desc_sw128(y2 + k * (16 * 128), kCols * 128, 1024),
-                           idesc_acc, (it > 0 || k > 0) ? 1u : 0u);                  // dV += P^T dO
-                mma_f16_ss(tmem_acc2, smem_desc_sw128(w + k * 32, 16, 1024), smem_desc_sw128(y1 + k * (16 * 128), kCols * 128, 1024),
-                           idesc_acc, (it > 0 || k > 0) ? 1u : 0u);                  // dK += dS^T Q
+                mma_f16_ss(tmem_acc1, desc_advance(du, k * 32), desc_advance(y2, k * (16 * 128)), idesc_acc,
+                           k > 0 ? 1u : acc);                                            // dV += P^T dO
+                mma_f16_ss(tmem_acc2, desc_advance(dw, k * 32), desc_advance(y1, k * (16 * 128)), idesc_acc,
+                           k > 0 ? 1u : acc);                                            // dK += dS^T Q
             } else {
-                mma_f16_ss(tmem_acc1, smem_desc_sw128(w + k * 32, 16, 1024), smem_desc_sw128(y1 + k * (16 * 128), kCols * 128, 1024),
-                           idesc_acc, (it > 0 || k > 0) ? 1u : 0u);                  // dQ += dS K
+                mma_f16_ss(tmem_acc1, desc_advance(dw, k * 32), desc_advance(y1, k * (16 * 128)), idesc_acc,
+                           k > 0 ? 1u : acc);                                            // dQ += dS K
             }
         }
-        tc_commit(&bars.stage_free[s]);
+        tc_commit(&bars.y_free[ys]);     // the streaming tile's ring stage may be refilled ...
+        tc_commit(&bars.uw_free[s]);     // ... and the U/W buffer rewritten once these MMAs have read them
+        ys = ys_next;
+        ypar = ypar_next;
     }
     tc_commit(bars.acc_done);
     return true;

@@ -15,13 +15,14 @@
 // storage dtype before the second products (:1336-1343, :1567-1586); everything else is fp32.
 //
 // Both kernels are one template. A "stationary" pair of [128, D] tiles (X1, X2) stays in shared memory,
-// a "streaming" pair of [64, D] tiles (Y1, Y2) runs through a 2-stage TMA ring:
+// a "streaming" pair of [64, D] tiles (Y1, Y2) runs through a 3-stage TMA ring:
 //     T1 = X1 Y1^T, T2 = X2 Y2^T            two 128x64 fp32 tiles in TMEM (double-buffered)
 //     threads (one per TMEM lane = stationary row) turn T1/T2 into 16-bit tiles U (P^T) and W (dS or dS^T)
 //     in 128B-swizzled shared memory (K-major A operands)
 //     acc1 += U Y2, acc2 += W Y1 (dKV)   or   acc1 += W Y1 (dQ)      accumulators stay in TMEM
 // The streaming tiles serve twice from the same bytes: as K-major B operands of T1/T2 and as N-major
 // ("MN-major") B operands of the accumulating products.
+#include <cstdlib>
 #include <type_traits>
 
 #include "attention.h"
@@ -38,7 +39,8 @@ using namespace sm100;
 
 constexpr int kRows = 128;   // stationary tile rows = TMEM lanes
 constexpr int kCols = 64;    // streaming tile rows = columns of T1/T2
-constexpr int kBwdThreads = 192;
+constexpr int kYStages = 3;  // depth of the streaming-tile ring: the TMA latency of tile it+1 hides behind tiles it-1 and it
+constexpr int kBwdThreads = 320;   // warps 0-7 compute (two warpgroups, each half of the tile's columns), 8 TMA, 9 MMA
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int MODE_DQ = 0, MODE_DKV = 1;
 
@@ -48,12 +50,13 @@ template <int D> struct BwdSmem {
     static constexpr int kYBytes = kChunks * kCols * 128;     // one streaming tile
     static constexpr int kX1 = 0;
     static constexpr int kX2 = kX1 + kXBytes;
-    static constexpr int kY = kX2 + kXBytes;                  // [2 stages][Y1 | Y2]
-    static constexpr int kU = kY + 4 * kYBytes;               // [2] x [128 rows][128 B]
+    static constexpr int kY = kX2 + kXBytes;                  // [kYStages][Y1 | Y2]
+    static constexpr int kU = kY + kYStages * 2 * kYBytes;    // [2] x [128 rows][128 B]
     static constexpr int kW = kU + 2 * kRows * 128;           // [2] x [128 rows][128 B]
-    static constexpr int kStats = kW + 2 * kRows * 128;       // [2 stages][2][64] fp32
-    static constexpr int kBars = kStats + 2 * 2 * kCols * 4;
+    static constexpr int kStats = kW + 2 * kRows * 128;       // [kYStages][2][64] fp32
+    static constexpr int kBars = kStats + kYStages * 2 * kCols * 4;
     static constexpr int kBytes = kBars + 256 + 1024;
+    static_assert(kBytes <= 232448, "attention backward shared memory exceeds the 227 KB a CTA may use");
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
