@@ -115,7 +115,10 @@ int launch_backward(void* dq, void* dk, void* dv, const void* dout, const void* 
     CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(qrows) * 2 * sizeof(float), s));
     float* delta_t = static_cast<float*>(scratch);
     float* lse2_t = delta_t + qrows;
-    attention_bwd_prep_kernel<T><<<static_cast<unsigned>((qrows + 3) / 4), 128, 0, s>>>(
+    const long long prep_rows_per_cta = 8LL * (32 / (D / 8)) * kPrepUnroll;
+    const long long prep_need = (qrows + prep_rows_per_cta - 1) / prep_rows_per_cta;
+    const long long prep_cap = static_cast<long long>(kNumSMs) * 8;
+    attention_bwd_prep_kernel<T><<<static_cast<unsigned>(prep_need < prep_cap ? prep_need : prep_cap), 256, 0, s>>>(
         delta_t, lse2_t, static_cast<const T*>(dout), static_cast<const T*>(out), lse, dm.batch, dm.sq, dm.hq, D);
     count_launch();
     CGPT_LAUNCH_CHECK();

@@ -75,33 +75,52 @@ template <> __device__ __forceinline__ std::uint32_t pack2<__nv_bfloat16>(float 
     return *reinterpret_cast<std::uint32_t*>(&h);
 }
 
-// delta and lse2 in [batch, heads, seq] order. One warp per (b, q, h) row of dO / O.
+// delta and lse2 in [batch, heads, seq] order. D/8 lanes own one (b, q, h) row of dO / O (one 16-byte chunk each), so
+// a warp covers 32/(D/8) rows per group and kPrepUnroll groups per trip, all of whose loads are issued before the
+// first use (memory-bound: 2 * D * 2 bytes per row).
+constexpr int kPrepUnroll = 4;
+
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 attention_bwd_prep_kernel(float* __restrict__ delta_t, float* __restrict__ lse2_t, const T* __restrict__ dout,
                           const T* __restrict__ out, const float* __restrict__ lse, int batch, int sq, int hq, int d) {
-    const long long row = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+    const int lpr = d / 8;                         // lanes per row (8 or 16)
+    const int rows_per_group = 32 / lpr;
     const int lane = threadIdx.x & 31;
+    const int sub = lane / lpr, l = lane % lpr;
     const long long rows = static_cast<long long>(batch) * sq * hq;
-    if (row >= rows) return;
-    float s = 0.f;
-    const T* a = dout + row * d;
-    const T* o = out + row * d;
-    for (int c = lane * 8; c < d; c += 256) {
-        float x[8], y[8];
-        load_vec<T, 8>(x, a + c);
-        load_vec<T, 8>(y, o + c);
+    const long long warp_id = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    const long long warps_total = static_cast<long long>(gridDim.x) * 8;
+    const long long per_trip = static_cast<long long>(rows_per_group) * kPrepUnroll;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (long long base = warp_id * per_trip; base < rows; base += warps_total * per_trip) {
+        uint4 a[kPrepUnroll], o[kPrepUnroll];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) s = fmaf(x[e], y[e], s);
-    }
-    s = warp_sum(s);
-    if (lane == 0) {
-        const int h = static_cast<int>(row % hq);
-        const int q = static_cast<int>((row / hq) % sq);
-        const long long b = row / (static_cast<long long>(hq) * sq);
-        const long long t = (b * hq + h) * sq + q;
-        delta_t[t] = s;
-        lse2_t[t] = lse[row] * kLog2e;
+        for (int u = 0; u < kPrepUnroll; ++u) {
+            const long long row = base + u * rows_per_group + sub;
+            a[u] = row < rows ? __ldcs(reinterpret_cast<const uint4*>(dout + row * d + l * 8)) : zero;
+            o[u] = row < rows ? __ldg(reinterpret_cast<const uint4*>(out + row * d + l * 8)) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < kPrepUnroll; ++u) {
+            const long long row = base + u * rows_per_group + sub;
+            Pack<T, 8> pa, po;
+            *reinterpret_cast<uint4*>(&pa) = a[u];
+            *reinterpret_cast<uint4*>(&po) = o[u];
+            float s = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) s = fmaf(to_f32<T>(pa.v[e]), to_f32<T>(po.v[e]), s);
+            for (int off = lpr >> 1; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+            if (l == 0 && row < rows) {
+                const int h = static_cast<int>(row % hq);
+                const long long bq = row / hq;
+                const int q = static_cast<int>(bq % sq);
+                const long long b = bq / sq;
+                const long long t = (b * hq + h) * sq + q;
+                delta_t[t] = s;
+                lse2_t[t] = lse[row] * kLog2e;
+            }
+        }
     }
 }
 

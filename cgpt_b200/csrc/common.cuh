@@ -109,12 +109,39 @@ __device__ __forceinline__ void load_vec_stream(float (&out)[N], const T* __rest
     for (int i = 0; i < N; ++i) out[i] = to_f32<T>(pk.v[i]);
 }
 
+// Round-to-nearest conversion of N floats into a Pack. 16-bit types convert two values per instruction
+// (cvt.rn.f16x2.f32 / cvt.rn.bf16x2.f32): same results as the scalar conversions, half the instructions.
+template <typename T, int N>
+__device__ __forceinline__ void convert_pack(Pack<T, N>& pk, const float (&in)[N]) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) pk.v[i] = from_f32<T>(in[i]);
+}
+template <int N>
+__device__ __forceinline__ void convert_pack(Pack<__half, N>& pk, const float (&in)[N]) {
+    if constexpr (N % 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < N; i += 2) *reinterpret_cast<__half2*>(&pk.v[i]) = __floats2half2_rn(in[i], in[i + 1]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) pk.v[i] = __float2half_rn(in[i]);
+    }
+}
+template <int N>
+__device__ __forceinline__ void convert_pack(Pack<__nv_bfloat16, N>& pk, const float (&in)[N]) {
+    if constexpr (N % 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < N; i += 2) *reinterpret_cast<__nv_bfloat162*>(&pk.v[i]) = __floats2bfloat162_rn(in[i], in[i + 1]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) pk.v[i] = __float2bfloat16_rn(in[i]);
+    }
+}
+
 template <typename T, int N>
 __device__ __forceinline__ void store_vec(T* __restrict__ p, const float (&in)[N]) {
     using Raw = typename RawVec<sizeof(T) * N>::type;
     Pack<T, N> pk;
-#pragma unroll
-    for (int i = 0; i < N; ++i) pk.v[i] = from_f32<T>(in[i]);
+    convert_pack(pk, in);
     *reinterpret_cast<Raw*>(p) = *reinterpret_cast<const Raw*>(&pk);
 }
 
@@ -122,10 +149,47 @@ template <typename T, int N>
 __device__ __forceinline__ void store_vec_stream(T* __restrict__ p, const float (&in)[N]) {
     using Raw = typename RawVec<sizeof(T) * N>::type;
     Pack<T, N> pk;
-#pragma unroll
-    for (int i = 0; i < N; ++i) pk.v[i] = from_f32<T>(in[i]);
+    convert_pack(pk, in);
     __stcs(reinterpret_cast<Raw*>(p), *reinterpret_cast<const Raw*>(&pk));
 }
+
+// Rounds a pair of fp32 values to the storage dtype and back (where the reference stores an intermediate tensor).
+template <typename T>
+__device__ __forceinline__ void round_pair_to_storage(float& a, float& b) {
+    a = to_f32<T>(from_f32<T>(a));
+    b = to_f32<T>(from_f32<T>(b));
+}
+template <>
+__device__ __forceinline__ void round_pair_to_storage<__half>(float& a, float& b) {
+    const float2 f = __half22float2(__floats2half2_rn(a, b));
+    a = f.x;
+    b = f.y;
+}
+template <>
+__device__ __forceinline__ void round_pair_to_storage<__nv_bfloat16>(float& a, float& b) {
+    const float2 f = __bfloat1622float2(__floats2bfloat162_rn(a, b));
+    a = f.x;
+    b = f.y;
+}
+
+// Division of a 31-bit dividend by a run-time constant: q = (n * mul) >> (31 + shift), exact for n < 2^31
+// (mul = floor(2^(31+shift) / d) + 1 with shift = ceil(log2 d) fits 32 bits).
+struct FastDiv {
+    unsigned d, mul, shift;
+    FastDiv() : d(1), mul(0x80000001u), shift(0) {}
+    explicit FastDiv(unsigned divisor) : d(divisor) {
+        shift = 0;
+        while ((1ull << shift) < divisor) ++shift;
+        mul = static_cast<unsigned>((1ull << (31 + shift)) / divisor + 1);
+    }
+    __host__ __device__ __forceinline__ unsigned div(unsigned n) const {
+        return static_cast<unsigned>((static_cast<unsigned long long>(n) * mul) >> (31 + shift));
+    }
+    __host__ __device__ __forceinline__ void divmod(unsigned n, unsigned& q, unsigned& r) const {
+        q = div(n);
+        r = n - q * d;
+    }
+};
 
 // ---------------------------------------------------------------------------------------------
 // Reductions

@@ -10,10 +10,16 @@
 // once and the gradient written once: 2 * rows * vocab * sizeof(T) algorithmic bytes.
 #include <math_constants.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "launch_counter.h"
+#include "sm100.cuh"
 
 namespace cgpt {
+
+unsigned int* tc_status_device_ptr();   // gemm.cu: status word raised when a bounded device-side wait runs out
+
 namespace {
 
 constexpr int kCeThreads = 512;
@@ -150,6 +156,8 @@ int ce_launch(float* row_loss, void* grad, const void* logits, const std::uint32
     CGPT_LAUNCH_CHECK();
     return CGPT_OK;
 }
+
+#include "cross_entropy_ring.cuh"
 }  // namespace
 
 int cross_entropy_rows(float* row_loss, void* grad, const void* logits, const std::uint32_t* targets, long long rows,
@@ -160,6 +168,12 @@ int cross_entropy_rows(float* row_loss, void* grad, const void* logits, const st
     CGPT_DISPATCH_DTYPE(dtype, T, {
         constexpr int V = 16 / sizeof(T);
         const bool vec = vocab % V == 0 && aligned16(logits) && aligned16(grad);
+        if constexpr (sizeof(T) == 2) {
+            unsigned pitch = 0;
+            const int stages = ring_stages<T>(vocab, logits, grad, &pitch);
+            if (stages > 0)
+                return ce_ring_launch<T>(row_loss, grad, logits, targets, rows, vocab, inv_total_rows, gradient_scale, stages, pitch, s);
+        }
         if (staged && vec) return ce_launch<T, true, V>(row_loss, grad, logits, targets, rows, vocab, inv_total_rows, gradient_scale, grid, row_bytes, s);
         if (staged) return ce_launch<T, true, 1>(row_loss, grad, logits, targets, rows, vocab, inv_total_rows, gradient_scale, grid, row_bytes, s);
         if (vec) return ce_launch<T, false, V>(row_loss, grad, logits, targets, rows, vocab, inv_total_rows, gradient_scale, grid, 0, s);

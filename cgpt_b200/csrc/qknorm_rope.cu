@@ -17,6 +17,8 @@ namespace cgpt {
 namespace {
 
 constexpr int kQkThreads = 256;
+constexpr int kFwdUnroll = 8;   // row groups a warp has in flight per trip
+constexpr int kBwdUnroll = 4;
 
 __device__ __forceinline__ float group_sum(float v, int lanes_per_row) {
     for (int o = lanes_per_row >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -29,143 +31,177 @@ struct QkDims {
     float eps;
 };
 
-// Row r in [0, tokens*(q_heads+kv_heads)): token = r / heads, head = r % heads; heads < q_heads are query heads.
-template <typename T, bool BACKWARD>
+template <typename T>
+__device__ __forceinline__ void unpack8(float (&out)[8], const uint4& raw) {
+    Pack<T, 8> pk;
+    *reinterpret_cast<uint4*>(&pk) = raw;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = to_f32<T>(pk.v[i]);
+}
+template <typename T>
+__device__ __forceinline__ void unpack4(float (&out)[4], const uint2& raw) {
+    Pack<T, 4> pk;
+    *reinterpret_cast<uint2*>(&pk) = raw;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) out[i] = to_f32<T>(pk.v[i]);
+}
+
+// Two phases per thread, query rows then key rows, so that a phase has one source tensor, one weight vector and one dw
+// accumulator (no per-element selects). Row r of a phase: token = r / heads_of_phase, head = r % heads_of_phase; both
+// tensors are [tokens, heads, head_dim] contiguous, so the row's offset is simply r * head_dim.
+// A warp works on U groups of 32/(head_dim/8) rows per trip; every 16-byte row load of the trip (x, and dy in the
+// backward pass) is issued before the first value is used: U (2U) independent loads in flight per thread.
+// Row indices fit 31 bits (checked by the host); divisions by heads and seq use precomputed multipliers.
+template <typename T, bool BACKWARD, int U>
 __global__ void __launch_bounds__(kQkThreads)
 qknorm_rope_kernel(T* __restrict__ out_q, T* __restrict__ out_k, const T* __restrict__ in_q, const T* __restrict__ in_k,
                    const T* __restrict__ x_q, const T* __restrict__ x_k, const T* __restrict__ w_q, const T* __restrict__ w_k,
-                   const T* __restrict__ cos_t, const T* __restrict__ sin_t, float* __restrict__ dw_partial, QkDims dm) {
+                   const T* __restrict__ cos_t, const T* __restrict__ sin_t, float* __restrict__ dw_partial, QkDims dm,
+                   FastDiv div_qh, FastDiv div_kh, FastDiv div_seq) {
     const int lpr = dm.head_dim / 8;                 // lanes per row
     const int rows_per_warp = 32 / lpr;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = lane / lpr, l = lane % lpr;      // row slot inside the warp, chunk inside the row
-    const int heads = dm.q_heads + dm.kv_heads;
-    const long long rows = dm.tokens * heads;
     const int d0 = l * 8;
     const float inv_d = 1.0f / static_cast<float>(dm.head_dim);
     const int half_rot = dm.rotary_dim / 2;
+    const bool rotate = d0 < dm.rotary_dim;
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+    const uint2 zero2 = make_uint2(0u, 0u);
+    const unsigned group = static_cast<unsigned>(rows_per_warp) * U;
+    const unsigned warps_total = gridDim.x * (kQkThreads / 32);
+    const unsigned warp_id = blockIdx.x * (kQkThreads / 32) + warp;
+    __shared__ float red[BACKWARD ? kQkThreads : 1][9];
 
-    float wq[8], wk[8], dwq[8], dwk[8];
-    load_vec<T, 8>(wq, w_q + d0);
-    load_vec<T, 8>(wk, w_k + d0);
+    for (int which = 0; which < 2; ++which) {
+        const T* __restrict__ in = which == 0 ? in_q : in_k;
+        const T* __restrict__ xs = which == 0 ? x_q : x_k;
+        T* __restrict__ out = which == 0 ? out_q : out_k;
+        const FastDiv div_heads = which == 0 ? div_qh : div_kh;
+        const unsigned rows = static_cast<unsigned>(dm.tokens) * div_heads.d;
+        float w[8], dw[8];
+        load_vec<T, 8>(w, (which == 0 ? w_q : w_k) + d0);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { dwq[i] = 0.f; dwk[i] = 0.f; }
+        for (int i = 0; i < 8; ++i) dw[i] = 0.f;
 
-    const long long warps_total = static_cast<long long>(gridDim.x) * (kQkThreads / 32);
-    const long long warp_id = static_cast<long long>(blockIdx.x) * (kQkThreads / 32) + warp;
-    for (long long base = warp_id * rows_per_warp; base < rows; base += warps_total * rows_per_warp) {
-        const long long r = base + sub;
-        const bool active = r < rows;
-        const long long token = active ? r / heads : 0;
-        const int head = active ? static_cast<int>(r % heads) : 0;
-        const bool is_q = head < dm.q_heads;
-        const long long off = is_q ? (token * dm.q_heads + head) * dm.head_dim + d0
-                                   : (token * dm.kv_heads + (head - dm.q_heads)) * dm.head_dim + d0;
-        float c[4], s[4];
-        const bool rotate = d0 < dm.rotary_dim;
-        if (active && rotate) {
-            const int pos = static_cast<int>(token % dm.seq) + dm.offset;
-            load_vec<T, 4>(c, cos_t + static_cast<long long>(pos) * half_rot + d0 / 2);
-            load_vec<T, 4>(s, sin_t + static_cast<long long>(pos) * half_rot + d0 / 2);
-        }
-        if (!BACKWARD) {
-            float x[8];
+        const unsigned trips = (rows + group * warps_total - 1) / (group * warps_total);
+        for (unsigned trip = 0; trip < trips; ++trip) {
+            const unsigned base = (trip * warps_total + warp_id) * group;
+            uint4 raw_in[U], raw_x[U];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) x[i] = 0.f;
-            if (active) load_vec_stream<T, 8>(x, (is_q ? in_q : in_k) + off);
-            float ss = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
-            ss = group_sum(ss, lpr);
-            const float inv = rsqrtf(ss * inv_d + dm.eps);
-            float y[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                // the reference rounds the normalised value to the storage dtype before RoPE reads it
-                y[i] = to_f32<T>(from_f32<T>(x[i] * inv * (is_q ? wq[i] : wk[i])));
+            for (int u = 0; u < U; ++u) {
+                const unsigned r = base + u * rows_per_warp + sub;
+                const bool active = r < rows;
+                const long long off = static_cast<long long>(r) * dm.head_dim + d0;
+                raw_in[u] = active ? __ldcs(reinterpret_cast<const uint4*>(in + off)) : zero4;
+                if (BACKWARD) raw_x[u] = active ? __ldcs(reinterpret_cast<const uint4*>(xs + off)) : zero4;
             }
-            if (rotate) {
 #pragma unroll
-                for (int p = 0; p < 4; ++p) {
-                    const float a = y[2 * p], b = y[2 * p + 1];
-                    y[2 * p] = fmaf(-b, s[p], a * c[p]);
-                    y[2 * p + 1] = fmaf(a, s[p], b * c[p]);
+            for (int u = 0; u < U; ++u) {
+                const unsigned r = base + u * rows_per_warp + sub;
+                const bool active = r < rows;
+                const long long off = static_cast<long long>(r) * dm.head_dim + d0;
+                // the rotary tables are small and stay in L1/L2: fetched here, not ahead, to keep registers for the row data
+                uint2 raw_c = zero2, raw_s = zero2;
+                if (active && rotate) {
+                    const unsigned token = div_heads.div(r);
+                    const unsigned pos = token - div_seq.div(token) * div_seq.d + dm.offset;
+                    const long long t = static_cast<long long>(pos) * half_rot + d0 / 2;
+                    raw_c = __ldg(reinterpret_cast<const uint2*>(cos_t + t));
+                    raw_s = __ldg(reinterpret_cast<const uint2*>(sin_t + t));
+                }
+                float c[4], s[4];
+                unpack4<T>(c, raw_c);
+                unpack4<T>(s, raw_s);
+                if (!BACKWARD) {
+                    float x[8];
+                    unpack8<T>(x, raw_in[u]);
+                    float ss = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
+                    ss = group_sum(ss, lpr);
+                    const float inv = rsqrtf(ss * inv_d + dm.eps);
+                    float y[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) y[i] = x[i] * inv * w[i];
+                    // the reference rounds the normalised value to the storage dtype before RoPE reads it
+#pragma unroll
+                    for (int i = 0; i < 8; i += 2) round_pair_to_storage<T>(y[i], y[i + 1]);
+                    if (rotate) {
+#pragma unroll
+                        for (int p = 0; p < 4; ++p) {
+                            const float a = y[2 * p], b = y[2 * p + 1];
+                            y[2 * p] = fmaf(-b, s[p], a * c[p]);
+                            y[2 * p + 1] = fmaf(a, s[p], b * c[p]);
+                        }
+                    }
+                    if (active) store_vec<T, 8>(out + off, y);
+                } else {
+                    float g[8], x[8];
+                    unpack8<T>(g, raw_in[u]);
+                    unpack8<T>(x, raw_x[u]);
+                    if (rotate) {
+#pragma unroll
+                        for (int p = 0; p < 4; ++p) {
+                            const float a = g[2 * p], b = g[2 * p + 1];
+                            // the reference rounds the un-rotated gradient to the storage dtype (output of rope_backward)
+                            g[2 * p] = fmaf(b, s[p], a * c[p]);
+                            g[2 * p + 1] = fmaf(-a, s[p], b * c[p]);
+                            round_pair_to_storage<T>(g[2 * p], g[2 * p + 1]);
+                        }
+                    }
+                    float sx = 0.f, sg = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        sx = fmaf(x[i], x[i], sx);
+                        sg = fmaf(g[i] * w[i], x[i], sg);
+                    }
+                    sx = group_sum(sx, lpr);
+                    sg = group_sum(sg, lpr);
+                    const float inv = rsqrtf(sx * inv_d + dm.eps);
+                    const float corr = sg * inv_d * inv * inv * inv;
+                    float dx[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        dx[i] = fmaf(-x[i], corr, g[i] * w[i] * inv);
+                        dw[i] += g[i] * (x[i] * inv);    // inactive rows hold zeros
+                    }
+                    if (active) store_vec<T, 8>(out + off, dx);
                 }
             }
-            if (active) store_vec<T, 8>((is_q ? out_q : out_k) + off, y);
-        } else {
-            float g[8], x[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) { g[i] = 0.f; x[i] = 0.f; }
-            if (active) {
-                load_vec_stream<T, 8>(g, (is_q ? in_q : in_k) + off);
-                load_vec_stream<T, 8>(x, (is_q ? x_q : x_k) + off);
-            }
-            if (rotate) {
-#pragma unroll
-                for (int p = 0; p < 4; ++p) {
-                    const float a = g[2 * p], b = g[2 * p + 1];
-                    // the reference rounds the un-rotated gradient to the storage dtype (output of rope_backward)
-                    g[2 * p] = to_f32<T>(from_f32<T>(fmaf(b, s[p], a * c[p])));
-                    g[2 * p + 1] = to_f32<T>(from_f32<T>(fmaf(-a, s[p], b * c[p])));
-                }
-            }
-            float sx = 0.f, sg = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                sx = fmaf(x[i], x[i], sx);
-                sg = fmaf(g[i] * (is_q ? wq[i] : wk[i]), x[i], sg);
-            }
-            sx = group_sum(sx, lpr);
-            sg = group_sum(sg, lpr);
-            const float inv = rsqrtf(sx * inv_d + dm.eps);
-            const float corr = sg * inv_d * inv * inv * inv;
-            float dx[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                dx[i] = fmaf(-x[i], corr, g[i] * (is_q ? wq[i] : wk[i]) * inv);
-                const float contrib = g[i] * (x[i] * inv);
-                if (is_q) dwq[i] += contrib; else dwk[i] += contrib;
-            }
-            if (active) store_vec<T, 8>((is_q ? out_q : out_k) + off, dx);
         }
-    }
 
-    if (BACKWARD) {
-        // Combine lanes that own the same columns (fixed order), then one partial row per CTA: [grid][2][head_dim].
-        __shared__ float red[kQkThreads][9];
-        for (int which = 0; which < 2; ++which) {
+        if (BACKWARD) {
+            // Combine lanes that own the same columns (fixed order), then one partial row per CTA: [grid][2][head_dim].
             __syncthreads();
 #pragma unroll
-            for (int i = 0; i < 8; ++i) red[threadIdx.x][i] = which == 0 ? dwq[i] : dwk[i];
+            for (int i = 0; i < 8; ++i) red[threadIdx.x][i] = dw[i];
             __syncthreads();
-            if (threadIdx.x < lpr) {
-                for (int i = 0; i < 8; ++i) {
-                    float acc = 0.f;
-                    for (int t = threadIdx.x; t < kQkThreads; t += lpr) acc += red[t][i];
-                    dw_partial[(static_cast<long long>(blockIdx.x) * 2 + which) * dm.head_dim + threadIdx.x * 8 + i] = acc;
-                }
+            for (int col = threadIdx.x; col < dm.head_dim; col += kQkThreads) {
+                float acc = 0.f;
+                for (int t = col >> 3; t < kQkThreads; t += lpr) acc += red[t][col & 7];
+                dw_partial[(static_cast<long long>(blockIdx.x) * 2 + which) * dm.head_dim + col] = acc;
             }
         }
     }
 }
 
-// dw[col] = sum of the per-CTA partials in a fixed order: 8 row lanes per column, then a shared-memory combine.
+// dw[col] = sum of the per-CTA partials in a fixed order: 32 row lanes per column, then a shared-memory combine.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 qknorm_dw_reduce_kernel(T* __restrict__ dw_q, T* __restrict__ dw_k, const float* __restrict__ partial, int parts, int head_dim) {
-    __shared__ float tile[8][33];
-    const int col = blockIdx.x * 32 + (threadIdx.x & 31);      // 0 .. 2*head_dim
-    const int rl = threadIdx.x >> 5;
+    __shared__ float tile[32][33];
+    const int cl = threadIdx.x & 31, rl = threadIdx.x >> 5;
+    const int col = blockIdx.x * 32 + cl;      // 0 .. 2*head_dim
     float acc = 0.f;
     if (col < 2 * head_dim)
-        for (int p = rl; p < parts; p += 8) acc += partial[static_cast<long long>(p) * 2 * head_dim + col];
-    tile[rl][threadIdx.x & 31] = acc;
+        for (int p = rl; p < parts; p += 32) acc += partial[static_cast<long long>(p) * 2 * head_dim + col];
+    tile[rl][cl] = acc;
     __syncthreads();
     if (rl == 0 && col < 2 * head_dim) {
         float total = 0.f;
 #pragma unroll
-        for (int r = 0; r < 8; ++r) total += tile[r][threadIdx.x & 31];
+        for (int r = 0; r < 32; ++r) total += tile[r][cl];
         if (col < head_dim) dw_q[col] = from_f32<T>(total);
         else dw_k[col - head_dim] = from_f32<T>(total);
     }
@@ -194,6 +230,7 @@ extern "C" int cgpt_qknorm_rope_forward(void* q, void* k, const void* q_pre, con
     if (batch == 0 || seq == 0 || q_heads == 0 || kv_heads == 0 || head_dim == 0 || rotary_dim > head_dim ||
         position_offset + seq > max_seq || batch * seq > (1ull << 40))
         return CGPT_ERR_SHAPE;
+    if (batch * seq * (q_heads + kv_heads) >= (1ull << 31)) return CGPT_ERR_UNSUPPORTED;   // 32-bit row indices in the kernel
     if (!(epsilon > 0.f)) return CGPT_ERR_OPTION;
     if (!fast_path_ok(head_dim, rotary_dim, dtype, {q, k, q_pre, k_pre, q_norm, k_norm, cos_table, sin_table}))
         return CGPT_ERR_UNSUPPORTED;
@@ -201,18 +238,19 @@ extern "C" int cgpt_qknorm_rope_forward(void* q, void* k, const void* q_pre, con
     const QkDims dm{static_cast<long long>(batch * seq), static_cast<int>(seq), static_cast<int>(q_heads),
                     static_cast<int>(kv_heads), static_cast<int>(head_dim), static_cast<int>(rotary_dim),
                     static_cast<int>(position_offset), epsilon};
-    const unsigned grid = kNumSMs * 8;
+    const FastDiv div_qh(static_cast<unsigned>(q_heads)), div_kh(static_cast<unsigned>(kv_heads)), div_seq(static_cast<unsigned>(seq));
+    const unsigned grid = kNumSMs * 4;
     if (dtype == CGPT_DTYPE_F16)
-        qknorm_rope_kernel<__half, false><<<grid, kQkThreads, 0, s>>>(
+        qknorm_rope_kernel<__half, false, kFwdUnroll><<<grid, kQkThreads, 0, s>>>(
             static_cast<__half*>(q), static_cast<__half*>(k), static_cast<const __half*>(q_pre), static_cast<const __half*>(k_pre),
             nullptr, nullptr, static_cast<const __half*>(q_norm), static_cast<const __half*>(k_norm),
-            static_cast<const __half*>(cos_table), static_cast<const __half*>(sin_table), nullptr, dm);
+            static_cast<const __half*>(cos_table), static_cast<const __half*>(sin_table), nullptr, dm, div_qh, div_kh, div_seq);
     else
-        qknorm_rope_kernel<__nv_bfloat16, false><<<grid, kQkThreads, 0, s>>>(
+        qknorm_rope_kernel<__nv_bfloat16, false, kFwdUnroll><<<grid, kQkThreads, 0, s>>>(
             static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(q_pre),
             static_cast<const __nv_bfloat16*>(k_pre), nullptr, nullptr, static_cast<const __nv_bfloat16*>(q_norm),
             static_cast<const __nv_bfloat16*>(k_norm), static_cast<const __nv_bfloat16*>(cos_table),
-            static_cast<const __nv_bfloat16*>(sin_table), nullptr, dm);
+            static_cast<const __nv_bfloat16*>(sin_table), nullptr, dm, div_qh, div_kh, div_seq);
     count_launch();
     CGPT_LAUNCH_CHECK();
     return CGPT_OK;
@@ -231,6 +269,7 @@ extern "C" int cgpt_qknorm_rope_backward(void* dq_pre, void* dk_pre, void* dq_no
     if (batch == 0 || seq == 0 || q_heads == 0 || kv_heads == 0 || head_dim == 0 || rotary_dim > head_dim ||
         position_offset + seq > max_seq || batch * seq > (1ull << 40))
         return CGPT_ERR_SHAPE;
+    if (batch * seq * (q_heads + kv_heads) >= (1ull << 31)) return CGPT_ERR_UNSUPPORTED;   // 32-bit row indices in the kernel
     if (!(epsilon > 0.f)) return CGPT_ERR_OPTION;
     if (!fast_path_ok(head_dim, rotary_dim, dtype, {dq_pre, dk_pre, dq_rot, dk_rot, q_pre, k_pre, q_norm, k_norm, cos_table, sin_table}))
         return CGPT_ERR_UNSUPPORTED;
@@ -238,31 +277,32 @@ extern "C" int cgpt_qknorm_rope_backward(void* dq_pre, void* dk_pre, void* dq_no
     const QkDims dm{static_cast<long long>(batch * seq), static_cast<int>(seq), static_cast<int>(q_heads),
                     static_cast<int>(kv_heads), static_cast<int>(head_dim), static_cast<int>(rotary_dim),
                     static_cast<int>(position_offset), epsilon};
+    const FastDiv div_qh(static_cast<unsigned>(q_heads)), div_kh(static_cast<unsigned>(kv_heads)), div_seq(static_cast<unsigned>(seq));
     const unsigned grid = kNumSMs * 4;
     void* scratch = nullptr;
     CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(grid) * 2 * head_dim * sizeof(float), s));
     float* partial = static_cast<float*>(scratch);
     const unsigned rgrid = static_cast<unsigned>((2 * head_dim + 31) / 32);
     if (dtype == CGPT_DTYPE_F16) {
-        qknorm_rope_kernel<__half, true><<<grid, kQkThreads, 0, s>>>(
+        qknorm_rope_kernel<__half, true, kBwdUnroll><<<grid, kQkThreads, 0, s>>>(
             static_cast<__half*>(dq_pre), static_cast<__half*>(dk_pre), static_cast<const __half*>(dq_rot),
             static_cast<const __half*>(dk_rot), static_cast<const __half*>(q_pre), static_cast<const __half*>(k_pre),
             static_cast<const __half*>(q_norm), static_cast<const __half*>(k_norm), static_cast<const __half*>(cos_table),
-            static_cast<const __half*>(sin_table), partial, dm);
+            static_cast<const __half*>(sin_table), partial, dm, div_qh, div_kh, div_seq);
         count_launch();
         CGPT_LAUNCH_CHECK();
-        qknorm_dw_reduce_kernel<__half><<<rgrid, 256, 0, s>>>(static_cast<__half*>(dq_norm), static_cast<__half*>(dk_norm), partial,
+        qknorm_dw_reduce_kernel<__half><<<rgrid, 1024, 0, s>>>(static_cast<__half*>(dq_norm), static_cast<__half*>(dk_norm), partial,
                                                              static_cast<int>(grid), static_cast<int>(head_dim));
     } else {
-        qknorm_rope_kernel<__nv_bfloat16, true><<<grid, kQkThreads, 0, s>>>(
+        qknorm_rope_kernel<__nv_bfloat16, true, kBwdUnroll><<<grid, kQkThreads, 0, s>>>(
             static_cast<__nv_bfloat16*>(dq_pre), static_cast<__nv_bfloat16*>(dk_pre), static_cast<const __nv_bfloat16*>(dq_rot),
             static_cast<const __nv_bfloat16*>(dk_rot), static_cast<const __nv_bfloat16*>(q_pre),
             static_cast<const __nv_bfloat16*>(k_pre), static_cast<const __nv_bfloat16*>(q_norm),
             static_cast<const __nv_bfloat16*>(k_norm), static_cast<const __nv_bfloat16*>(cos_table),
-            static_cast<const __nv_bfloat16*>(sin_table), partial, dm);
+            static_cast<const __nv_bfloat16*>(sin_table), partial, dm, div_qh, div_kh, div_seq);
         count_launch();
         CGPT_LAUNCH_CHECK();
-        qknorm_dw_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, s>>>(static_cast<__nv_bfloat16*>(dq_norm),
+        qknorm_dw_reduce_kernel<__nv_bfloat16><<<rgrid, 1024, 0, s>>>(static_cast<__nv_bfloat16*>(dq_norm),
                                                                     static_cast<__nv_bfloat16*>(dk_norm), partial,
                                                                     static_cast<int>(grid), static_cast<int>(head_dim));
     }

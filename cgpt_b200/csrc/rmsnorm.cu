@@ -227,6 +227,8 @@ rmsnorm_dw_reduce_kernel(T* __restrict__ dw, const float* __restrict__ partial, 
     }
 }
 
+#include "rmsnorm_warp.cuh"
+
 struct Plan {
     int vec, cpt, wpr;
 };
@@ -272,6 +274,28 @@ int grid_for(std::size_t rows, int wpr, int ctas_per_sm) {
 template <typename T, int VEC>
 int launch_forward(void* y, const void* x, const void* w, std::size_t rows, std::size_t hidden,
                    float eps, const Plan& p, cudaStream_t s) {
+    if constexpr (sizeof(T) == 2 && VEC == 8) {
+        if (warp_rows::applicable(hidden, VEC, sizeof(T))) {
+            const int cpt = static_cast<int>((hidden / 8 + 31) / 32);
+            const std::size_t need = (rows + 2 * warp_rows::kWarps - 1) / (2 * warp_rows::kWarps);
+            const std::size_t cap = static_cast<std::size_t>(kNumSMs) * 4;
+            const int grid = static_cast<int>(need < cap ? need : cap);
+#define CGPT_RMS_FWD_WARP(CPT)                                                                              \
+    warp_rows::rmsnorm_forward_warp_kernel<T, CPT><<<grid, warp_rows::kThreads, 0, s>>>(                    \
+        static_cast<T*>(y), static_cast<const T*>(x), static_cast<const T*>(w), static_cast<long long>(rows), \
+        static_cast<int>(hidden), eps)
+            switch (cpt) {
+                case 1: CGPT_RMS_FWD_WARP(1); break;
+                case 2: CGPT_RMS_FWD_WARP(2); break;
+                case 3: CGPT_RMS_FWD_WARP(3); break;
+                default: CGPT_RMS_FWD_WARP(4); break;
+            }
+#undef CGPT_RMS_FWD_WARP
+            count_launch();
+            CGPT_LAUNCH_CHECK();
+            return CGPT_OK;
+        }
+    }
     const int grid = grid_for(rows, p.wpr, 8);
 #define CGPT_RMS_FWD(CPT)                                                                      \
     rmsnorm_forward_kernel<T, VEC, CPT><<<grid, kThreads, 0, s>>>(                              \
@@ -291,10 +315,46 @@ int launch_forward(void* y, const void* x, const void* w, std::size_t rows, std:
 template <typename T, int VEC>
 int launch_backward(void* dx, void* dw, const void* dy, const void* x, const void* w,
                     const void* ra, const void* rb, std::size_t rows, std::size_t hidden, float eps,
-                    const Plan& p, cudaStream_t s) {
-    const int grid = grid_for(rows, p.wpr, 4);
-    void* scratch = nullptr;
-    CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(grid) * hidden * sizeof(float), s));
+                    const Plan& p, cudaStream_t s, float* fixed_scratch = nullptr, std::size_t fixed_floats = 0) {
+    // fixed_scratch != nullptr: the per-CTA partial rows go there (capacity fixed_floats) and the grid is capped to fit;
+    // otherwise they come from the library's arena.
+    const std::size_t fit = fixed_scratch != nullptr ? fixed_floats / hidden : ~std::size_t{0};
+    if (fit == 0) return CGPT_ERR_SHAPE;
+    if constexpr (sizeof(T) == 2 && VEC == 8) {
+        if (warp_rows::applicable(hidden, VEC, sizeof(T))) {
+            const int cpt = static_cast<int>((hidden / 8 + 31) / 32);
+            const std::size_t need = (rows + warp_rows::kWarps - 1) / warp_rows::kWarps;
+            const std::size_t cap = static_cast<std::size_t>(kNumSMs) * 2;
+            int grid = static_cast<int>(need < cap ? need : cap);
+            if (static_cast<std::size_t>(grid) > fit) grid = static_cast<int>(fit);
+            void* partial = fixed_scratch;
+            if (partial == nullptr) CGPT_TRY(scratch_get(&partial, static_cast<std::size_t>(grid) * hidden * sizeof(float), s));
+            const std::size_t smem = static_cast<std::size_t>(cpt) * 2 * warp_rows::kThreads * sizeof(float4);
+#define CGPT_RMS_BWD_WARP(CPT)                                                                                 \
+    warp_rows::rmsnorm_backward_warp_kernel<T, CPT><<<grid, warp_rows::kThreads, smem, s>>>(                   \
+        static_cast<T*>(dx), static_cast<float*>(partial), static_cast<const T*>(dy), static_cast<const T*>(x), \
+        static_cast<const T*>(w), static_cast<const T*>(ra), static_cast<const T*>(rb),                        \
+        static_cast<long long>(rows), static_cast<int>(hidden), eps)
+            switch (cpt) {
+                case 1: CGPT_RMS_BWD_WARP(1); break;
+                case 2: CGPT_RMS_BWD_WARP(2); break;
+                case 3: CGPT_RMS_BWD_WARP(3); break;
+                default: CGPT_RMS_BWD_WARP(4); break;
+            }
+#undef CGPT_RMS_BWD_WARP
+            count_launch();
+            CGPT_LAUNCH_CHECK();
+            warp_rows::dw_reduce_wide_kernel<T><<<static_cast<unsigned>((hidden + 31) / 32), 1024, 0, s>>>(
+                static_cast<T*>(dw), static_cast<const float*>(partial), grid, static_cast<int>(hidden));
+            count_launch();
+            CGPT_LAUNCH_CHECK();
+            return CGPT_OK;
+        }
+    }
+    int grid = grid_for(rows, p.wpr, 4);
+    if (static_cast<std::size_t>(grid) > fit) grid = static_cast<int>(fit);
+    void* scratch = fixed_scratch;
+    if (scratch == nullptr) CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(grid) * hidden * sizeof(float), s));
 #define CGPT_RMS_BWD(CPT)                                                                       \
     rmsnorm_backward_kernel<T, VEC, CPT><<<grid, kThreads, 0, s>>>(                              \
         static_cast<T*>(dx), static_cast<float*>(scratch), static_cast<const T*>(dy),          \
@@ -401,34 +461,6 @@ int noalloc_scratch(float** out) {
     return CGPT_OK;
 }
 
-template <typename T, int VEC>
-int launch_backward_fixed_scratch(void* dx, void* dw, const void* dy, const void* x, const void* w, const void* ra,
-                                  const void* rb, std::size_t rows, std::size_t hidden, float eps, const Plan& p,
-                                  float* scratch, cudaStream_t s) {
-    int grid = grid_for(rows, p.wpr, 4);
-    const std::size_t fit = kNoAllocFloats / hidden;   // CTAs whose partial rows fit in the fixed array
-    if (fit == 0) return CGPT_ERR_SHAPE;
-    if (static_cast<std::size_t>(grid) > fit) grid = static_cast<int>(fit);
-#define CGPT_RMS_BWD_FIXED(CPT)                                                                  \
-    rmsnorm_backward_kernel<T, VEC, CPT><<<grid, kThreads, 0, s>>>(                               \
-        static_cast<T*>(dx), scratch, static_cast<const T*>(dy), static_cast<const T*>(x),      \
-        static_cast<const T*>(w), static_cast<const T*>(ra), static_cast<const T*>(rb),         \
-        static_cast<long long>(rows), static_cast<int>(hidden), eps, p.wpr)
-    switch (p.cpt) {
-        case 1: CGPT_RMS_BWD_FIXED(1); break;
-        case 2: CGPT_RMS_BWD_FIXED(2); break;
-        default: CGPT_RMS_BWD_FIXED(4); break;
-    }
-#undef CGPT_RMS_BWD_FIXED
-    count_launch();
-    CGPT_LAUNCH_CHECK();
-    rmsnorm_dw_reduce_kernel<T><<<static_cast<unsigned>((hidden + 31) / 32), 256, 0, s>>>(
-        static_cast<T*>(dw), scratch, grid, static_cast<int>(hidden));
-    count_launch();
-    CGPT_LAUNCH_CHECK();
-    return CGPT_OK;
-}
-
 }  // namespace
 }  // namespace cgpt
 
@@ -461,10 +493,10 @@ extern "C" int cgpt_rmsnorm_backward_noalloc(void* dx, void* dw, const void* dy,
         if (!make_plan<T>(hidden, al, &p)) return CGPT_ERR_UNSUPPORTED;
         constexpr int kMaxVec = 16 / sizeof(T);
         if (p.vec == kMaxVec)
-            return launch_backward_fixed_scratch<T, kMaxVec>(dx, dw, dy, x, w, residual_a, residual_b, rows, hidden, epsilon, p, scratch, s);
+            return launch_backward<T, kMaxVec>(dx, dw, dy, x, w, residual_a, residual_b, rows, hidden, epsilon, p, s, scratch, kNoAllocFloats);
         if (p.vec == 4)
-            return launch_backward_fixed_scratch<T, 4>(dx, dw, dy, x, w, residual_a, residual_b, rows, hidden, epsilon, p, scratch, s);
-        return launch_backward_fixed_scratch<T, 1>(dx, dw, dy, x, w, residual_a, residual_b, rows, hidden, epsilon, p, scratch, s);
+            return launch_backward<T, 4>(dx, dw, dy, x, w, residual_a, residual_b, rows, hidden, epsilon, p, s, scratch, kNoAllocFloats);
+        return launch_backward<T, 1>(dx, dw, dy, x, w, residual_a, residual_b, rows, hidden, epsilon, p, s, scratch, kNoAllocFloats);
     });
     return CGPT_OK;
 }
