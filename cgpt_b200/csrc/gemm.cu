@@ -352,27 +352,38 @@ inline bool use_v1_gemm() {
     return v1;
 }
 
+// C[M,N] (+)= sum_i A_i[M,K_i] * B_i, i < segments (1..kMaxKSegments): one launch, one pass over C.
 template <typename T, int BN, bool A_MN, bool B_MN>
-int launch_tc(T* C, const T* A, const T* B, int M, int N, int K, int accumulate, int dtype, cudaStream_t s) {
+int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int segments, int M, int N, int accumulate, int dtype,
+              cudaStream_t s) {
     using Cfg = GemmCfg<BN>;
-    CUtensorMap ta, tb;
-    {
+    GemmOperands ops;
+    ops.segments = segments;
+    int total_kb = 0;
+    long long K = 0;   // summed: split heuristics and the FLOP count
+    for (int i = 0; i < kMaxKSegments; ++i) {
+        const int g = i < segments ? i : 0;   // unused slots repeat segment 0 so that every map is valid
+        const int Ki = Ks[g];
         // innermost dimension first
-        const std::uint64_t dims_k[2] = {static_cast<std::uint64_t>(K), static_cast<std::uint64_t>(M)};
-        const std::uint64_t dims_m[2] = {static_cast<std::uint64_t>(M), static_cast<std::uint64_t>(K)};
-        const std::uint64_t st_k[1] = {static_cast<std::uint64_t>(K) * 2}, st_m[1] = {static_cast<std::uint64_t>(M) * 2};
-        const std::uint32_t box_k[2] = {BK, BM}, box_m[2] = {64, BK};
-        CGPT_TRY(make_tensor_map(&ta, dtype, A, 2, A_MN ? dims_m : dims_k, A_MN ? st_m : st_k, A_MN ? box_m : box_k));
+        const std::uint64_t a_dims_k[2] = {static_cast<std::uint64_t>(Ki), static_cast<std::uint64_t>(M)};
+        const std::uint64_t a_dims_m[2] = {static_cast<std::uint64_t>(M), static_cast<std::uint64_t>(Ki)};
+        const std::uint64_t a_st_k[1] = {static_cast<std::uint64_t>(Ki) * 2}, a_st_m[1] = {static_cast<std::uint64_t>(M) * 2};
+        const std::uint32_t a_box_k[2] = {BK, BM}, a_box_m[2] = {64, BK};
+        CGPT_TRY(make_tensor_map(&ops.a[i], dtype, As[g], 2, A_MN ? a_dims_m : a_dims_k, A_MN ? a_st_m : a_st_k, A_MN ? a_box_m : a_box_k));
+        const std::uint64_t b_dims_k[2] = {static_cast<std::uint64_t>(Ki), static_cast<std::uint64_t>(N)};
+        const std::uint64_t b_dims_n[2] = {static_cast<std::uint64_t>(N), static_cast<std::uint64_t>(Ki)};
+        const std::uint64_t b_st_k[1] = {static_cast<std::uint64_t>(Ki) * 2}, b_st_n[1] = {static_cast<std::uint64_t>(N) * 2};
+        const std::uint32_t b_box_k[2] = {BK, BN}, b_box_n[2] = {64, BK};
+        CGPT_TRY(make_tensor_map(&ops.b[i], dtype, Bs[g], 2, B_MN ? b_dims_n : b_dims_k, B_MN ? b_st_n : b_st_k, B_MN ? b_box_n : b_box_k));
+        if (i < segments) {
+            total_kb += (Ki + BK - 1) / BK;
+            K += Ki;
+        }
+        ops.kb_end[i] = total_kb;
     }
-    {
-        const std::uint64_t dims_k[2] = {static_cast<std::uint64_t>(K), static_cast<std::uint64_t>(N)};
-        const std::uint64_t dims_n[2] = {static_cast<std::uint64_t>(N), static_cast<std::uint64_t>(K)};
-        const std::uint64_t st_k[1] = {static_cast<std::uint64_t>(K) * 2}, st_n[1] = {static_cast<std::uint64_t>(N) * 2};
-        const std::uint32_t box_k[2] = {BK, BN}, box_n[2] = {64, BK};
-        CGPT_TRY(make_tensor_map(&tb, dtype, B, 2, B_MN ? dims_n : dims_k, B_MN ? st_n : st_k, B_MN ? box_n : box_k));
-    }
+    const CUtensorMap& ta = ops.a[0];
+    const CUtensorMap& tb = ops.b[0];
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-    const int total_kb = (K + BK - 1) / BK;
     // Split K when the output tiles alone leave most SMs idle and K is long enough to amortise it.
     int splits = 1;
     const int tiles = tiles_m * tiles_n;
@@ -406,9 +417,9 @@ int launch_tc(T* C, const T* A, const T* B, int M, int N, int K, int accumulate,
     }
     const bool timed = g_timing.enabled && g_timing.used + 2 <= g_timing.events.size();
     if (timed) CGPT_CUDA_TRY(cudaEventRecord(g_timing.events[g_timing.used], s));
-    if (use_v1_gemm()) {
+    if (use_v1_gemm() && segments == 1) {
         const dim3 grid(tiles_m, tiles_n, splits);
-        kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, C, partial, M, N, K, kb_per_split, epi);
+        kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, C, partial, M, N, static_cast<int>(K), kb_per_split, epi);
     } else {
         const long long units = static_cast<long long>(tiles) * splits;
         const unsigned grid = static_cast<unsigned>(units < kNumSMs ? units : kNumSMs);
@@ -421,7 +432,7 @@ int launch_tc(T* C, const T* A, const T* B, int M, int N, int K, int accumulate,
             CGPT_TRY(make_tensor_map(&tc, dtype, C, 2, dims_c, st_c, box_c));
             epi = kEpiStoreTma;
         }
-        pkernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, tc, C, partial, M, N, K, tiles_m, tiles_n, splits, kb_per_split, epi);
+        pkernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ops, tc, C, partial, M, N, total_kb, tiles_m, tiles_n, splits, kb_per_split, epi);
     }
     count_launch();
     CGPT_LAUNCH_CHECK();
@@ -443,15 +454,15 @@ int launch_tc(T* C, const T* A, const T* B, int M, int N, int K, int accumulate,
 }
 
 template <typename T>
-int launch_tc_layout(T* C, const T* A, const T* B, int M, int N, int K, int a_mn, int b_mn, int accumulate, int dtype,
-                     cudaStream_t s) {
+int launch_tc_layout(T* C, const T* const* A, const T* const* B, const int* K, int segments, int M, int N, int a_mn, int b_mn,
+                     int accumulate, int dtype, cudaStream_t s) {
     // 128x256 tiles whenever N allows: a 128x128 tile needs as many shared-memory operand bytes per MMA as the
     // tensor core can consume, 128x256 needs 3/4 of that per FLOP. Few tiles are compensated by split-K.
     const bool wide = N >= 256;
 #define CGPT_GEMM_CASE(AM, BMN)                                                                  \
     if (a_mn == AM && b_mn == BMN)                                                               \
-        return wide ? launch_tc<T, 256, AM != 0, BMN != 0>(C, A, B, M, N, K, accumulate, dtype, s) \
-                    : launch_tc<T, 128, AM != 0, BMN != 0>(C, A, B, M, N, K, accumulate, dtype, s);
+        return wide ? launch_tc<T, 256, AM != 0, BMN != 0>(C, A, B, K, segments, M, N, accumulate, dtype, s) \
+                    : launch_tc<T, 128, AM != 0, BMN != 0>(C, A, B, K, segments, M, N, accumulate, dtype, s);
     CGPT_GEMM_CASE(0, 0)
     CGPT_GEMM_CASE(0, 1)
     CGPT_GEMM_CASE(1, 1)
@@ -462,36 +473,60 @@ int launch_tc_layout(T* C, const T* A, const T* B, int M, int N, int K, int a_mn
 
 }  // namespace
 
-// C[M,N] (+)= A * B. a_mn = 0: A stored [M,K] (K contiguous); 1: A stored [K,M]. b_mn = 0: B stored
-// [N,K]; 1: B stored [K,N]. Chooses the tensor-core kernel for 16-bit dtypes when TMA can address the
-// operands (16-byte aligned bases, leading dimensions a multiple of 8 elements), else the SIMT kernel.
+// C[M,N] (+)= sum_i A_i * B_i over `segments` operand pairs chained along K (1 for a plain GEMM).
+// a_mn = 0: A_i stored [M,K_i] (K contiguous); 1: A_i stored [K_i,M]. b_mn = 0: B_i stored [N,K_i]; 1: B_i stored
+// [K_i,N]. Chooses the tensor-core kernel for 16-bit dtypes when TMA can address the operands (16-byte aligned
+// bases, leading dimensions a multiple of 8 elements), else one SIMT launch per segment.
+int gemm_dispatch_segments(void* C, const void* const* A, const void* const* B, const long long* K, int segments, long long M,
+                           long long N, int a_mn, int b_mn, int accumulate, int dtype, bool force_simt, cudaStream_t s) {
+    if (!C || !A || !B || !K) return CGPT_ERR_NULL;
+    if (segments < 1 || segments > kMaxKSegments) return CGPT_ERR_SHAPE;
+    if (!valid_float_dtype(dtype)) return CGPT_ERR_DTYPE;
+    if (M <= 0 || N <= 0 || M > 0x7fffffffll || N > 0x7fffffffll) return CGPT_ERR_SHAPE;
+    bool tc_ok = !force_simt && dtype != CGPT_DTYPE_F32 && (reinterpret_cast<std::uintptr_t>(C) % 2 == 0) && M * N >= 64 * 64;
+    long long k_total = 0;
+    int k32[kMaxKSegments] = {0, 0, 0};
+    for (int i = 0; i < segments; ++i) {
+        if (!A[i] || !B[i]) return CGPT_ERR_NULL;
+        if (K[i] <= 0 || K[i] > 0x7fffffffll) return CGPT_ERR_SHAPE;
+        const long long a_ld = a_mn ? M : K[i], b_ld = b_mn ? N : K[i];
+        tc_ok = tc_ok && aligned16(A[i]) && aligned16(B[i]) && a_ld % 8 == 0 && b_ld % 8 == 0;
+        k_total += K[i];
+        k32[i] = static_cast<int>(K[i]);
+    }
+    if (k_total > 0x7fffffffll) return CGPT_ERR_SHAPE;
+    tc_ok = tc_ok && k_total >= 32;
+    if (tc_ok) {
+        if (dtype == CGPT_DTYPE_F16)
+            return launch_tc_layout<__half>(static_cast<__half*>(C), reinterpret_cast<const __half* const*>(A),
+                                            reinterpret_cast<const __half* const*>(B), k32, segments, static_cast<int>(M),
+                                            static_cast<int>(N), a_mn, b_mn, accumulate, dtype, s);
+        return launch_tc_layout<__nv_bfloat16>(static_cast<__nv_bfloat16*>(C), reinterpret_cast<const __nv_bfloat16* const*>(A),
+                                               reinterpret_cast<const __nv_bfloat16* const*>(B), k32, segments, static_cast<int>(M),
+                                               static_cast<int>(N), a_mn, b_mn, accumulate, dtype, s);
+    }
+    for (int i = 0; i < segments; ++i) {
+        const long long Ki = K[i];
+        const long long a_sm = a_mn ? 1 : Ki, a_sk = a_mn ? M : 1, b_sn = b_mn ? 1 : Ki, b_sk = b_mn ? N : 1;
+        const dim3 grid(static_cast<unsigned>((N + 63) / 64), static_cast<unsigned>((M + 63) / 64));
+        const int acc = (accumulate || i > 0) ? 1 : 0;
+        CGPT_DISPATCH_DTYPE(dtype, T, {
+            gemm_simt_kernel<T><<<grid, 256, 0, s>>>(static_cast<T*>(C), static_cast<const T*>(A[i]), static_cast<const T*>(B[i]),
+                                                     static_cast<int>(M), static_cast<int>(N), static_cast<int>(Ki), a_sm, a_sk, b_sn,
+                                                     b_sk, acc);
+            count_launch();
+            CGPT_LAUNCH_CHECK();
+        });
+    }
+    return CGPT_OK;
+}
+
 int gemm_dispatch(void* C, const void* A, const void* B, long long M, long long N, long long K, int a_mn, int b_mn,
                   int accumulate, int dtype, bool force_simt, cudaStream_t s) {
     if (!C || !A || !B) return CGPT_ERR_NULL;
-    if (!valid_float_dtype(dtype)) return CGPT_ERR_DTYPE;
-    if (M <= 0 || N <= 0 || K <= 0 || M > 0x7fffffffll || N > 0x7fffffffll || K > 0x7fffffffll) return CGPT_ERR_SHAPE;
-    const long long a_ld = a_mn ? M : K, b_ld = b_mn ? N : K;
-    const bool tc_ok = !force_simt && dtype != CGPT_DTYPE_F32 && aligned16(A) && aligned16(B) &&
-                       (reinterpret_cast<std::uintptr_t>(C) % 2 == 0) && a_ld % 8 == 0 && b_ld % 8 == 0 &&
-                       M * N >= 64 * 64 && K >= 32;
-    if (tc_ok) {
-        if (dtype == CGPT_DTYPE_F16)
-            return launch_tc_layout<__half>(static_cast<__half*>(C), static_cast<const __half*>(A), static_cast<const __half*>(B),
-                                            static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), a_mn, b_mn, accumulate, dtype, s);
-        return launch_tc_layout<__nv_bfloat16>(static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(A),
-                                               static_cast<const __nv_bfloat16*>(B), static_cast<int>(M), static_cast<int>(N),
-                                               static_cast<int>(K), a_mn, b_mn, accumulate, dtype, s);
-    }
-    const long long a_sm = a_mn ? 1 : K, a_sk = a_mn ? M : 1, b_sn = b_mn ? 1 : K, b_sk = b_mn ? N : 1;
-    const dim3 grid(static_cast<unsigned>((N + 63) / 64), static_cast<unsigned>((M + 63) / 64));
-    CGPT_DISPATCH_DTYPE(dtype, T, {
-        gemm_simt_kernel<T><<<grid, 256, 0, s>>>(static_cast<T*>(C), static_cast<const T*>(A), static_cast<const T*>(B),
-                                                 static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), a_sm, a_sk, b_sn,
-                                                 b_sk, accumulate);
-        count_launch();
-        CGPT_LAUNCH_CHECK();
-    });
-    return CGPT_OK;
+    if (K <= 0 || K > 0x7fffffffll) return CGPT_ERR_SHAPE;
+    if (!force_simt && K < 32) force_simt = true;
+    return gemm_dispatch_segments(C, &A, &B, &K, 1, M, N, a_mn, b_mn, accumulate, dtype, force_simt, s);
 }
 
 unsigned int* tc_status_device_ptr() {
@@ -548,6 +583,19 @@ extern "C" int cgpt_linear_backward(void* dx, void* dw, void* db, const void* dy
         CGPT_TRY(column_sum(db, dy, T, O, accumulate_bias, dtype, s));
     }
     return CGPT_OK;
+}
+
+extern "C" int cgpt_linear_backward_input_fused(void* dx, const void* const* dy, const void* const* w,
+                                                const size_t* out_features, size_t count, size_t rows, size_t in_features,
+                                                int accumulate_input, int dtype, cgpt_stream_t stream) {
+    if (!dx || !dy || !w || !out_features) return CGPT_ERR_NULL;
+    if (count < 1 || count > static_cast<size_t>(kMaxKSegments)) return CGPT_ERR_SHAPE;
+    long long ks[kMaxKSegments] = {0, 0, 0};
+    for (size_t i = 0; i < count; ++i) ks[i] = static_cast<long long>(out_features[i]);
+    // dX = sum_i dY_i * W_i: A_i = dY_i [rows, out_i] (K-major), B_i = W_i [out_i, in] read as [K, N]
+    return gemm_dispatch_segments(dx, dy, w, ks, static_cast<int>(count), static_cast<long long>(rows),
+                                  static_cast<long long>(in_features), 0, 1, accumulate_input, dtype, false,
+                                  static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int cgpt_b200_device_status(unsigned int* status_out, int clear) {

@@ -53,11 +53,22 @@ __device__ __forceinline__ void gemm_store_chunk(const std::uint32_t (&r)[32], T
     }
 }
 
+// Operands of C = sum_i A_i * B_i: up to kMaxKSegments (A_i, B_i) pairs that share M and N and are chained along K
+// (the input gradient of several projections that read the same input: dX = dQ Wq + dK Wk + dV Wv in one pass).
+// Segment i covers K blocks [kb_end[i-1], kb_end[i]); a segment whose K is not a multiple of BK is zero-filled by TMA.
+constexpr int kMaxKSegments = 3;
+struct GemmOperands {
+    CUtensorMap a[kMaxKSegments];
+    CUtensorMap b[kMaxKSegments];
+    int kb_end[kMaxKSegments];
+    int segments;
+};
+
 template <typename T, int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                               const __grid_constant__ CUtensorMap tmap_c, T* __restrict__ C, float* __restrict__ partial, int M, int N, int K, int tiles_m, int tiles_n,
-                               int splits, int kb_per_split, int epilogue) {
+gemm_tcgen05_persistent_kernel(const __grid_constant__ GemmOperands ops, const __grid_constant__ CUtensorMap tmap_c,
+                               T* __restrict__ C, float* __restrict__ partial, int M, int N, int total_kb, int tiles_m,
+                               int tiles_n, int splits, int kb_per_split, int epilogue) {
     using Cfg = GemmCfg<BN>;
     extern __shared__ unsigned char gemm_smem_raw[];
     const std::uint32_t raw = smem_u32(gemm_smem_raw);
@@ -72,7 +83,6 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int total_kb = (K + BK - 1) / BK;
     const int tiles = tiles_m * tiles_n;
     const int units = tiles * splits;
 
@@ -80,8 +90,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const
         for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
         mbar_init_fence();
-        tma_prefetch_desc(&tmap_a);
-        tma_prefetch_desc(&tmap_b);
+        for (int i = 0; i < ops.segments; ++i) { tma_prefetch_desc(&ops.a[i]); tma_prefetch_desc(&ops.b[i]); }
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, 2 * BN);
@@ -109,18 +118,24 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a, const
                     mbar_expect_tx(&full[s], Cfg::kStageBytes);
                     unsigned char* a_dst = smem + s * Cfg::kStageBytes;
                     unsigned char* b_dst = a_dst + Cfg::kABytes;
-                    const int k0 = (kb_begin + i) * BK;
+                    const int kb = kb_begin + i;
+                    int seg = 0, kb_first = 0;
+                    if (ops.segments > 1 && kb >= ops.kb_end[0]) { seg = 1; kb_first = ops.kb_end[0]; }
+                    if (ops.segments > 2 && kb >= ops.kb_end[1]) { seg = 2; kb_first = ops.kb_end[1]; }
+                    const CUtensorMap* tmap_a = &ops.a[seg];
+                    const CUtensorMap* tmap_b = &ops.b[seg];
+                    const int k0 = (kb - kb_first) * BK;
                     if (!A_MN) {
-                        tma_load_2d(a_dst, &tmap_a, &full[s], k0, tile_m * BM);
+                        tma_load_2d(a_dst, tmap_a, &full[s], k0, tile_m * BM);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * (BK * 128), &tmap_a, &full[s], tile_m * BM + j * 64, k0);
+                        for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * (BK * 128), tmap_a, &full[s], tile_m * BM + j * 64, k0);
                     }
                     if (!B_MN) {
-                        tma_load_2d(b_dst, &tmap_b, &full[s], k0, tile_n * BN);
+                        tma_load_2d(b_dst, tmap_b, &full[s], k0, tile_n * BN);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * (BK * 128), &tmap_b, &full[s], tile_n * BN + j * 64, k0);
+                        for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * (BK * 128), tmap_b, &full[s], tile_n * BN + j * 64, k0);
                     }
                 }
             }

@@ -147,10 +147,16 @@ extern "C" int cgpt_block_backward(void* grad_in, const void* grad_out, const vo
     CGPT_TRY(cgpt_linear_backward(ws.d_act, g->down_proj, nullptr, grad_out, sv->activated, w->down_proj, m.rows, m.inter,
                                   m.d, 0, 0, 0, dt, stream));
     CGPT_TRY(cgpt_swiglu_backward(ws.d_gate, ws.d_up, ws.d_act, sv->gate, sv->up, m.rows * m.inter, 0, 0, dt, stream));
-    CGPT_TRY(cgpt_linear_backward(ws.d_ffn_norm_in, g->gate_proj, nullptr, ws.d_gate, sv->norm, w->gate_proj, m.rows, m.d,
-                                  m.inter, 0, 0, 0, dt, stream));
-    CGPT_TRY(cgpt_linear_backward(ws.d_ffn_norm_in, g->up_proj, nullptr, ws.d_up, sv->norm, w->up_proj, m.rows, m.d,
-                                  m.inter, 1, 0, 0, dt, stream));
+    {   // d(ffn norm output) = d_gate Wg + d_up Wu in one pass (the reference accumulates two GEMMs into the buffer)
+        const void* dys[2] = {ws.d_gate, ws.d_up};
+        const void* wts[2] = {w->gate_proj, w->up_proj};
+        const size_t outs[2] = {m.inter, m.inter};
+        CGPT_TRY(cgpt_linear_backward_input_fused(ws.d_ffn_norm_in, dys, wts, outs, 2, m.rows, m.d, 0, dt, stream));
+    }
+    CGPT_TRY(cgpt_linear_backward(nullptr, g->gate_proj, nullptr, ws.d_gate, sv->norm, nullptr, m.rows, m.d, m.inter, 0, 0, 0,
+                                  dt, stream));
+    CGPT_TRY(cgpt_linear_backward(nullptr, g->up_proj, nullptr, ws.d_up, sv->norm, nullptr, m.rows, m.d, m.inter, 0, 0, 0, dt,
+                                  stream));
     // grad_in = grad_out + d(ffn_norm)  (the reference's D2D copy + add_inplace, :678-681)
     CGPT_TRY(cgpt_rmsnorm_backward(grad_in, g->ffn_norm, ws.d_ffn_norm_in, in, w->ffn_norm, grad_out, nullptr, m.rows, m.d,
                                    eps, dt, stream));
@@ -176,12 +182,19 @@ extern "C" int cgpt_block_backward(void* grad_in, const void* grad_out, const vo
     }
     // the attention-norm output was overwritten by the FFN norm in the forward: recompute it (:725)
     CGPT_TRY(cgpt_rmsnorm_forward(ws.norm_a, in, w->attention_norm, m.rows, m.d, eps, dt, stream));
-    CGPT_TRY(cgpt_linear_backward(ws.d_attn_norm_in, g->q_projection, nullptr, ws.dq_pre, ws.norm_a, w->q_projection,
-                                  m.rows, m.d, m.qdim, 0, 0, 0, dt, stream));
-    CGPT_TRY(cgpt_linear_backward(ws.d_attn_norm_in, g->k_projection, nullptr, ws.dk_pre, ws.norm_a, w->k_projection,
-                                  m.rows, m.d, m.kvdim, 1, 0, 0, dt, stream));
-    CGPT_TRY(cgpt_linear_backward(ws.d_attn_norm_in, g->v_projection, nullptr, ws.dv, ws.norm_a, w->v_projection, m.rows,
-                                  m.d, m.kvdim, 1, 0, 0, dt, stream));
+    {   // d(attention norm output) = dQ Wq + dK Wk + dV Wv in one pass over the buffer (:726-744 runs three
+        // GEMMs, the last two accumulating into it)
+        const void* dys[3] = {ws.dq_pre, ws.dk_pre, ws.dv};
+        const void* wts[3] = {w->q_projection, w->k_projection, w->v_projection};
+        const size_t outs[3] = {m.qdim, m.kvdim, m.kvdim};
+        CGPT_TRY(cgpt_linear_backward_input_fused(ws.d_attn_norm_in, dys, wts, outs, 3, m.rows, m.d, 0, dt, stream));
+    }
+    CGPT_TRY(cgpt_linear_backward(nullptr, g->q_projection, nullptr, ws.dq_pre, ws.norm_a, nullptr, m.rows, m.d, m.qdim, 0, 0,
+                                  0, dt, stream));
+    CGPT_TRY(cgpt_linear_backward(nullptr, g->k_projection, nullptr, ws.dk_pre, ws.norm_a, nullptr, m.rows, m.d, m.kvdim, 0, 0,
+                                  0, dt, stream));
+    CGPT_TRY(cgpt_linear_backward(nullptr, g->v_projection, nullptr, ws.dv, ws.norm_a, nullptr, m.rows, m.d, m.kvdim, 0, 0, 0,
+                                  dt, stream));
     // grad_in += d(attention_norm)
     return cgpt_rmsnorm_backward(grad_in, g->attention_norm, ws.d_attn_norm_in, in, w->attention_norm, grad_in, nullptr,
                                  m.rows, m.d, eps, dt, stream);

@@ -103,6 +103,25 @@ def linear_backward(grad_input, grad_weight, grad_bias, grad_output, input, weig
                                    int(o.accumulate_bias), dtype_code(input), stream_ptr(stream)), "linear_backward")
 
 
+def linear_backward_input_fused(grad_input, grad_outputs, weights, stream=None, accumulate_input: bool = False):
+    """grad_input (+)= sum_i grad_outputs[i] @ weights[i] for up to three projections of the same input, in one
+    pass (cgpt_linear_backward_input_fused; the reference runs one accumulating linear_backward per projection)."""
+    import ctypes as C
+    n = len(grad_outputs)
+    _require(1 <= n <= 3 and len(weights) == n, "linear_backward_input_fused: 1..3 projections")
+    _same_cuda_dtype("linear_backward_input_fused", grad_input, *grad_outputs, *weights)
+    in_f = grad_input.shape[-1]
+    rows = grad_input.numel() // in_f
+    for dy, w in zip(grad_outputs, weights):
+        _require(w.dim() == 2 and w.shape[1] == in_f and dy.shape[-1] == w.shape[0] and dy.numel() == rows * w.shape[0],
+                 "linear_backward_input_fused: incompatible shapes")
+    dys = (C.c_void_p * n)(*[ptr(t) for t in grad_outputs])
+    ws = (C.c_void_p * n)(*[ptr(t) for t in weights])
+    outs = (C.c_size_t * n)(*[w.shape[0] for w in weights])
+    check(lib.cgpt_linear_backward_input_fused(ptr(grad_input), dys, ws, outs, n, rows, in_f, int(accumulate_input),
+                                               dtype_code(grad_input), stream_ptr(stream)), "linear_backward_input_fused")
+
+
 def gemm(c, a, b, m, n, k, a_layout=0, b_layout=0, accumulate=False, force_simt=False, stream=None):
     """Raw contraction C[m,n] (+)= A B of the library (see cgpt_gemm in include/cgpt_b200.h)."""
     _same_cuda_dtype("gemm", c, a, b)

@@ -88,6 +88,17 @@ int cgpt_linear_backward(void* dx, void* dw, void* db, const void* dy, const voi
                          size_t rows, size_t in_features, size_t out_features, int accumulate_input,
                          int accumulate_weight, int accumulate_bias, int dtype, cgpt_stream_t stream);
 
+/* Input gradient of `count` (1..3) projections that read the same input, in one pass:
+ *      dX[rows,in] (+)= sum_i dY_i[rows,out_i] W_i[out_i,in].
+ * No single counterpart in the reference: it is what the block backward obtains from consecutive
+ * linear_backward calls whose later ones accumulate into grad_input (reference src/core/transformer_block.cu:
+ * 669-675 for gate/up, 726-744 for q/k/v). The sum over i stays in the fp32 accumulator, so dX is rounded to the
+ * storage dtype once instead of after every projection. dy, w: arrays of `count` device pointers (host arrays);
+ * out_features: `count` sizes. Falls back to one SIMT launch per projection for fp32 or unaligned operands. */
+int cgpt_linear_backward_input_fused(void* dx, const void* const* dy, const void* const* w,
+                                     const size_t* out_features, size_t count, size_t rows, size_t in_features,
+                                     int accumulate_input, int dtype, cgpt_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Grouped-query softmax attention, forward with saved log-sum-exp and backward.
  * Replaces flash_gqa_attention_forward_with_lse (reference include/ops/attention.h:60-81,

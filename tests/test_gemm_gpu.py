@@ -106,3 +106,22 @@ def test_linear_forward_backward_model_shapes(ops, rows, inf, outf):
 def test_device_status_clean(ops):
     from cgpt_b200 import _lib
     assert _lib.device_status(clear=False) == 0, "a tensor-core kernel gave up on a bounded wait"
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,in_f,outs", [(512, 256, (256, 64, 64)), (4096, 1024, (1024, 256, 256)), (1000, 136, (200, 72)),
+                                            (2048, 1024, (2048, 2048)), (256, 128, (64,))])
+def test_linear_backward_input_fused(ops, dtype, rows, in_f, outs):
+    """dX = sum_i dY_i W_i in one launch against the fp32 sum of matmuls; also with accumulation into dX."""
+    g = torch.Generator(device="cuda").manual_seed(rows + in_f + len(outs))
+    dys = [torch.randn(rows, o, generator=g, device="cuda").to(dtype) for o in outs]
+    ws = [(torch.randn(o, in_f, generator=g, device="cuda") * 0.05).to(dtype) for o in outs]
+    want = sum(dy.float() @ w.float() for dy, w in zip(dys, ws))
+    dx = torch.full((rows, in_f), float("nan"), device="cuda", dtype=dtype)
+    ops.linear_backward_input_fused(dx, dys, ws)
+    torch.cuda.synchronize()
+    assert_close(host(dx), host(want), TOL[dtype], f"fused dX {dtype} {rows}x{in_f} {outs}")
+    base = torch.randn(rows, in_f, generator=g, device="cuda").to(dtype)
+    dx2 = base.clone()
+    ops.linear_backward_input_fused(dx2, dys, ws, accumulate_input=True)
+    assert_close(host(dx2), host(want + base.float()), TOL[dtype], f"fused dX accumulate {dtype}")
