@@ -71,8 +71,8 @@ __device__ __forceinline__ bool bwd_compute(unsigned char* smem, const BwdBars& 
                         lse2 = st[c0 + j + e]; delta = st[kCols + c0 + j + e];
                         if (need_mask) visible = x_idx <= dm.offset + col;
                     }
-                    const float sc = __uint_as_float(t1[j + e]) * scale2;
-                    p[e] = visible ? fast_exp2(sc - lse2) : 0.f;
+                    const float pe = fast_exp2(fmaf(__uint_as_float(t1[j + e]), scale2, -lse2));   // 2^(s*scale2 - lse2)
+                    p[e] = visible ? pe : 0.f;
                     ds[e] = p[e] * (__uint_as_float(t2[j + e]) - delta) * dm.scale;
                 }
                 pu[j >> 1] = pack2<T>(p[0], p[1]);

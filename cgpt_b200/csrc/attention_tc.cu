@@ -2,13 +2,14 @@
 // any GQA ratio, causal (with query_position_offset) or full, Sq and Sk arbitrary.
 //
 // Forward (this file, first part): one CTA per (128-query tile, query head, batch).
-//   warp 4      TMA producer: Q tile once, then K/V tiles of 128 keys through a 2-stage ring.
-//   warp 5      MMA issuer: S = Q K^T (128x128xD) into one of two TMEM buffers, one tile ahead of the
+//   warp 8      TMA producer: Q tile once, then K/V tiles of 128 keys through a 2-stage ring.
+//   warp 9      MMA issuer: S = Q K^T (128x128xD) into one of two TMEM buffers, one tile ahead of the
 //               softmax; PV = P V (128xDx128) into a third TMEM region once P is in shared memory.
-//   warps 0-3   softmax: thread t owns query row t = TMEM lane t. Reads its S row from TMEM (two passes of
-//               32-column chunks: row max, then exp2 and fp16 P written to 128B-swizzled shared memory as
-//               the K-major A operand of the PV MMA), keeps the output row O (D fp32) and the running
-//               max / sum in registers, and folds each PV tile in with the usual rescale.
+//   warps 0-7   softmax, two warpgroups: threads t and t+128 share query row t = TMEM lane t; each takes 64 of the
+//               tile's 128 score columns (row max, exchanged with the partner through shared memory; then exp2 and
+//               16-bit P written to 128B-swizzled shared memory as the K-major A operand of the PV MMA) and half of
+//               the output row O (D/2 fp32 registers), folding each PV tile in with the usual rescale. The softmax
+//               is a latency chain per tile, not an issue-rate problem: halving the chain per thread is what pays.
 // Numerics as the reference's tensor-core forward (src/ops/attention.cu:709-900): scores in the exp2
 // domain (s * scale * log2 e), P rounded to the storage dtype before the PV product, fp32 O and sums,
 // LSE = (max2 + log2(sum)) * ln 2 (natural log, scale included).
@@ -31,7 +32,7 @@ namespace {
 using namespace sm100;
 
 constexpr int kTile = 128;           // queries per CTA tile and keys per KV tile
-constexpr int kFwdThreads = 192;
+constexpr int kFwdThreads = 320;     // warps 0-7 softmax (two warpgroups, half of the tile's columns each), 8 TMA, 9 MMA
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kMaskValue = -1.0e30f;
@@ -43,13 +44,21 @@ template <int D> struct FwdSmem {
     static constexpr int kK = kQ + kTileBytes;             // 2 stages
     static constexpr int kV = kK + 2 * kTileBytes;         // 2 stages
     static constexpr int kP = kV + 2 * kTileBytes;         // [128, 128] 16-bit = 2 chunks
-    static constexpr int kBars = kP + 2 * kTile * 128;
+    static constexpr int kXchg = kP + 2 * kTile * 128;     // [2 parities + final][2 halves][128 rows] fp32, then a fail flag
+    static constexpr int kBars = kXchg + 3 * 2 * kTile * 4 + 16;
     static constexpr int kBytes = kBars + 256 + 1024;      // + barriers + alignment slack
 };
 
 // Byte offset of 16-byte chunk `c16` (0..7) of row `row` inside a 128B-swizzled [rows][128 B] tile.
 __device__ __forceinline__ std::uint32_t swz(int row, int c16) {
     return static_cast<std::uint32_t>(row * 128 + ((c16 ^ (row & 7)) << 4));
+}
+
+// 2^x on the special-function unit (flushes denormal results to zero, which is what a vanishing probability should be).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 template <typename T> __device__ __forceinline__ std::uint32_t pack2(float a, float b);
@@ -96,21 +105,23 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); mbar_init(&s_full[s], 1); }
-        mbar_init(p_full, kTile);
+        mbar_init(p_full, 2 * kTile);
         mbar_init(pv_full, 1);
         mbar_init_fence();
         tma_prefetch_desc(&tmap_q); tma_prefetch_desc(&tmap_k); tma_prefetch_desc(&tmap_v);
     }
-    if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    if (warp == 9) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    float* xchg = reinterpret_cast<float*>(smem + L::kXchg);
+    volatile int* fail_flag = reinterpret_cast<volatile int*>(smem + L::kXchg + 3 * 2 * kTile * 4);
+    if (threadIdx.x == 0) *fail_flag = 0;
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const std::uint32_t tmem = *tmem_slot;
-    const std::uint32_t tmem_s[2] = {tmem, tmem + 128};
-    const std::uint32_t tmem_pv = tmem + 256;
+    const std::uint32_t tmem_pv = tmem + 256;   // S buffers: columns [0,128) and [128,256), chosen by tile parity
     bool failed = false;
 
-    if (warp == 4) {
+    if (warp == 8) {
         if (lane == 0) {
             mbar_expect_tx(q_full, L::kTileBytes);
 #pragma unroll
@@ -128,20 +139,25 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                     tma_load_4d(smem + L::kV + s * L::kTileBytes + c * kTile * 128, &tmap_v, &v_full[s], c * 64, kvh, i * kTile, b);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         if (lane == 0) {
             constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
             constexpr std::uint32_t idesc_s = idesc_f16(fmt, 0, 0, kTile, kTile);   // S: A = Q (K-major), B = K (K-major)
             constexpr std::uint32_t idesc_pv = idesc_f16(fmt, 0, 1, kTile, D);      // PV: A = P (K-major), B = V (N-major)
-            const std::uint32_t q_base = smem_u32(smem + L::kQ);
-            const std::uint32_t p_base = smem_u32(smem + L::kP);
+            // One thread issues every MMA, so the descriptors are built once; a K step or a ring stage only adds a
+            // constant to the descriptor's 14-bit address field.
+            constexpr std::uint32_t kStage16 = L::kTileBytes >> 4;
+            const std::uint64_t q_desc = smem_desc_sw128(smem_u32(smem + L::kQ), 16, 1024);
+            const std::uint64_t k_desc0 = smem_desc_sw128(smem_u32(smem + L::kK), 16, 1024);
+            const std::uint64_t p_desc = smem_desc_sw128(smem_u32(smem + L::kP), 16, 1024);
+            const std::uint64_t v_desc0 = smem_desc_sw128(smem_u32(smem + L::kV), kTile * 128, 1024);
             auto issue_s = [&](int i) {
-                const std::uint32_t k_base = smem_u32(smem + L::kK + (i & 1) * L::kTileBytes);
+                const std::uint64_t k_desc = k_desc0 + (i & 1) * kStage16;
+                const std::uint32_t tmem_s = tmem + (i & 1) * 128;
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
-                    const std::uint32_t off = (k >> 2) * (kTile * 128) + (k & 3) * 32;
-                    mma_f16_ss(tmem_s[i & 1], smem_desc_sw128(q_base + off, 16, 1024), smem_desc_sw128(k_base + off, 16, 1024),
-                               idesc_s, k > 0 ? 1u : 0u);
+                    const std::uint32_t off16 = ((k >> 2) * (kTile * 128) + (k & 3) * 32) >> 4;
+                    mma_f16_ss(tmem_s, q_desc + off16, k_desc + off16, idesc_s, k > 0 ? 1u : 0u);
                 }
                 tc_commit(&s_full[i & 1]);
             };
@@ -157,12 +173,11 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                     }
                     if (!mbar_wait(&v_full[i & 1], (i >> 1) & 1) || !mbar_wait(p_full, i & 1)) { failed = true; break; }
                     tc_fence_after_sync();
-                    const std::uint32_t v_base = smem_u32(smem + L::kV + (i & 1) * L::kTileBytes);
+                    const std::uint64_t v_desc = v_desc0 + (i & 1) * kStage16;
 #pragma unroll
                     for (int k = 0; k < kTile / 16; ++k) {
-                        const std::uint32_t a_off = (k >> 2) * (kTile * 128) + (k & 3) * 32;
-                        mma_f16_ss(tmem_pv, smem_desc_sw128(p_base + a_off, 16, 1024),
-                                   smem_desc_sw128(v_base + k * (16 * 128), kTile * 128, 1024), idesc_pv, k > 0 ? 1u : 0u);
+                        const std::uint32_t a_off16 = ((k >> 2) * (kTile * 128) + (k & 3) * 32) >> 4;
+                        mma_f16_ss(tmem_pv, p_desc + a_off16, v_desc + ((k * (16 * 128)) >> 4), idesc_pv, k > 0 ? 1u : 0u);
                     }
                     tc_commit(pv_full);
                     tc_commit(&kv_empty[i & 1]);
@@ -170,61 +185,87 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
             }
         }
     } else {
-        // ---------------------------------------------------------------- softmax warps: thread = query row
-        const int row = threadIdx.x;            // 0..127 = TMEM lane
+        // ---------------------------------------------------------------- softmax warps
+        // Two threads share a query row (= TMEM lane): warpgroup `half` handles columns [64*half, 64*half+64) of every
+        // score tile and columns [D/2*half, ...) of the output row. Per tile they exchange their partial row maxima
+        // through shared memory (one named barrier); the row sums stay partial until the end.
+        const int row = threadIdx.x & (kTile - 1);
+        const int half = threadIdx.x >> 7;
         const int q_idx = q0 + row;
-        const std::uint32_t lane_base = static_cast<std::uint32_t>(warp * 32) << 16;
+        const std::uint32_t lane_base = static_cast<std::uint32_t>((warp & 3) * 32) << 16;
         const float scale2 = dm.scale * kLog2e;
-        float o_reg[D];
+        constexpr int DH = D / 2;
+        float o_reg[DH];
 #pragma unroll
-        for (int d = 0; d < D; ++d) o_reg[d] = 0.f;
+        for (int d = 0; d < DH; ++d) o_reg[d] = 0.f;
         float m_run = kMaskValue, l_run = 0.f;
-        unsigned char* p_smem = smem + L::kP;
+        unsigned char* p_smem = smem + L::kP + half * (kTile * 128);   // this half's 64-column swizzle atom
         for (int i = 0; i < n_kv; ++i) {
-            if (!mbar_wait(&s_full[i & 1], (i >> 1) & 1)) failed = true;
-            failed = __any_sync(0xffffffffu, failed);
-            if (failed) break;
-            tc_fence_after_sync();
-            const int kv0 = i * kTile;
-            const bool need_mask = (kv0 + kTile > dm.sk) || (dm.causal && kv0 + kTile - 1 > dm.offset + q0);
+            if (!failed && !mbar_wait(&s_full[i & 1], (i >> 1) & 1)) failed = true;
+            const int kv0 = i * kTile + half * 64;                    // first key of this thread's columns
+            const bool need_mask = (kv0 + 64 > dm.sk) || (dm.causal && kv0 + 63 > dm.offset + q0);
             const int limit = dm.causal ? (dm.offset + q_idx < dm.sk - 1 ? dm.offset + q_idx : dm.sk - 1) : dm.sk - 1;  // last visible key
-            // pass 1: row maximum
-            float m_new = m_run;
-#pragma unroll 1
-            for (int c0 = 0; c0 < kTile; c0 += 32) {
-                std::uint32_t r[32];
-                tmem_ld_32x32(tmem_s[i & 1] + lane_base + c0, r);
+            const std::uint32_t tmem_s = tmem + (i & 1) * 128 + half * 64 + lane_base;
+            float* my_slot = xchg + ((i & 1) * 2 + half) * kTile + row;
+            const float* other_slot = xchg + ((i & 1) * 2 + (half ^ 1)) * kTile + row;
+            // pass 1: maximum over this thread's 64 scores. Unmasked tiles take it on the raw scores (scale2 > 0).
+            float m_part = kMaskValue;
+            if (!failed) {
+                tc_fence_after_sync();
+                std::uint32_t r0[32], r1[32];
+                tmem_ld_32x32_x2(tmem_s, r0, tmem_s + 32, r1);
+                if (need_mask) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    float s2 = __uint_as_float(r[j]) * scale2;
-                    if (need_mask && kv0 + c0 + j > limit) s2 = kMaskValue;
-                    m_new = fmaxf(m_new, s2);
-                }
-            }
-            const float alpha = exp2f(m_run - m_new);
-            // pass 2: probabilities -> shared memory (K-major A operand of the PV product), row sum
-            float row_sum = 0.f;
-#pragma unroll 1
-            for (int c0 = 0; c0 < kTile; c0 += 32) {
-                std::uint32_t r[32];
-                tmem_ld_32x32(tmem_s[i & 1] + lane_base + c0, r);
-                std::uint32_t packed[16];
-#pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    float a = __uint_as_float(r[j]) * scale2, bb = __uint_as_float(r[j + 1]) * scale2;
-                    if (need_mask) {
-                        if (kv0 + c0 + j > limit) a = kMaskValue;
-                        if (kv0 + c0 + j + 1 > limit) bb = kMaskValue;
+                    for (int j = 0; j < 32; ++j) {
+                        m_part = fmaxf(m_part, kv0 + j > limit ? kMaskValue : __uint_as_float(r0[j]) * scale2);
+                        m_part = fmaxf(m_part, kv0 + 32 + j > limit ? kMaskValue : __uint_as_float(r1[j]) * scale2);
                     }
-                    const float pa = exp2f(a - m_new), pb = exp2f(bb - m_new);
-                    row_sum += pa + pb;
-                    packed[j >> 1] = pack2<T>(pa, pb);
+                } else {
+                    float raw_max = -3.0e38f;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) raw_max = fmaxf(raw_max, fmaxf(__uint_as_float(r0[j]), __uint_as_float(r1[j])));
+                    m_part = raw_max * scale2;
                 }
-                unsigned char* atom = p_smem + (c0 >> 6) * (kTile * 128);
-                const int c16 = (c0 & 63) >> 3;
+            } else {
+                *fail_flag = 1;
+            }
+            *my_slot = m_part;
+            asm volatile("bar.sync 1, 256;" ::: "memory");            // both halves published their maxima (or the flag)
+            if (*fail_flag != 0) { failed = true; break; }             // uniform over the 256 threads
+            const float m_new = fmaxf(m_run, fmaxf(m_part, *other_slot));
+            const float alpha = fast_exp2(m_run - m_new);
+            // pass 2: p = 2^(s * scale2 - m) -> shared memory (K-major A operand of the PV product), partial row sum
+            float row_sum = 0.f;
+            const float neg_m = -m_new;
+#pragma unroll 1
+            for (int c0 = 0; c0 < 64; c0 += 32) {
+                std::uint32_t r[32];
+                tmem_ld_32x32(tmem_s + c0, r);
+                std::uint32_t packed[16];
+                // two straight-line variants (no branch inside the unrolled body: the exponentials of a chunk must be
+                // free to overlap)
+                if (need_mask) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const float a = kv0 + c0 + j > limit ? kMaskValue : __uint_as_float(r[j]) * scale2;
+                        const float bb = kv0 + c0 + j + 1 > limit ? kMaskValue : __uint_as_float(r[j + 1]) * scale2;
+                        const float pa = fast_exp2(a + neg_m), pb = fast_exp2(bb + neg_m);
+                        row_sum += pa + pb;
+                        packed[j >> 1] = pack2<T>(pa, pb);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const float pa = fast_exp2(fmaf(__uint_as_float(r[j]), scale2, neg_m));
+                        const float pb = fast_exp2(fmaf(__uint_as_float(r[j + 1]), scale2, neg_m));
+                        row_sum += pa + pb;
+                        packed[j >> 1] = pack2<T>(pa, pb);
+                    }
+                }
+                const int c16 = c0 >> 3;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4)
-                    *reinterpret_cast<uint4*>(atom + swz(row, c16 + q4)) =
+                    *reinterpret_cast<uint4*>(p_smem + swz(row, c16 + q4)) =
                         make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
             }
             tc_fence_before_sync();      // TMEM reads of S done before the MMA warp may overwrite this buffer
@@ -232,30 +273,35 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
             mbar_arrive(p_full);
             l_run = l_run * alpha + row_sum;
             m_run = m_new;
-            if (!mbar_wait(pv_full, i & 1)) failed = true;
-            failed = __any_sync(0xffffffffu, failed);
-            if (failed) break;
+            if (!mbar_wait(pv_full, i & 1)) { failed = true; continue; }   // reported at the next exchange
             tc_fence_after_sync();
 #pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
+            for (int c0 = 0; c0 < DH; c0 += 32) {
                 std::uint32_t r[32];
-                tmem_ld_32x32(tmem_pv + lane_base + c0, r);
+                tmem_ld_32x32(tmem_pv + lane_base + half * DH + c0, r);
 #pragma unroll
                 for (int j = 0; j < 32; ++j) o_reg[c0 + j] = fmaf(o_reg[c0 + j], alpha, __uint_as_float(r[j]));
             }
             tc_fence_before_sync();
         }
+        // total row sum = the two halves' partial sums (same order in both threads)
+        if (failed) *fail_flag = 1;
+        float* l_slots = xchg + 4 * kTile;   // own region: the per-tile slots may still be read by the partner
+        l_slots[half * kTile + row] = l_run;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (*fail_flag != 0) failed = true;
         if (!failed && q_idx < dm.sq) {
-            const float inv = 1.0f / l_run;
-            T* dst = out + ((static_cast<long long>(b) * dm.sq + q_idx) * dm.hq + h) * D;
+            const float l_total = l_slots[row] + l_slots[kTile + row];
+            const float inv = 1.0f / l_total;
+            T* dst = out + ((static_cast<long long>(b) * dm.sq + q_idx) * dm.hq + h) * D + half * DH;
 #pragma unroll
-            for (int d = 0; d < D; d += 8) {
+            for (int d = 0; d < DH; d += 8) {
                 float v8[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) v8[e] = o_reg[d + e] * inv;
                 store_vec<T, 8>(dst + d, v8);
             }
-            if (lse != nullptr) lse[(static_cast<long long>(b) * dm.sq + q_idx) * dm.hq + h] = (m_run + log2f(l_run)) * kLn2;
+            if (half == 0 && lse != nullptr) lse[(static_cast<long long>(b) * dm.sq + q_idx) * dm.hq + h] = (m_run + log2f(l_total)) * kLn2;
         }
     }
 
@@ -266,7 +312,7 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, 512);
     }
@@ -309,6 +355,7 @@ int launch_forward(void* out, float* lse, const void* q, const void* k, const vo
 int attention_forward_tc_launch(void* out, float* lse, const void* q, const void* k, const void* v, const AttnDims& dm,
                                 int dtype, cudaStream_t s) {
     if (dtype == CGPT_DTYPE_F32 || (dm.d != 64 && dm.d != 128)) return CGPT_ERR_UNSUPPORTED;
+    if (!(dm.scale > 0.f)) return CGPT_ERR_UNSUPPORTED;   // the kernel takes row maxima before scaling
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return CGPT_ERR_UNSUPPORTED;
     if (dm.hq > 65535 || dm.batch > 65535) return CGPT_ERR_UNSUPPORTED;
     if (dtype == CGPT_DTYPE_F16)
