@@ -82,7 +82,7 @@ template <int BN> struct GemmCfg {
 // Device status word shared by the contraction kernels: non-zero means a bounded wait ran out.
 __device__ unsigned int g_gemm_status = 0;
 
-enum : int { kEpiStore = 0, kEpiAccumulate = 1, kEpiPartial = 2, kEpiNone = 3, kEpiStoreTma = 4 };
+enum : int { kEpiStore = 0, kEpiAccumulate = 1, kEpiPartial = 2, kEpiNone = 3, kEpiStoreTma = 4, kEpiStageOnly = 5, kEpiStoreTmaFixed = 6 };
 
 // Optional timing of the tensor-core GEMM launches (eager mode only, never during stream capture):
 // a CUDA event pair around every gemm_tcgen05_kernel launch plus its algorithmic FLOPs.
@@ -412,8 +412,8 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
     }
     int epi = splits > 1 ? kEpiPartial : (accumulate ? kEpiAccumulate : kEpiStore);
     {   // diagnosis only: CGPT_B200_GEMM_NOSTORE=1 drains the accumulator but skips the global stores
-        static const bool nostore = [] { const char* e = std::getenv("CGPT_B200_GEMM_NOSTORE"); return e && e[0] == '1'; }();
-        if (nostore) epi = 3;
+        static const int nostore = [] { const char* e = std::getenv("CGPT_B200_GEMM_NOSTORE"); return e ? std::atoi(e) : 0; }();
+        if (nostore == 1) epi = kEpiNone;
     }
     const bool timed = g_timing.enabled && g_timing.used + 2 <= g_timing.events.size();
     if (timed) CGPT_CUDA_TRY(cudaEventRecord(g_timing.events[g_timing.used], s));
@@ -431,6 +431,11 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
             const std::uint32_t box_c[2] = {64, BM};
             CGPT_TRY(make_tensor_map(&tc, dtype, C, 2, dims_c, st_c, box_c));
             epi = kEpiStoreTma;
+            // diagnosis only: CGPT_B200_GEMM_NOSTORE=2 stages the tile in shared memory but never issues the TMA store
+            // and =3 issues every TMA store to the first 16 KB of C (same store mechanics, no memory-system load)
+            static const int diag = [] { const char* e = std::getenv("CGPT_B200_GEMM_NOSTORE"); return e ? std::atoi(e) : 0; }();
+            if (diag == 2) epi = kEpiStageOnly;
+            if (diag == 3) epi = kEpiStoreTmaFixed;
         }
         pkernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ops, tc, C, partial, M, N, total_kb, tiles_m, tiles_n, splits, kb_per_split, epi);
     }

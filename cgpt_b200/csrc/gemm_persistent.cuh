@@ -187,7 +187,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ GemmOperands ops, const _
             tc_fence_after_sync();
             const int row = tile_m * BM + quarter * 32 + lane;
             const std::uint32_t tmem_acc = tmem_base + buf * BN + (static_cast<std::uint32_t>(quarter * 32) << 16);
-            if (epilogue == kEpiStoreTma) {
+            if (epilogue == kEpiStoreTma || epilogue == kEpiStageOnly || epilogue == kEpiStoreTmaFixed) {
                 // Stage 64 columns of the tile as 16-bit values in 128B-swizzled shared memory and let TMA write
                 // them out as full lines (a direct store would give every lane a different row: 16-byte pieces).
                 const int et = threadIdx.x - 64;              // 0..127 within the epilogue warps
@@ -209,10 +209,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ GemmOperands ops, const _
                     }
                     fence_proxy_async_smem();
                     asm volatile("bar.sync 1, 128;" ::: "memory");
-                    if (et == 0) {
+                    if (et == 0 && epilogue != kEpiStageOnly) {
+                        const bool fixed = epilogue == kEpiStoreTmaFixed;   // diagnosis: every store lands on the same 16 KB
                         asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                                     ::"l"(reinterpret_cast<std::uint64_t>(&tmap_c)), "r"(smem_u32(buf_s)), "r"(tile_n * BN + c0),
-                                       "r"(tile_m * BM)
+                                     ::"l"(reinterpret_cast<std::uint64_t>(&tmap_c)), "r"(smem_u32(buf_s)),
+                                       "r"(fixed ? 0 : tile_n * BN + c0), "r"(fixed ? 0 : tile_m * BM)
                                      : "memory");
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
