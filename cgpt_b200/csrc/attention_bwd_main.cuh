@@ -22,19 +22,25 @@ attention_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid
     bars.t_full = bars.uw_free + 2;             // [2]
     bars.w_full = bars.uw_free + 4;             // [2]
     bars.acc_done = bars.uw_free + 6;
-    bars.trace = (trace != nullptr && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && blockIdx.z == gridDim.z / 2) ? trace : nullptr;
+    bars.trace = (trace != nullptr && blockIdx.x == gridDim.x / 4) ? trace : nullptr;
     std::uint32_t* tmem_slot = reinterpret_cast<std::uint32_t*>(bars.acc_done + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // 1-D grid, heaviest tiles first over ALL (head, batch) pairs: CTAs start in blockIdx order, so the light tiles of
+    // the causal triangle fill the tail of the launch instead of a heavy tile starting last.
+    const int heads_here = MODE == MODE_DQ ? dm.hq : dm.hkv;
+    const int pairs = heads_here * dm.batch;
+    const int tile_rank = static_cast<int>(blockIdx.x) / pairs;           // 0 = most streaming tiles
+    const int pair = static_cast<int>(blockIdx.x) % pairs;
     BwdGeom g;
-    g.b = blockIdx.z;
+    g.b = pair / heads_here;
     g.ratio = dm.hq / dm.hkv;
     g.i0 = 0;
     g.n_q = 0;
     if (MODE == MODE_DQ) {
         const int q_tiles = (dm.sq + kRows - 1) / kRows;
-        g.x0 = (q_tiles - 1 - static_cast<int>(blockIdx.x)) * kRows;   // longest rows first
-        g.h = blockIdx.y;
+        g.x0 = (q_tiles - 1 - tile_rank) * kRows;   // the last query tile sees the most keys
+        g.h = pair % heads_here;
         g.kvh = g.h / g.ratio;
         int q_last = g.x0 + kRows - 1;
         if (q_last > dm.sq - 1) q_last = dm.sq - 1;
@@ -42,8 +48,8 @@ attention_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid
         if (last_key > dm.sk - 1) last_key = dm.sk - 1;
         g.n_it = last_key / kCols + 1;
     } else {
-        g.x0 = static_cast<int>(blockIdx.x) * kRows;
-        g.kvh = blockIdx.y;
+        g.x0 = tile_rank * kRows;                   // the first key tile is seen by the most queries (causal)
+        g.kvh = pair % heads_here;
         g.h = g.kvh * g.ratio;
         int first_q = dm.causal ? g.x0 - dm.offset : 0;
         if (first_q < 0) first_q = 0;
@@ -143,7 +149,7 @@ int launch_backward(void* dq, void* dk, void* dv, const void* dout, const void* 
     }
     unsigned int* status = tc_status_device_ptr();
     if (status == nullptr) return CGPT_ERR_STATE;
-    const dim3 grid_q((dm.sq + kRows - 1) / kRows, dm.hq, dm.batch);
+    const dim3 grid_q(static_cast<unsigned>(((dm.sq + kRows - 1) / kRows) * dm.hq * dm.batch));
     // CGPT_B200_ATTN_TRACE=<device pointer of 2*64*8 uint64> records per-iteration timestamps of one CTA per kernel (diagnosis)
     unsigned long long* trace = nullptr;
     if (const char* e = std::getenv("CGPT_B200_ATTN_TRACE")) trace = reinterpret_cast<unsigned long long*>(std::strtoull(e, nullptr, 0));
@@ -151,7 +157,7 @@ int launch_backward(void* dq, void* dk, void* dv, const void* dout, const void* 
                                               accumulate, status, trace);
     count_launch();
     CGPT_LAUNCH_CHECK();
-    const dim3 grid_kv((dm.sk + kRows - 1) / kRows, dm.hkv, dm.batch);
+    const dim3 grid_kv(static_cast<unsigned>(((dm.sk + kRows - 1) / kRows) * dm.hkv * dm.batch));
     kkv<<<grid_kv, kBwdThreads, L::kBytes, s>>>(k128, v128, q64, do64, static_cast<T*>(dk), static_cast<T*>(dv), lse2_t, delta_t, dm,
                                                 accumulate, status, trace ? trace + 64 * 8 : nullptr);
     count_launch();

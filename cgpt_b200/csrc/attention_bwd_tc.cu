@@ -137,7 +137,7 @@ int attention_backward_tc_launch(void* dq, void* dk, void* dv, const void* dout,
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !aligned16(dout) || !aligned16(dq) ||
         !aligned16(dk) || !aligned16(dv))
         return CGPT_ERR_UNSUPPORTED;
-    if (dm.hq > 65535 || dm.batch > 65535) return CGPT_ERR_UNSUPPORTED;
+    if (static_cast<long long>((dm.sq + kRows - 1) / kRows + (dm.sk + kRows - 1) / kRows) * dm.hq * dm.batch > 0x7fffffffll) return CGPT_ERR_UNSUPPORTED;   // 1-D grids
     if (dtype == CGPT_DTYPE_F16)
         return dm.d == 64 ? launch_backward<__half, 64>(dq, dk, dv, dout, out, lse, q, k, v, dm, accumulate, dtype, s)
                           : launch_backward<__half, 128>(dq, dk, dv, dout, out, lse, q, k, v, dm, accumulate, dtype, s);

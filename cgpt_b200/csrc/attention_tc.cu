@@ -92,8 +92,11 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q_tiles = (dm.sq + kTile - 1) / kTile;
-    const int q_tile = q_tiles - 1 - static_cast<int>(blockIdx.x);   // longest rows first
-    const int h = blockIdx.y, b = blockIdx.z;
+    // 1-D grid, longest query tiles first over ALL (head, batch) pairs: the short tiles of the causal triangle fill the
+    // tail of the launch.
+    const int pairs = dm.hq * dm.batch;
+    const int q_tile = q_tiles - 1 - static_cast<int>(blockIdx.x) / pairs;
+    const int h = (static_cast<int>(blockIdx.x) % pairs) % dm.hq, b = (static_cast<int>(blockIdx.x) % pairs) / dm.hq;
     const int kvh = h / (dm.hq / dm.hkv);
     const int q0 = q_tile * kTile;
     int q_last = q0 + kTile - 1;
@@ -343,7 +346,7 @@ int launch_forward(void* out, float* lse, const void* q, const void* k, const vo
     }
     unsigned int* status = tc_status_device_ptr();
     if (status == nullptr) return CGPT_ERR_STATE;
-    const dim3 grid((dm.sq + kTile - 1) / kTile, dm.hq, dm.batch);
+    const dim3 grid(static_cast<unsigned>(((dm.sq + kTile - 1) / kTile) * dm.hq * dm.batch));
     kernel<<<grid, kFwdThreads, L::kBytes, s>>>(tq, tk, tv, static_cast<T*>(out), lse, dm, status);
     count_launch();
     CGPT_LAUNCH_CHECK();
@@ -357,7 +360,7 @@ int attention_forward_tc_launch(void* out, float* lse, const void* q, const void
     if (dtype == CGPT_DTYPE_F32 || (dm.d != 64 && dm.d != 128)) return CGPT_ERR_UNSUPPORTED;
     if (!(dm.scale > 0.f)) return CGPT_ERR_UNSUPPORTED;   // the kernel takes row maxima before scaling
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return CGPT_ERR_UNSUPPORTED;
-    if (dm.hq > 65535 || dm.batch > 65535) return CGPT_ERR_UNSUPPORTED;
+    if (static_cast<long long>((dm.sq + kTile - 1) / kTile + (dm.sk + kTile - 1) / kTile) * dm.hq * dm.batch > 0x7fffffffll) return CGPT_ERR_UNSUPPORTED;   // 1-D grids
     if (dtype == CGPT_DTYPE_F16)
         return dm.d == 64 ? launch_forward<__half, 64>(out, lse, q, k, v, dm, dtype, s) : launch_forward<__half, 128>(out, lse, q, k, v, dm, dtype, s);
     return dm.d == 64 ? launch_forward<__nv_bfloat16, 64>(out, lse, q, k, v, dm, dtype, s)
