@@ -39,15 +39,15 @@ class TransformerModelOptions:
     block_options: TransformerBlockOptions = field(default_factory=TransformerBlockOptions)
 
 
-def preset(name: str) -> TransformerModelOptions:
+def preset(name: str, vocabulary_size: int = 32000) -> TransformerModelOptions:
     """Model presets of the reference trainer (train/train.cpp:140-149) plus the tiny CPU-runnable model."""
     if name == "104m":
         b = TransformerBlockOptions(1024, 2048, 8, 2, 128, 128)
-        return TransformerModelOptions(32000, 8, b)
+        return TransformerModelOptions(vocabulary_size, 8, b)
     if name == "small":
-        return TransformerModelOptions(32000, 4, TransformerBlockOptions(512, 1024, 4, 1, 128, 128))
+        return TransformerModelOptions(vocabulary_size, 4, TransformerBlockOptions(512, 1024, 4, 1, 128, 128))
     if name == "tiny":
-        return TransformerModelOptions(32000, 2, TransformerBlockOptions(256, 688, 4, 2, 64, 64))
+        return TransformerModelOptions(vocabulary_size, 2, TransformerBlockOptions(256, 688, 4, 2, 64, 64))
     raise ValueError(f"unknown preset {name}")
 
 

@@ -91,6 +91,20 @@ class TrainStep:
             self._allreduce_gradients()
             O.adamw_step_many_async(self.entries, self.adamw_options, self.adamw_workspace)
 
+    def validation_loss(self) -> float:
+        """Loss of the batch currently in token_ids/targets without an optimizer step (train/train.cpp:490-530 runs
+        forward + loss on held-out batches). The loss layer also rewrites the LM-head and final-norm gradient buffers;
+        the next training step overwrites them again."""
+        st, ws, bw, o = self.storage, self.workspace, self.backward_workspace, self.options
+        with torch.cuda.stream(self.stream):
+            keep = M.transformer_model_forward(None, self.token_ids, self.batch, self.seq, st, ws, self.cos, self.sin, None,
+                                               None, o, scratch=bw)
+            M.cut_cross_entropy_forward_backward(self.loss, bw.grad_normalized, st.g_lm_head, ws.normalized, st.lm_head,
+                                                 self.targets, self.rows, None, 1.0, chunk_rows=self.cce_chunk_rows)
+            self.stream.synchronize()
+        del keep
+        return float(self.loss.item())
+
     def read_loss(self) -> float:
         """Device -> host read of the last step's loss (synchronises the step's stream)."""
         self.stream.synchronize()

@@ -1,0 +1,40 @@
+"""The training driver end to end on one GPU: a tiny model trains on a repeating token pattern, writes the reference's
+safetensors layout plus optimizer state, and a second run resumes from it (step count and moments included)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_train_save_resume(tmp_path, capsys):
+    from cgpt_b200 import train_cli
+    from safetensors import safe_open
+    tokens = np.tile(np.arange(97, dtype=np.int32) % 50, 400)          # learnable: next token is a function of the current
+    path = str(tmp_path / "tokens.npy")
+    np.save(path, tokens)
+    out1, out2 = str(tmp_path / "run1"), str(tmp_path / "run2")
+    common = ["--input", path, "--model", "tiny", "--vocab-size", "64", "--batch-size", "4", "--sequence-length", "64",
+              "--validation-interval", "20", "--validation-batches", "2", "--learning-rate", "1e-3",
+              "--min-learning-rate", "1e-4", "--save-avg-loss"]
+    assert train_cli.main(common + ["--max-steps", "40", "--output-dir", out1]) == 0
+    text = capsys.readouterr().out
+    pick = lambda t: [float(l.split(" loss ")[1].split()[0]) for l in t.splitlines()
+                      if l.startswith("step ") and "/" in l.split()[1]]
+    losses = pick(text)
+    assert len(losses) == 4 and losses[-1] < 0.5 * losses[0], text
+    assert "validation loss" in text
+    assert os.path.exists(os.path.join(out1, "model.safetensors")) and os.path.exists(os.path.join(out1, "optimizer.safetensors"))
+    assert open(os.path.join(out1, "loss.csv")).readline().strip() == "step,loss"
+    with safe_open(os.path.join(out1, "model.safetensors"), framework="pt") as f:
+        assert "lm_head.weight" in f.keys() and f.get_tensor("model.layers.1.self_attn.q_norm.weight").dtype == torch.float16
+    # resume: continues at step 40 with the saved moments, so the loss keeps falling from where it was
+    assert train_cli.main(common + ["--max-steps", "60", "--load-dir", out1, "--output-dir", out2]) == 0
+    text2 = capsys.readouterr().out
+    assert "resuming at step 40" in text2
+    losses2 = pick(text2)
+    assert len(losses2) == 2 and max(losses2) < 0.5 * losses[0], text2   # a cold restart would be back near ln(64)
+    with safe_open(os.path.join(out2, "optimizer.safetensors"), framework="pt") as f:
+        assert '"step": 60' in f.metadata()["extra"]
