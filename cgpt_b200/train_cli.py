@@ -152,14 +152,23 @@ def main(argv=None) -> int:
                 st.master_parameter.copy_(p.float())
         log(f"loaded {args.load_dir}, resuming at step {first_step}")
 
-    host_ids = torch.empty(B, S, dtype=torch.int32).pin_memory()
-    host_targets = torch.empty(B, S, dtype=torch.int32).pin_memory()
+    # The step is asynchronous: the host runs several steps ahead of the GPU, so a pinned staging buffer may only be
+    # rewritten once the copy that reads it has executed. A small ring of buffers, each guarded by an event.
+    ring = [(torch.empty(B, S, dtype=torch.int32).pin_memory(), torch.empty(B, S, dtype=torch.int32).pin_memory(),
+             torch.cuda.Event()) for _ in range(4)]
+    staged = 0
 
     def stage(sample_rows: np.ndarray) -> None:
+        nonlocal staged
+        host_ids, host_targets, copied = ring[staged % len(ring)]
+        if staged >= len(ring):
+            copied.synchronize()
+        staged += 1
         rows = torch.from_numpy(rank_slice(sample_rows, rank, B))
         host_ids.copy_(rows[:, :-1])
         host_targets.copy_(rows[:, 1:])
         ts.upload_batch(host_ids, host_targets)
+        copied.record(ts.stream)
 
     def validate() -> float:
         total = 0.0

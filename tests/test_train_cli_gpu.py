@@ -38,3 +38,18 @@ def test_train_save_resume(tmp_path, capsys):
     assert len(losses2) == 2 and max(losses2) < 0.5 * losses[0], text2   # a cold restart would be back near ln(64)
     with safe_open(os.path.join(out2, "optimizer.safetensors"), framework="pt") as f:
         assert '"step": 60' in f.metadata()["extra"]
+
+
+def test_loss_on_random_tokens_stays_at_entropy(tmp_path, capsys):
+    """Uniform random ids cannot be predicted: the training loss (always measured on a batch the model has not seen)
+    must stay near ln(vocab). A driver that lets the GPU re-read a staging buffer would train on one batch repeatedly
+    and report a loss well below it."""
+    import math
+    from cgpt_b200 import train_cli
+    args = ["--synthetic", "600000", "--model", "tiny", "--vocab-size", "4096", "--batch-size", "8", "--sequence-length", "128",
+            "--max-steps", "40", "--validation-interval", "40", "--validation-batches", "2", "--learning-rate", "1e-3",
+            "--min-learning-rate", "1e-3", "--output-dir", str(tmp_path / "o")]
+    assert train_cli.main(args) == 0
+    text = capsys.readouterr().out
+    losses = [float(l.split(" loss ")[1].split()[0]) for l in text.splitlines() if l.startswith("step ") and "/" in l.split()[1]]
+    assert len(losses) == 4 and all(abs(x - math.log(4096)) < 0.35 for x in losses), text
