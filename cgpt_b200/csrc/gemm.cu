@@ -73,10 +73,11 @@ constexpr int kGemmThreads = 192;
 
 template <int BN> struct GemmCfg {
     static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr int kStoreBufs = 2;   // staging buffers of the TMA-store epilogue
     static constexpr int kABytes = BM * BK * 2;
     static constexpr int kBBytes = BN * BK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + 2 * BM * 128 /*store staging*/;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kStoreBufs * BM * 128 /*store staging*/;
 };
 
 // Device status word shared by the contraction kernels: non-zero means a bounded wait ran out.
@@ -345,6 +346,7 @@ column_sum_kernel(T* __restrict__ out, const T* __restrict__ in, long long rows,
 }
 
 #include "gemm_persistent.cuh"
+#include "gemm_swiglu.cuh"
 
 // CGPT_B200_GEMM_V1=1 selects the one-tile-per-CTA kernel instead of the persistent one (for A/B timing).
 inline bool use_v1_gemm() {
@@ -534,6 +536,28 @@ int gemm_dispatch(void* C, const void* A, const void* B, long long M, long long 
     return gemm_dispatch_segments(C, &A, &B, &K, 1, M, N, a_mn, b_mn, accumulate, dtype, force_simt, s);
 }
 
+// gate = X Wg^T, up = X Wu^T, act = swiglu(gate, up) in one launch when the tensor-core path applies.
+int linear_swiglu_dispatch(void* gate, void* up, void* act, const void* x, const void* wg, const void* wu, long long M, long long N,
+                           long long K, int dtype, cudaStream_t s) {
+    if (!gate || !up || !act || !x || !wg || !wu) return CGPT_ERR_NULL;
+    if (!valid_float_dtype(dtype)) return CGPT_ERR_DTYPE;
+    if (M <= 0 || N <= 0 || K <= 0 || M > 0x7fffffffll || N > 0x7fffffffll || K > 0x7fffffffll) return CGPT_ERR_SHAPE;
+    int rc = CGPT_ERR_UNSUPPORTED;
+    if (dtype == CGPT_DTYPE_F16)
+        rc = launch_gemm_swiglu<__half>(static_cast<__half*>(gate), static_cast<__half*>(up), static_cast<__half*>(act),
+                                        static_cast<const __half*>(x), static_cast<const __half*>(wg), static_cast<const __half*>(wu),
+                                        static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), dtype, s);
+    else if (dtype == CGPT_DTYPE_BF16)
+        rc = launch_gemm_swiglu<__nv_bfloat16>(static_cast<__nv_bfloat16*>(gate), static_cast<__nv_bfloat16*>(up),
+                                               static_cast<__nv_bfloat16*>(act), static_cast<const __nv_bfloat16*>(x),
+                                               static_cast<const __nv_bfloat16*>(wg), static_cast<const __nv_bfloat16*>(wu),
+                                               static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), dtype, s);
+    if (rc != CGPT_ERR_UNSUPPORTED) return rc;
+    CGPT_TRY(gemm_dispatch(gate, x, wg, M, N, K, 0, 0, 0, dtype, false, s));
+    CGPT_TRY(gemm_dispatch(up, x, wu, M, N, K, 0, 0, 0, dtype, false, s));
+    return cgpt_swiglu_forward(act, gate, up, static_cast<size_t>(M) * static_cast<size_t>(N), dtype, s);
+}
+
 unsigned int* tc_status_device_ptr() {
     static unsigned int* p = nullptr;   // one device per process
     if (p == nullptr) {
@@ -588,6 +612,14 @@ extern "C" int cgpt_linear_backward(void* dx, void* dw, void* db, const void* dy
         CGPT_TRY(column_sum(db, dy, T, O, accumulate_bias, dtype, s));
     }
     return CGPT_OK;
+}
+
+extern "C" int cgpt_linear_swiglu_forward(void* gate, void* up, void* activated, const void* x, const void* w_gate,
+                                          const void* w_up, size_t rows, size_t in_features, size_t intermediate, int dtype,
+                                          cgpt_stream_t stream) {
+    return linear_swiglu_dispatch(gate, up, activated, x, w_gate, w_up, static_cast<long long>(rows),
+                                  static_cast<long long>(intermediate), static_cast<long long>(in_features), dtype,
+                                  static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int cgpt_linear_backward_input_fused(void* dx, const void* const* dy, const void* const* w,

@@ -73,8 +73,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ GemmOperands ops, const _
     extern __shared__ unsigned char gemm_smem_raw[];
     const std::uint32_t raw = smem_u32(gemm_smem_raw);
     unsigned char* smem = gemm_smem_raw + ((1024u - (raw & 1023u)) & 1023u);
-    unsigned char* staging = smem + Cfg::kStages * Cfg::kStageBytes;   // 2 x [128 rows][128 B], 1024-byte aligned
-    std::uint64_t* bars = reinterpret_cast<std::uint64_t*>(staging + 2 * BM * 128);
+    unsigned char* staging = smem + Cfg::kStages * Cfg::kStageBytes;   // kStoreBufs x [128 rows][128 B], 1024-byte aligned
+    std::uint64_t* bars = reinterpret_cast<std::uint64_t*>(staging + Cfg::kStoreBufs * BM * 128);
     std::uint64_t* full = bars;
     std::uint64_t* empty = bars + Cfg::kStages;
     std::uint64_t* acc_full = bars + 2 * Cfg::kStages;       // [2]

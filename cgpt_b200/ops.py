@@ -103,6 +103,19 @@ def linear_backward(grad_input, grad_weight, grad_bias, grad_output, input, weig
                                    int(o.accumulate_bias), dtype_code(input), stream_ptr(stream)), "linear_backward")
 
 
+def linear_swiglu_forward(gate, up, activated, input, gate_weight, up_weight, stream=None):
+    """gate = input @ gate_weight.T, up = input @ up_weight.T, activated = swiglu(gate, up) in one launch
+    (cgpt_linear_swiglu_forward; the reference's block forward calls linear_forward twice and swiglu_forward)."""
+    _same_cuda_dtype("linear_swiglu_forward", gate, up, activated, input, gate_weight, up_weight)
+    inter, in_f = gate_weight.shape
+    rows = input.numel() // in_f
+    _require(up_weight.shape == gate_weight.shape and input.shape[-1] == in_f
+             and all(t.numel() == rows * inter and t.shape[-1] == inter for t in (gate, up, activated)),
+             "linear_swiglu_forward: incompatible shapes")
+    check(lib.cgpt_linear_swiglu_forward(ptr(gate), ptr(up), ptr(activated), ptr(input), ptr(gate_weight), ptr(up_weight),
+                                         rows, in_f, inter, dtype_code(input), stream_ptr(stream)), "linear_swiglu_forward")
+
+
 def linear_backward_input_fused(grad_input, grad_outputs, weights, stream=None, accumulate_input: bool = False):
     """grad_input (+)= sum_i grad_outputs[i] @ weights[i] for up to three projections of the same input, in one
     pass (cgpt_linear_backward_input_fused; the reference runs one accumulating linear_backward per projection)."""

@@ -88,6 +88,15 @@ int cgpt_linear_backward(void* dx, void* dw, void* db, const void* dy, const voi
                          size_t rows, size_t in_features, size_t out_features, int accumulate_input,
                          int accumulate_weight, int accumulate_bias, int dtype, cgpt_stream_t stream);
 
+/* Gate and up projections with the SwiGLU activation in the GEMM epilogue:
+ *      gate = X Wg^T, up = X Wu^T, activated = gate / (1 + exp(-gate)) * up      (all [rows, intermediate]).
+ * Replaces the sequence linear_forward, linear_forward, swiglu_forward of the block forward (reference
+ * src/core/transformer_block.cu:566-579, src/ops/swiglu.cu:69-71) with one launch: both projections are rounded to the
+ * storage dtype and written (the backward pass reads them), and the activation is computed from the rounded values, so
+ * results equal the three-call sequence. Runs as that sequence when the tensor-core path does not apply (fp32, unaligned). */
+int cgpt_linear_swiglu_forward(void* gate, void* up, void* activated, const void* x, const void* w_gate, const void* w_up,
+                               size_t rows, size_t in_features, size_t intermediate, int dtype, cgpt_stream_t stream);
+
 /* Input gradient of `count` (1..3) projections that read the same input, in one pass:
  *      dX[rows,in] (+)= sum_i dY_i[rows,out_i] W_i[out_i,in].
  * No single counterpart in the reference: it is what the block backward obtains from consecutive

@@ -125,3 +125,24 @@ def test_linear_backward_input_fused(ops, dtype, rows, in_f, outs):
     dx2 = base.clone()
     ops.linear_backward_input_fused(dx2, dys, ws, accumulate_input=True)
     assert_close(host(dx2), host(want + base.float()), TOL[dtype], f"fused dX accumulate {dtype}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,in_f,inter", [(256, 128, 128), (4096, 1024, 2048), (1000, 136, 200), (384, 256, 688)])
+def test_linear_swiglu_forward(ops, dtype, rows, in_f, inter):
+    """Fused gate/up/activation against the three separate operators (same rounding points) and the fp32 matmul."""
+    g = torch.Generator(device="cuda").manual_seed(rows + inter)
+    x = torch.randn(rows, in_f, generator=g, device="cuda").to(dtype)
+    wg = (torch.randn(inter, in_f, generator=g, device="cuda") * 0.1).to(dtype)
+    wu = (torch.randn(inter, in_f, generator=g, device="cuda") * 0.1).to(dtype)
+    gate, up, act = (torch.full((rows, inter), float("nan"), device="cuda", dtype=dtype) for _ in range(3))
+    ops.linear_swiglu_forward(gate, up, act, x, wg, wu)
+    g_ref, u_ref, a_ref = torch.empty_like(gate), torch.empty_like(up), torch.empty_like(act)
+    ops.linear_forward(g_ref, x, wg)
+    ops.linear_forward(u_ref, x, wu)
+    ops.swiglu_forward(a_ref, g_ref, u_ref)
+    torch.cuda.synchronize()
+    assert_close(host(gate), host(x.float() @ wg.float().t()), TOL[dtype], "gate vs fp32")
+    assert_close(host(up), host(x.float() @ wu.float().t()), TOL[dtype], "up vs fp32")
+    assert torch.equal(gate, g_ref) and torch.equal(up, u_ref), "projections differ from linear_forward"
+    assert torch.equal(act, a_ref), "activation differs from swiglu_forward on the stored projections"
