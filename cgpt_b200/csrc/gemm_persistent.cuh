@@ -234,7 +234,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ GemmOperands ops, const _
         }
     }
 
-    if (threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // TMA stores of this CTA are complete
+    if (threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the staging buffers have been read; the writes drain on their own
     if (failed) {
         atomicExch(&g_gemm_status, 1u);
         const unsigned long long t0 = globaltimer_ns();
