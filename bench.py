@@ -38,6 +38,13 @@ BATCH, SEQ = 32, 1024
 PUBLISHED_TOKENS_PER_S = 151400.0   # reference README.md:168 (4.62 steps/s at 32 x 1024, hardware not stated)
 
 
+# DRAM bytes of one launch of the dominant kernel, from an ncu capture of its most frequent large shape in the step
+# (profiles/gemm_tcgen05_persistent_32768x2048x1024.md): dram__bytes_read.sum 71.3 MB + dram__bytes_write.sum 77.3 MB.
+GEMM_TRAFFIC_BYTES = 148.6e6
+GEMM_TRAFFIC_NOTE = ("ncu, one launch of the 32768x2048x1024 forward GEMM (algorithmic A+B+C = 205.5 MB; part of C is still "
+                     "in L2 when the kernel ends); the step's 156 launches have other shapes, none re-reads its operands from DRAM")
+
+
 def workload_config(n_gpus: int) -> dict:
     return {"workload": "cgpt 104m preset training step (L8 d1024 Hq8/Hkv2 D128 I2048 V32000 tied), fp16 + fp32 master, "
                         "loss scale 1024, AdamW lr 3e-4 b(.9,.95) wd .1 clip 1.0, cut-cross-entropy loss",
@@ -241,7 +248,8 @@ def run_ours(args) -> None:
             if peak is None:
                 peak, which = 1400.0, "fallback (1.4 PFLOP/s sustained)"
             line["roofline"] = {"bound": "tensor", "achieved": gemm["tflops"], "peak": peak, "unit": "TFLOP/s",
-                                "frac": gemm["tflops"] / peak, "traffic": None, "kernel": "gemm_tcgen05_persistent_kernel",
+                                "frac": gemm["tflops"] / peak, "traffic": GEMM_TRAFFIC_BYTES,
+                                "traffic_note": GEMM_TRAFFIC_NOTE, "kernel": "gemm_tcgen05_persistent_kernel",
                                 "launches_per_step": gemm["launches"], "ms_per_step_in_kernel": gemm["ms"],
                                 "share_of_step": gemm["ms"] / ms_step, "peak_source": which,
                                 "model_flops_per_step": gemm["model_flops"], "model_tflops": gemm["model_flops"] / ms_step / 1e9}
