@@ -99,6 +99,7 @@ SIGNATURES = {
     "cgpt_b200_launch_count": (C.c_uint64, []),
     "cgpt_b200_device_status": (_i, [C.POINTER(C.c_uint), _i]),
     "cgpt_b200_reserve_scratch": (_i, [_sz]),
+    "cgpt_b200_set_branch_streams": (_i, [_i]),
     "cgpt_b200_gemm_timing": (_i, [_i]),
     "cgpt_b200_gemm_timing_read": (_i, [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(_u64)]),
     "cgpt_gemm": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _i, _i, _i, _i, _i, _vp]),

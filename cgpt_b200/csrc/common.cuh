@@ -61,6 +61,21 @@ private:
     std::size_t held_ = 0;
 };
 
+// While alive, scratch_get calls of this thread are served from arena `lane` (1 = ops issued on the side stream).
+struct ScratchLane {
+    explicit ScratchLane(int lane);
+    ~ScratchLane();
+    ScratchLane(const ScratchLane&) = delete;
+    ScratchLane& operator=(const ScratchLane&) = delete;
+
+private:
+    int previous_;
+};
+
+// Two-stream execution of the block's independent branches (runtime.cu).
+bool branch_streams_enabled();
+int side_stream_get(cudaStream_t main, cudaStream_t* side, cudaEvent_t* fork, cudaEvent_t* join);
+
 // ---------------------------------------------------------------------------------------------
 // Scalar conversion
 // ---------------------------------------------------------------------------------------------

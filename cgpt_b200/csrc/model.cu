@@ -11,6 +11,8 @@
 //     copies of the backward are folded into the RMSNorm-backward kernels (residual operands);
 //   * bias gradients are not computed (the model has no biases; the reference reduces them anyway);
 //   * one backward workspace serves all layers (the reference allocates one per layer).
+#include <cstdlib>
+
 #include "internal.h"
 
 using namespace cgpt;
@@ -51,7 +53,7 @@ struct Carver {
 };
 
 struct BlockScratch {
-    void *attn_proj, *ffn_out;                       // forward
+    void *attn_proj, *ffn_out, *norm_f;              // forward (norm_f: attention-norm output, not kept)
     void *d_act, *d_gate, *d_up, *d_ffn_norm_in;     // backward, MLP branch
     void *d_attn_out, *dq, *dk, *dv, *dq_pre, *dk_pre, *norm_a, *d_attn_norm_in;
     void *grad_a, *grad_b;                           // model backward ping-pong
@@ -66,6 +68,7 @@ BlockScratch carve(void* base, const Dims& m) {
     // forward and backward scratch never live at the same time, so they overlay each other
     s.attn_proj = c.take(rd);
     s.ffn_out = c.take(rd);
+    s.norm_f = c.take(rd);
     const std::size_t fwd_used = c.used;
     c.used = 0;
     s.d_act = c.take(ri);
@@ -86,6 +89,83 @@ BlockScratch carve(void* base, const Dims& m) {
     return s;
 }
 
+// The block is a parallel-residual block: its attention branch and its MLP branch both start from the block input
+// (forward) or from the output gradient (backward) and only meet again at the end. They are issued on two streams, the
+// caller's and the library's side stream, so that the memory-bound kernels of one branch (norms, QK-norm/RoPE, SwiGLU,
+// reductions) run underneath the tensor-core kernels of the other. Fork and join are event record/wait pairs, which
+// stream capture turns into graph edges; everything issued on the side stream takes library scratch from lane 1.
+struct Branches {
+    cudaStream_t main = nullptr, side = nullptr;
+    cudaEvent_t fork_event = nullptr, join_event = nullptr;
+    bool two = false;
+    int begin(cudaStream_t main_stream) {
+        main = main_stream;
+        side = main_stream;
+        two = false;
+        if (!branch_streams_enabled()) return CGPT_OK;
+        const int rc = side_stream_get(main_stream, &side, &fork_event, &join_event);
+        if (rc == CGPT_ERR_STATE) {   // first use inside a capture: run both branches on the caller's stream
+            side = main_stream;
+            return CGPT_OK;
+        }
+        CGPT_TRY(rc);
+        two = true;
+        return CGPT_OK;
+    }
+    int fork() const {
+        if (!two) return CGPT_OK;
+        CGPT_CUDA_TRY(cudaEventRecord(fork_event, main));
+        CGPT_CUDA_TRY(cudaStreamWaitEvent(side, fork_event, 0));
+        return CGPT_OK;
+    }
+    int join() const {
+        if (!two) return CGPT_OK;
+        CGPT_CUDA_TRY(cudaEventRecord(join_event, side));
+        CGPT_CUDA_TRY(cudaStreamWaitEvent(main, join_event, 0));
+        return CGPT_OK;
+    }
+    int lane() const { return two ? 1 : 0; }
+};
+
+int mlp_forward(const void* in, const cgpt_block_params* w, const cgpt_block_saved* sv, const BlockScratch& ws, const Dims& m,
+                int dt, float eps, cudaStream_t stream) {
+    CGPT_TRY(cgpt_rmsnorm_forward(sv->norm, in, w->ffn_norm, m.rows, m.d, eps, dt, stream));
+    // gate, up and the activation (two GEMMs and an activation pass in the reference, :566-579). The one-launch form
+    // (cgpt_linear_swiglu_forward, same results bit for bit) measured 300 us against 292 us for the three launches at
+    // the 104m shape, so the block uses it only on request: CGPT_B200_FUSED_SWIGLU=1.
+    static const bool fused_swiglu = [] { const char* e = std::getenv("CGPT_B200_FUSED_SWIGLU"); return e && e[0] == '1'; }();
+    if (fused_swiglu) {
+        CGPT_TRY(cgpt_linear_swiglu_forward(sv->gate, sv->up, sv->activated, sv->norm, w->gate_proj, w->up_proj, m.rows, m.d,
+                                            m.inter, dt, stream));
+    } else {
+        CGPT_TRY(cgpt_linear_forward(sv->gate, sv->norm, w->gate_proj, m.rows, m.d, m.inter, dt, stream));
+        CGPT_TRY(cgpt_linear_forward(sv->up, sv->norm, w->up_proj, m.rows, m.d, m.inter, dt, stream));
+        CGPT_TRY(cgpt_swiglu_forward(sv->activated, sv->gate, sv->up, m.rows * m.inter, dt, stream));
+    }
+    return cgpt_linear_forward(ws.ffn_out, sv->activated, w->down_proj, m.rows, m.inter, m.d, dt, stream);
+}
+
+// MLP branch of the backward (transformer_block.cu:663-681): ends with grad_in = grad_out + d(ffn_norm).
+int mlp_backward(void* grad_in, const void* grad_out, const void* in, const cgpt_block_params* w, const cgpt_block_params* g,
+                 const cgpt_block_saved* sv, const BlockScratch& ws, const Dims& m, int dt, float eps, cudaStream_t stream) {
+    CGPT_TRY(cgpt_linear_backward(ws.d_act, g->down_proj, nullptr, grad_out, sv->activated, w->down_proj, m.rows, m.inter,
+                                  m.d, 0, 0, 0, dt, stream));
+    CGPT_TRY(cgpt_swiglu_backward(ws.d_gate, ws.d_up, ws.d_act, sv->gate, sv->up, m.rows * m.inter, 0, 0, dt, stream));
+    {   // d(ffn norm output) = d_gate Wg + d_up Wu in one pass (the reference accumulates two GEMMs into the buffer)
+        const void* dys[2] = {ws.d_gate, ws.d_up};
+        const void* wts[2] = {w->gate_proj, w->up_proj};
+        const size_t outs[2] = {m.inter, m.inter};
+        CGPT_TRY(cgpt_linear_backward_input_fused(ws.d_ffn_norm_in, dys, wts, outs, 2, m.rows, m.d, 0, dt, stream));
+    }
+    CGPT_TRY(cgpt_linear_backward(nullptr, g->gate_proj, nullptr, ws.d_gate, sv->norm, nullptr, m.rows, m.d, m.inter, 0, 0, 0,
+                                  dt, stream));
+    CGPT_TRY(cgpt_linear_backward(nullptr, g->up_proj, nullptr, ws.d_up, sv->norm, nullptr, m.rows, m.d, m.inter, 0, 0, 0, dt,
+                                  stream));
+    // grad_in = grad_out + d(ffn_norm)  (the reference's D2D copy + add_inplace, :678-681)
+    return cgpt_rmsnorm_backward(grad_in, g->ffn_norm, ws.d_ffn_norm_in, in, w->ffn_norm, grad_out, nullptr, m.rows, m.d, eps,
+                                 dt, stream);
+}
+
 }  // namespace
 
 extern "C" size_t cgpt_block_workspace_bytes(const cgpt_model_config* cfg, size_t batch, size_t seq) {
@@ -104,11 +184,18 @@ extern "C" int cgpt_block_forward(void* out, const void* in, const cgpt_block_pa
     const BlockScratch ws = carve(workspace, m);
     const int dt = cfg->dtype;
     const float eps = cfg->rms_epsilon;
-    // attention branch
-    CGPT_TRY(cgpt_rmsnorm_forward(sv->norm, in, w->attention_norm, m.rows, m.d, eps, dt, stream));
-    CGPT_TRY(cgpt_linear_forward(sv->query_pre_norm, sv->norm, w->q_projection, m.rows, m.d, m.qdim, dt, stream));
-    CGPT_TRY(cgpt_linear_forward(sv->key_pre_norm, sv->norm, w->k_projection, m.rows, m.d, m.kvdim, dt, stream));
-    CGPT_TRY(cgpt_linear_forward(sv->value, sv->norm, w->v_projection, m.rows, m.d, m.kvdim, dt, stream));
+    Branches br;
+    CGPT_TRY(br.begin(static_cast<cudaStream_t>(stream)));
+    CGPT_TRY(br.fork());
+    {   // MLP branch on the same block input (parallel residual), on the side stream
+        ScratchLane lane(br.lane());
+        CGPT_TRY(mlp_forward(in, w, sv, ws, m, dt, eps, br.side));
+    }
+    // attention branch on the caller's stream; its norm output is not kept (sv->norm holds the FFN norm's)
+    CGPT_TRY(cgpt_rmsnorm_forward(ws.norm_f, in, w->attention_norm, m.rows, m.d, eps, dt, stream));
+    CGPT_TRY(cgpt_linear_forward(sv->query_pre_norm, ws.norm_f, w->q_projection, m.rows, m.d, m.qdim, dt, stream));
+    CGPT_TRY(cgpt_linear_forward(sv->key_pre_norm, ws.norm_f, w->k_projection, m.rows, m.d, m.kvdim, dt, stream));
+    CGPT_TRY(cgpt_linear_forward(sv->value, ws.norm_f, w->v_projection, m.rows, m.d, m.kvdim, dt, stream));
     {   // per-head QK-norm then RoPE: one fused pass when the shape allows it, else the three separate ops
         int rc = cgpt_qknorm_rope_forward(sv->query, sv->key, sv->query_pre_norm, sv->key_pre_norm, w->q_norm, w->k_norm,
                                           cos_table, sin_table, batch, seq, m.hq, m.hkv, m.hd, cfg->rotary_dim,
@@ -124,21 +211,7 @@ extern "C" int cgpt_block_forward(void* out, const void* in, const cgpt_block_pa
     CGPT_TRY(cgpt_attention_forward(sv->attention_output, sv->attention_logsumexp, sv->query, sv->key, sv->value, batch,
                                     seq, seq, m.hq, m.hkv, m.hd, 0.0f, 1, position_offset, dt, 0, stream));
     CGPT_TRY(cgpt_linear_forward(ws.attn_proj, sv->attention_output, w->o_projection, m.rows, m.qdim, m.d, dt, stream));
-    // MLP branch on the same block input (parallel residual)
-    CGPT_TRY(cgpt_rmsnorm_forward(sv->norm, in, w->ffn_norm, m.rows, m.d, eps, dt, stream));
-    // gate, up and the activation (two GEMMs and an activation pass in the reference, :566-579). The one-launch form
-    // (cgpt_linear_swiglu_forward, same results bit for bit) measured 300 us against 292 us for the three launches at
-    // the 104m shape, so the block uses it only on request: CGPT_B200_FUSED_SWIGLU=1.
-    static const bool fused_swiglu = [] { const char* e = std::getenv("CGPT_B200_FUSED_SWIGLU"); return e && e[0] == '1'; }();
-    if (fused_swiglu) {
-        CGPT_TRY(cgpt_linear_swiglu_forward(sv->gate, sv->up, sv->activated, sv->norm, w->gate_proj, w->up_proj, m.rows, m.d,
-                                            m.inter, dt, stream));
-    } else {
-        CGPT_TRY(cgpt_linear_forward(sv->gate, sv->norm, w->gate_proj, m.rows, m.d, m.inter, dt, stream));
-        CGPT_TRY(cgpt_linear_forward(sv->up, sv->norm, w->up_proj, m.rows, m.d, m.inter, dt, stream));
-        CGPT_TRY(cgpt_swiglu_forward(sv->activated, sv->gate, sv->up, m.rows * m.inter, dt, stream));
-    }
-    CGPT_TRY(cgpt_linear_forward(ws.ffn_out, sv->activated, w->down_proj, m.rows, m.inter, m.d, dt, stream));
+    CGPT_TRY(br.join());
     return cgpt_add(out, in, ws.attn_proj, ws.ffn_out, m.rows * m.d, dt, stream);
 }
 
@@ -152,23 +225,13 @@ extern "C" int cgpt_block_backward(void* grad_in, const void* grad_out, const vo
     const BlockScratch ws = carve(workspace, m);
     const int dt = cfg->dtype;
     const float eps = cfg->rms_epsilon;
-    // ---- MLP branch (transformer_block.cu:663-675)
-    CGPT_TRY(cgpt_linear_backward(ws.d_act, g->down_proj, nullptr, grad_out, sv->activated, w->down_proj, m.rows, m.inter,
-                                  m.d, 0, 0, 0, dt, stream));
-    CGPT_TRY(cgpt_swiglu_backward(ws.d_gate, ws.d_up, ws.d_act, sv->gate, sv->up, m.rows * m.inter, 0, 0, dt, stream));
-    {   // d(ffn norm output) = d_gate Wg + d_up Wu in one pass (the reference accumulates two GEMMs into the buffer)
-        const void* dys[2] = {ws.d_gate, ws.d_up};
-        const void* wts[2] = {w->gate_proj, w->up_proj};
-        const size_t outs[2] = {m.inter, m.inter};
-        CGPT_TRY(cgpt_linear_backward_input_fused(ws.d_ffn_norm_in, dys, wts, outs, 2, m.rows, m.d, 0, dt, stream));
+    Branches br;
+    CGPT_TRY(br.begin(static_cast<cudaStream_t>(stream)));
+    CGPT_TRY(br.fork());
+    {   // ---- MLP branch on the side stream; it writes grad_in = grad_out + d(ffn_norm)
+        ScratchLane lane(br.lane());
+        CGPT_TRY(mlp_backward(grad_in, grad_out, in, w, g, sv, ws, m, dt, eps, br.side));
     }
-    CGPT_TRY(cgpt_linear_backward(nullptr, g->gate_proj, nullptr, ws.d_gate, sv->norm, nullptr, m.rows, m.d, m.inter, 0, 0, 0,
-                                  dt, stream));
-    CGPT_TRY(cgpt_linear_backward(nullptr, g->up_proj, nullptr, ws.d_up, sv->norm, nullptr, m.rows, m.d, m.inter, 0, 0, 0, dt,
-                                  stream));
-    // grad_in = grad_out + d(ffn_norm)  (the reference's D2D copy + add_inplace, :678-681)
-    CGPT_TRY(cgpt_rmsnorm_backward(grad_in, g->ffn_norm, ws.d_ffn_norm_in, in, w->ffn_norm, grad_out, nullptr, m.rows, m.d,
-                                   eps, dt, stream));
     // ---- attention branch (:682-747)
     CGPT_TRY(cgpt_linear_backward(ws.d_attn_out, g->o_projection, nullptr, grad_out, sv->attention_output, w->o_projection,
                                   m.rows, m.qdim, m.d, 0, 0, 0, dt, stream));
@@ -204,7 +267,8 @@ extern "C" int cgpt_block_backward(void* grad_in, const void* grad_out, const vo
                                   0, dt, stream));
     CGPT_TRY(cgpt_linear_backward(nullptr, g->v_projection, nullptr, ws.dv, ws.norm_a, nullptr, m.rows, m.d, m.kvdim, 0, 0, 0,
                                   dt, stream));
-    // grad_in += d(attention_norm)
+    // grad_in += d(attention_norm): needs the MLP branch's grad_in
+    CGPT_TRY(br.join());
     return cgpt_rmsnorm_backward(grad_in, g->attention_norm, ws.d_attn_norm_in, in, w->attention_norm, grad_in, nullptr,
                                  m.rows, m.d, eps, dt, stream);
 }

@@ -3,6 +3,8 @@ from __future__ import annotations
 
 import ctypes as C
 
+import os
+
 import torch
 
 from ._lib import check, lib
@@ -28,14 +30,20 @@ def time_gemms(train_step, steps: int = 2) -> dict:
     """Runs `steps` eager (non-graph) model steps with event pairs around every tensor-core GEMM launch and returns
     the per-step totals: ms inside the kernel, algorithmic TFLOP/s, launches, and the model FLOPs of a step."""
     ts = train_step
+    # one stream for this pass: with the block's two branches on two streams a GEMM's event pair would also span the
+    # time it waits for SMs held by the other branch's kernels
+    check(lib.cgpt_b200_set_branch_streams(0), "set_branch_streams")
     check(lib.cgpt_b200_gemm_timing(1), "gemm_timing")
-    with torch.cuda.stream(ts.stream):
-        for _ in range(steps):
-            ts.enqueue_model_step()
-    ts.stream.synchronize()
-    ms, fl, n = C.c_double(0), C.c_double(0), C.c_uint64(0)
-    check(lib.cgpt_b200_gemm_timing_read(C.byref(ms), C.byref(fl), C.byref(n)), "gemm_timing_read")
-    check(lib.cgpt_b200_gemm_timing(0), "gemm_timing")
+    try:
+        with torch.cuda.stream(ts.stream):
+            for _ in range(steps):
+                ts.enqueue_model_step()
+        ts.stream.synchronize()
+        ms, fl, n = C.c_double(0), C.c_double(0), C.c_uint64(0)
+        check(lib.cgpt_b200_gemm_timing_read(C.byref(ms), C.byref(fl), C.byref(n)), "gemm_timing_read")
+    finally:
+        check(lib.cgpt_b200_gemm_timing(0), "gemm_timing")
+        check(lib.cgpt_b200_set_branch_streams(int(os.environ.get("CGPT_B200_BRANCH_STREAMS", "0") == "1")), "set_branch_streams")
     tokens = ts.batch * ts.seq
     model = (model_flops_per_token(ts.options) + attention_flops_per_token(ts.options, ts.seq)) * tokens
     return {"ms": ms.value / steps, "tflops": fl.value / ms.value / 1e9 if ms.value > 0 else 0.0,

@@ -55,6 +55,17 @@ uint64_t cgpt_b200_launch_count(void);
  * those kernels (on an mbarrier fed by TMA or by tcgen05.commit) is bounded; a kernel whose wait ran out
  * sets the word to non-zero and returns. Synchronises the device. */
 int cgpt_b200_device_status(unsigned int* status_out, int clear);
+/* The transformer block's attention branch and MLP branch are independent until the block's last operation (parallel
+ * residual; reference src/core/transformer_block.cu:466-595, :644-748 issues them one after the other on one stream).
+ * When enabled, cgpt_block_forward / cgpt_block_backward (and the model functions built on them) issue the MLP branch on
+ * a side stream owned by the library, forked from and joined back into the caller's stream with events, so that the memory-bound
+ * kernels of one branch run underneath the tensor-core kernels of the other. Under stream capture the fork and join
+ * become graph edges. The side stream is created by the first call on a device, which must therefore be made outside
+ * of a capture (a first call inside a capture runs both branches on the caller's stream). enable = 0 (the initial
+ * state unless the environment variable CGPT_B200_BRANCH_STREAMS=1 is set) keeps both branches on the caller's stream:
+ * the 104m training step is power-capped on B200 and gained only 0.3-0.6 % from the overlap. */
+int cgpt_b200_set_branch_streams(int enable);
+
 /* Measurement aid for benchmarks: with enable != 0 the library records a CUDA event pair around every
  * tensor-core GEMM launch (eager mode only; do not enable while capturing a graph) together with the
  * launch's algorithmic FLOPs (2*m*n*k); cgpt_b200_gemm_timing_read synchronises the device and returns the

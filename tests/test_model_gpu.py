@@ -213,3 +213,30 @@ def test_loss_after_50_identical_steps(M):
     assert gpu_losses[-1] < gpu_losses[0] - 0.05, "training must reduce the loss"
     assert abs(gpu_losses[0] - cpu_losses[0]) <= 1e-3
     assert abs(gpu_losses[-1] - cpu_losses[-1]) <= 1e-3, (gpu_losses[-1], cpu_losses[-1])
+
+
+def test_two_stream_branches_match_one_stream():
+    """The block's MLP branch on the library's side stream (fork/join by events, also inside a captured graph) gives
+    bit-identical gradients and weights to the single-stream order."""
+    from cgpt_b200 import _lib
+    from cgpt_b200 import model as M, optim as OPT
+    from cgpt_b200.train import TrainStep
+    opts = M.TransformerModelOptions(512, 2, M.TransformerBlockOptions(256, 512, 2, 1, 128, 128))
+    ids = torch.randint(0, 512, (2 * 128,), dtype=torch.int32)
+    results = []
+    for enable, graph in ((0, False), (1, False), (1, True)):
+        _lib.check(_lib.lib.cgpt_b200_set_branch_streams(enable), "set_branch_streams")
+        try:
+            ts = TrainStep(opts, 2, 128, seed=3, use_graph=graph, adamw=OPT.AdamWOptions(3e-4, 0.9, 0.95, 1e-8, 0.1, 1024.0, 1.0))
+            ts.token_ids.copy_(ids)
+            ts.targets.copy_(torch.roll(ids, -1))
+            for _ in range(3):
+                ts.step()
+            loss = ts.read_loss()
+            assert ts.check() and _lib.device_status() == 0
+            results.append((loss, ts.storage.flat_gradients.clone(), ts.storage.token_embedding.clone()))
+        finally:
+            _lib.check(_lib.lib.cgpt_b200_set_branch_streams(0), "set_branch_streams")
+    for loss, grads, emb in results[1:]:
+        assert loss == results[0][0]
+        assert torch.equal(grads, results[0][1]) and torch.equal(emb, results[0][2])
