@@ -95,6 +95,7 @@ SIGNATURES = {
     "cgpt_block_backward": (_i, [_vp, _vp, _vp, _pBP, _pBP, _pBS, _vp, _vp, _vp, _pMC, _sz, _sz, _sz, _vp]),
     "cgpt_model_forward": (_i, [_vp, _vp, _pMT, _pMS, _vp, _vp, _vp, _pMC, _sz, _sz, _vp]),
     "cgpt_model_backward": (_i, [_vp, _vp, _vp, _pMT, _pMT, _pMS, _vp, _vp, _vp, _pMC, _sz, _sz, _vp]),
+    "cgpt_model_backward_steps": (_i, [_vp, _vp, _vp, _pMT, _pMT, _pMS, _vp, _vp, _vp, _pMC, _sz, _sz, _sz, _sz, _vp]),
     "cgpt_b200_version": (C.c_char_p, []),
     "cgpt_b200_launch_count": (C.c_uint64, []),
     "cgpt_b200_device_status": (_i, [C.POINTER(C.c_uint), _i]),

@@ -294,34 +294,51 @@ extern "C" int cgpt_model_forward(void* logits, const uint32_t* token_ids, const
     return CGPT_OK;
 }
 
-extern "C" int cgpt_model_backward(const void* grad_logits, void* grad_normalized, const uint32_t* token_ids,
-                                   const cgpt_model_tensors* w, const cgpt_model_tensors* g, const cgpt_model_saved* sv,
-                                   void* workspace, const void* cos_table, const void* sin_table,
-                                   const cgpt_model_config* cfg, size_t batch, size_t seq, cgpt_stream_t stream) {
+extern "C" int cgpt_model_backward_steps(const void* grad_logits, void* grad_normalized, const uint32_t* token_ids,
+                                         const cgpt_model_tensors* w, const cgpt_model_tensors* g, const cgpt_model_saved* sv,
+                                         void* workspace, const void* cos_table, const void* sin_table,
+                                         const cgpt_model_config* cfg, size_t batch, size_t seq, size_t step_begin,
+                                         size_t step_end, cgpt_stream_t stream) {
     if (!grad_normalized || !token_ids || !w || !g || !sv || !workspace || !w->layers || !g->layers || !sv->layers ||
         !sv->layer_inputs)
         return CGPT_ERR_NULL;
     Dims m;
     CGPT_TRY(check_cfg(cfg, batch, seq, &m));
+    const std::size_t L = cfg->layers;
+    if (step_begin > step_end || step_end > L + 2) return CGPT_ERR_SHAPE;
     const BlockScratch ws = carve(workspace, m);
     const int dt = cfg->dtype;
-    if (grad_logits != nullptr) {  // transformer_model.cu:358-361
-        CGPT_TRY(cgpt_linear_backward(grad_normalized, g->lm_head, nullptr, grad_logits, sv->normalized, w->lm_head, m.rows,
-                                      m.d, cfg->vocab, 0, 0, 0, dt, stream));
+    for (std::size_t step = step_begin; step < step_end; ++step) {
+        if (step == 0) {
+            if (grad_logits != nullptr) {  // transformer_model.cu:358-361
+                CGPT_TRY(cgpt_linear_backward(grad_normalized, g->lm_head, nullptr, grad_logits, sv->normalized, w->lm_head,
+                                              m.rows, m.d, cfg->vocab, 0, 0, 0, dt, stream));
+            }
+            CGPT_TRY(cgpt_rmsnorm_backward(ws.grad_a, g->final_norm, grad_normalized, sv->hidden, w->final_norm, nullptr,
+                                           nullptr, m.rows, m.d, cfg->rms_epsilon, dt, stream));
+        } else if (step <= L) {
+            // the gradient ping-pongs between grad_a and grad_b: step s reads the buffer step s-1 wrote
+            const std::size_t l = L - step;
+            void* in_grad = (step % 2 == 1) ? ws.grad_a : ws.grad_b;
+            void* out_grad = (step % 2 == 1) ? ws.grad_b : ws.grad_a;
+            CGPT_TRY(cgpt_block_backward(out_grad, in_grad, sv->layer_inputs[l], &w->layers[l], &g->layers[l], &sv->layers[l],
+                                         workspace, cos_table, sin_table, cfg, batch, seq, 0, stream));
+        } else {
+            // transformer_model.cu:375-380: tied embeddings add the lookup gradient into the LM-head gradient
+            const void* last = (L % 2 == 0) ? ws.grad_a : ws.grad_b;
+            const bool tied = cfg->tied_embeddings != 0;
+            CGPT_TRY(cgpt_embedding_backward(tied ? g->lm_head : g->token_embedding, last, token_ids, m.rows, cfg->vocab, m.d, 1,
+                                             tied ? 1 : 0, dt, stream));
+        }
     }
-    void* current = ws.grad_a;
-    void* previous = ws.grad_b;
-    CGPT_TRY(cgpt_rmsnorm_backward(current, g->final_norm, grad_normalized, sv->hidden, w->final_norm, nullptr, nullptr,
-                                   m.rows, m.d, cfg->rms_epsilon, dt, stream));
-    for (std::size_t l = cfg->layers; l-- > 0;) {
-        CGPT_TRY(cgpt_block_backward(previous, current, sv->layer_inputs[l], &w->layers[l], &g->layers[l], &sv->layers[l],
-                                     workspace, cos_table, sin_table, cfg, batch, seq, 0, stream));
-        void* t = current;
-        current = previous;
-        previous = t;
-    }
-    // transformer_model.cu:375-380: tied embeddings add the lookup gradient into the LM-head gradient
-    const bool tied = cfg->tied_embeddings != 0;
-    return cgpt_embedding_backward(tied ? g->lm_head : g->token_embedding, current, token_ids, m.rows, cfg->vocab, m.d, 1,
-                                   tied ? 1 : 0, dt, stream);
+    return CGPT_OK;
+}
+
+extern "C" int cgpt_model_backward(const void* grad_logits, void* grad_normalized, const uint32_t* token_ids,
+                                   const cgpt_model_tensors* w, const cgpt_model_tensors* g, const cgpt_model_saved* sv,
+                                   void* workspace, const void* cos_table, const void* sin_table,
+                                   const cgpt_model_config* cfg, size_t batch, size_t seq, cgpt_stream_t stream) {
+    if (!cfg) return CGPT_ERR_NULL;
+    return cgpt_model_backward_steps(grad_logits, grad_normalized, token_ids, w, g, sv, workspace, cos_table, sin_table, cfg, batch,
+                                     seq, 0, static_cast<size_t>(cfg->layers) + 2, stream);
 }

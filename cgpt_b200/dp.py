@@ -37,3 +37,40 @@ def allreduce_buckets(buckets, group=None, async_op: bool = False):
         if async_op:
             works.append(w)
     return works
+
+
+class BucketReducer:
+    """Starts the all-reduce of each bucket as soon as the backward has finished every gradient in it.
+
+    ``buckets`` are consecutive views of one flat buffer whose storage order is the order in which the backward
+    finishes gradients. ``advance(final_elements)`` is called after a piece of the backward with the number of
+    leading elements that are now final; every bucket that lies entirely below that mark and has not been started is
+    reduced asynchronously (the collective runs on the communication stream and overlaps the rest of the backward).
+    ``finish()`` starts whatever is left and waits for all of them."""
+
+    def __init__(self, buckets, group=None):
+        self.buckets = list(buckets)
+        self.group = group
+        self.ends = []
+        total = 0
+        for b in self.buckets:
+            total += b.numel()
+            self.ends.append(total)
+        self.started = 0
+        self.works = []
+
+    def advance(self, final_elements: int) -> int:
+        """Returns how many buckets were started by this call."""
+        n = 0
+        while self.started < len(self.buckets) and self.ends[self.started] <= final_elements:
+            self.works.append(dist.all_reduce(self.buckets[self.started], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+            self.started += 1
+            n += 1
+        return n
+
+    def finish(self) -> None:
+        self.advance(self.ends[-1] if self.ends else 0)
+        for w in self.works:
+            w.wait()
+        self.works = []
+        self.started = 0

@@ -231,6 +231,23 @@ class ModelStorage:
         self.g_final_norm = view("final_norm", self.final_norm)
         self.g_layers = [{n: view(f"layers.{li}.{n}", t) for n, t in layer.items()} for li, layer in enumerate(self.layers)]
 
+    def final_gradient_elements(self, steps_done: int) -> int:
+        """Elements at the start of ``flat_gradients`` that are final once the backward has run steps
+        0 .. steps_done-1 (0 = final norm, 1..layers = blocks from the last to the first, layers+1 = embedding).
+        The buffer is laid out in exactly that order; with tied embeddings the LM-head gradient shares the
+        embedding's slot and only becomes final with the last step."""
+        L = self.options.num_layers
+        if steps_done <= 0:
+            return 0
+        if steps_done >= L + 2:
+            return self.flat_gradients.numel()
+        if steps_done == L + 1:
+            # all blocks done; an untied LM-head gradient was already complete before the backward started
+            return self.gradient_offsets["token_embedding"]
+        # steps 0 .. steps_done-1 finished the final norm and blocks L-1 .. L-steps_done+1: the next block's first
+        # tensor (the layout lists a block's tensors in reverse field order) is where the final prefix ends
+        return self.gradient_offsets[f"layers.{L - steps_done}.{BLOCK_PARAM_FIELDS[-1]}"]
+
     def parameters_and_gradients(self):
         """(parameter, gradient) pairs in the trainer's order (train/train.cpp:302-320)."""
         pairs = [(self.token_embedding, self.g_token_embedding)]
@@ -304,10 +321,13 @@ def transformer_model_forward(logits, device_token_ids, batch_size, sequence_len
 def transformer_model_backward(grad_logits, device_token_ids, batch_size, sequence_length, storage: ModelStorage,
                                forward_workspace: TransformerModelWorkspace,
                                backward_workspace: TransformerModelBackwardWorkspace, cos_cache, sin_cache,
-                               cublas_context, stream, options: TransformerModelOptions):
+                               cublas_context, stream, options: TransformerModelOptions,
+                               steps: tuple[int, int] | None = None):
     """transformer_model_backward (include/core/transformer_model.h:176-190). ``grad_logits=None`` starts from
     ``backward_workspace.grad_normalized`` (already written by the cut-cross-entropy loss together with the
-    LM-head gradient)."""
+    LM-head gradient). ``steps=(begin, end)`` runs only that range of the backward's steps (0 = final norm,
+    1..layers = blocks from last to first, layers+1 = embedding), for drivers that start reducing finished
+    gradients in between; the default runs all of them."""
     if device_token_ids is None or batch_size == 0 or sequence_length == 0 or len(storage.g_layers) != options.num_layers:
         raise _lib.CgptInvalidArgument("transformer model backward: invalid model state or token IDs")
     rows = batch_size * sequence_length
@@ -315,10 +335,12 @@ def transformer_model_backward(grad_logits, device_token_ids, batch_size, sequen
         raise _lib.CgptInvalidArgument("transformer model backward: invalid logits gradient or workspace shape")
     cfg = _config(options, storage.dtype, cos_cache.shape[0], storage.tied)
     w, g, keep = _model_structs(storage)
-    check(lib.cgpt_model_backward(ptr(grad_logits), ptr(backward_workspace.grad_normalized), ptr(device_token_ids),
-                                  C.byref(w), C.byref(g), C.byref(forward_workspace.c),
-                                  backward_workspace.block.buffer.data_ptr(), ptr(cos_cache), ptr(sin_cache), C.byref(cfg),
-                                  batch_size, sequence_length, stream_ptr(stream)), "transformer_model_backward")
+    begin, end = steps if steps is not None else (0, options.num_layers + 2)
+    check(lib.cgpt_model_backward_steps(ptr(grad_logits), ptr(backward_workspace.grad_normalized), ptr(device_token_ids),
+                                        C.byref(w), C.byref(g), C.byref(forward_workspace.c),
+                                        backward_workspace.block.buffer.data_ptr(), ptr(cos_cache), ptr(sin_cache),
+                                        C.byref(cfg), batch_size, sequence_length, begin, end, stream_ptr(stream)),
+          "transformer_model_backward")
     return keep
 
 

@@ -18,7 +18,8 @@ from . import optim as O
 class TrainStep:
     def __init__(self, options: M.TransformerModelOptions, batch: int, seq: int, *, dtype=torch.float16, seed: int = 0,
                  loss_scale: float = 1024.0, adamw: O.AdamWOptions | None = None, process_group=None,
-                 bucket_bytes: int = 48 << 20, use_graph: bool = True, cce_chunk_rows: int = 0, device="cuda"):
+                 bucket_bytes: int = 48 << 20, use_graph: bool = True, cce_chunk_rows: int = 0, device="cuda",
+                 overlap_allreduce: bool | None = None):
         self.options, self.batch, self.seq, self.dtype = options, batch, seq, dtype
         self.rows = batch * seq
         self.pg = process_group
@@ -41,8 +42,12 @@ class TrainStep:
         self.adamw_workspace = O.AdamWWorkspace()
         self.stream = torch.cuda.Stream(device=device)
         self.graph = None
-        self.use_graph = use_graph
+        # With more than one rank the bucketed all-reduce overlaps the backward: the step is then issued eagerly, piece by
+        # piece (a captured graph would have to contain the collectives); one rank replays the captured graph.
+        self.overlap_allreduce = (self.world > 1) if overlap_allreduce is None else (overlap_allreduce and self.world > 1)
+        self.use_graph = use_graph and not self.overlap_allreduce
         self._buckets = self._make_buckets(bucket_bytes)
+        self._reducer = dp.BucketReducer(self._buckets, self.pg) if self.overlap_allreduce else None
         self._keep = None
 
     # ------------------------------------------------------------------------------------------ pieces
@@ -64,12 +69,23 @@ class TrainStep:
         M.cut_cross_entropy_forward_backward(self.loss, bw.grad_normalized, st.g_lm_head, ws.normalized, st.lm_head,
                                              self.targets, self.rows, None, dp.gradient_scale(self.loss_scale, self.world),
                                              chunk_rows=self.cce_chunk_rows)
-        k2 = M.transformer_model_backward(None, self.token_ids, self.batch, self.seq, st, ws, bw, self.cos, self.sin,
-                                          None, None, o)
+        if self._reducer is None:
+            k2 = M.transformer_model_backward(None, self.token_ids, self.batch, self.seq, st, ws, bw, self.cos, self.sin,
+                                              None, None, o)
+        else:
+            # backward step by step; after each, the buckets that are complete go out on the communication stream
+            k2 = None
+            for step in range(o.num_layers + 2):
+                k2 = M.transformer_model_backward(None, self.token_ids, self.batch, self.seq, st, ws, bw, self.cos,
+                                                  self.sin, None, None, o, steps=(step, step + 1))
+                self._reducer.advance(st.final_gradient_elements(step + 1))
         self._keep = (k1, k2)
 
     def _allreduce_gradients(self) -> None:
         if self.world == 1:
+            return
+        if self._reducer is not None:
+            self._reducer.finish()      # the collectives were started during the backward
             return
         dp.allreduce_buckets(self._buckets, group=self.pg)
 

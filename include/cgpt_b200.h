@@ -415,6 +415,17 @@ int cgpt_model_backward(const void* grad_logits, void* grad_normalized, const ui
                         const cgpt_model_tensors* weights, const cgpt_model_tensors* grads,
                         const cgpt_model_saved* saved, void* workspace, const void* cos_table, const void* sin_table,
                         const cgpt_model_config* cfg, size_t batch, size_t seq, cgpt_stream_t stream);
+/* The same backward in pieces, for callers that interleave it with other work (a data-parallel driver starts the
+ * all-reduce of the gradients that are already final). Steps: 0 = LM head (if grad_logits) + final norm,
+ * 1 .. layers = the blocks from the last to the first (step s is layer `layers - s`), layers + 1 = embedding.
+ * Runs steps [step_begin, step_end); consecutive calls on one stream covering 0 .. layers + 2 in order equal one
+ * cgpt_model_backward call (which is implemented as exactly that). The reference has only the whole-model call
+ * (include/core/transformer_model.h:176-190). */
+int cgpt_model_backward_steps(const void* grad_logits, void* grad_normalized, const uint32_t* token_ids,
+                              const cgpt_model_tensors* weights, const cgpt_model_tensors* grads,
+                              const cgpt_model_saved* saved, void* workspace, const void* cos_table,
+                              const void* sin_table, const cgpt_model_config* cfg, size_t batch, size_t seq,
+                              size_t step_begin, size_t step_end, cgpt_stream_t stream);
 
 #ifdef __cplusplus
 } /* extern "C" */

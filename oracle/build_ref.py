@@ -1,4 +1,5 @@
-"""Builds the reference's own CPU operators into ``oracle/_ref/libcgpt_ref_cpu.so`` (TEST INFRASTRUCTURE).
+"""Builds the reference's own CPU operators into ``oracle/_ref/libcgpt_ref_cpu.so`` and its own CUDA operators, for
+sm_100a, into ``oracle/_ref/libcgpt_ref_cuda.so`` (TEST INFRASTRUCTURE).
 
 Sources are compiled where they lie under the reference checkout (default ``/root/reference``); nothing
 is copied. The only file of this repository in the link is ``oracle/ref_wrap.cpp``, a flat C wrapper.
@@ -34,6 +35,18 @@ CPU_SOURCES = [
 ]
 CUDA_SOURCES = ["src/core/tensor.cu", "src/optim/adamw.cu"]  # host code paths only are exercised
 
+# The reference's GPU operators (everything on the path except the cuBLASLt-based linear files), for the second
+# library oracle/_ref/libcgpt_ref_cuda.so: the reference's own kernels, rebuilt for sm_100a.
+LIB_CUDA = OUT / "libcgpt_ref_cuda.so"
+GPU_SOURCES = [
+    "src/core/tensor.cu", "src/ops/attention.cu", "src/ops/cross_entropy.cu", "src/ops/cut_cross_entropy.cu",
+    "src/ops/embedding.cu", "src/ops/rmsnorm.cu", "src/ops/rope.cu", "src/ops/softmax.cu", "src/ops/swiglu.cu",
+    "src/ops/backward/attention_backward.cu", "src/ops/backward/embedding_backward.cu",
+    "src/ops/backward/rmsnorm_backward.cu", "src/ops/backward/rope_backward.cu", "src/ops/backward/swiglu_backward.cu",
+]
+# per-file options of the reference's CMakeLists.txt:54
+FAST_MATH = {"src/ops/cross_entropy.cu", "src/ops/softmax.cu"}
+
 
 def build(reference: Path, force: bool = False) -> Path | None:
     if not (reference / "src" / "ops" / "cpu").is_dir():
@@ -43,6 +56,7 @@ def build(reference: Path, force: bool = False) -> Path | None:
     wrap = HERE / "ref_wrap.cpp"
     inputs = [reference / s for s in CPU_SOURCES + CUDA_SOURCES] + [wrap]
     if LIB.exists() and not force and all(LIB.stat().st_mtime > p.stat().st_mtime for p in inputs):
+        build_cuda(reference, force)
         return LIB
     inc = ["-I", str(reference / "include"), "-I", str(reference / "include" / "core"), "-I", "/usr/local/cuda/include"]
     cxx = ["/usr/bin/g++", "-std=c++20", "-O3", "-mavx2", "-mfma", "-mf16c", "-fopenmp", "-fPIC", "-include", "cstdint",
@@ -75,7 +89,47 @@ def build(reference: Path, force: bool = False) -> Path | None:
          *map(str, objects)])
     for o in objects:
         o.unlink(missing_ok=True)
+    build_cuda(reference, force)
     return LIB
+
+
+def build_cuda(reference: Path, force: bool = False) -> Path | None:
+    """The reference's CUDA operators + oracle/ref_wrap_cuda.cpp -> oracle/_ref/libcgpt_ref_cuda.so (sm_100a)."""
+    wrap = HERE / "ref_wrap_cuda.cpp"
+    inputs = [reference / s for s in GPU_SOURCES + CPU_SOURCES] + [wrap]
+    if LIB_CUDA.exists() and not force and all(LIB_CUDA.stat().st_mtime > p.stat().st_mtime for p in inputs):
+        return LIB_CUDA
+    inc = ["-I", str(reference / "include"), "-I", str(reference / "include" / "core"), "-I", "/usr/local/cuda/include"]
+    nvcc = ["/usr/local/cuda/bin/nvcc", "-ccbin", "/usr/bin/g++", "-std=c++20", "-O3", "-include", "cstdint",
+            "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC,-fopenmp", "-DCGPT_ENABLE_OPENMP=1", *inc]
+    cxx = ["/usr/bin/g++", "-std=c++20", "-O3", "-mavx2", "-mfma", "-mf16c", "-fopenmp", "-fPIC", "-include", "cstdint",
+           "-DCGPT_ENABLE_OPENMP=1", *inc]
+    jobs, objects = [], []
+    for rel in GPU_SOURCES:
+        obj = OUT / ("gpu_" + rel.replace("/", "_") + ".o")
+        objects.append(obj)
+        jobs.append([*nvcc, *(["--use_fast_math"] if rel in FAST_MATH else []), "-c", str(reference / rel), "-o", str(obj)])
+    for rel in CPU_SOURCES:   # the GPU entry points dispatch to these for CPU tensors, so the symbols must resolve
+        obj = OUT / ("gpu_" + rel.replace("/", "_") + ".o")
+        objects.append(obj)
+        jobs.append([*cxx, "-c", str(reference / rel), "-o", str(obj)])
+    obj = OUT / "ref_wrap_cuda.o"
+    objects.append(obj)
+    jobs.append([*cxx, "-c", str(wrap), "-o", str(obj)])
+
+    def run(cmd):
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError("command failed: " + " ".join(cmd) + "\n" + proc.stdout + proc.stderr)
+
+    with concurrent.futures.ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as pool:
+        list(pool.map(run, jobs))
+    run(["/usr/local/cuda/bin/nvcc", "-ccbin", "/usr/bin/g++", "-shared", "-cudart", "shared", "-Xcompiler", "-fopenmp",
+         "-gencode", "arch=compute_100a,code=sm_100a", "-Xlinker", "-rpath,/usr/local/cuda/lib64", "-Xlinker", "--no-undefined",
+         "-o", str(LIB_CUDA), *map(str, objects)])
+    for o in objects:
+        o.unlink(missing_ok=True)
+    return LIB_CUDA
 
 
 def main() -> None:

@@ -97,3 +97,58 @@ def test_bucket_helpers_validate():
         dp.gradient_scale(1024.0, 0)
     assert dp.gradient_scale(1024.0, 8) == 128.0
     assert [b.numel() for b in dp.make_buckets(torch.zeros(10, dtype=torch.float16), 8)] == [4, 4, 2]
+
+
+def test_final_gradient_prefix_follows_backward_order():
+    """ModelStorage.final_gradient_elements: after k backward steps exactly the tensors those steps finish lie below
+    the mark, in the flat buffer's order (final norm, blocks from last to first, embedding-side tensors last)."""
+    from cgpt_b200 import model as M
+    for tied in (True, False):
+        st = M.ModelStorage(M.preset("tiny", vocabulary_size=64), torch.float16, seed=0, tied=tied, device="cpu")
+        L = st.options.num_layers
+        marks = [st.final_gradient_elements(k) for k in range(L + 3)]
+        assert marks[0] == 0 and marks[-1] == st.flat_gradients.numel() and marks == sorted(marks)
+        assert marks[1] >= st.final_norm.numel() and marks[1] <= st.gradient_offsets[f"layers.{L - 1}.down_proj"]
+        for k in range(1, L + 1):          # after step k (block L-k) every tensor of blocks >= L-k lies below the mark
+            for li in range(L - k, L):
+                for name, t in st.layers[li].items():
+                    assert st.gradient_offsets[f"layers.{li}.{name}"] + t.numel() <= marks[k + 1]
+            for li in range(0, L - k):     # ... and no tensor of an unfinished block does
+                for name in st.layers[li]:
+                    assert st.gradient_offsets[f"layers.{li}.{name}"] >= marks[k + 1]
+        assert st.gradient_offsets["token_embedding"] >= marks[L + 1]     # the embedding step is the last one
+
+
+def _bucket_reducer_worker(rank, world, port, out):
+    import torch.distributed as dist
+    from cgpt_b200 import dp
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        flat = torch.arange(1000, dtype=torch.float32) * (rank + 1)
+        buckets = dp.make_buckets(flat, 4 * 300)               # 300, 300, 300, 100 elements
+        red = dp.BucketReducer(buckets, dist.group.WORLD)
+        started = [red.advance(n) for n in (0, 299, 300, 650, 899, 900)]
+        red.finish()
+        want = torch.arange(1000, dtype=torch.float32) * sum(r + 1 for r in range(world))
+        out.put((rank, started, bool(torch.equal(flat, want)), red.started))
+        out.close(); out.join_thread()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_bucket_reducer_starts_only_complete_buckets():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = 29650 + os.getpid() % 200
+    procs = [ctx.Process(target=_bucket_reducer_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, started, equal, left in results:
+        assert started == [0, 0, 1, 1, 0, 1], started      # a bucket goes out only when its last element is final
+        assert equal and left == 0
