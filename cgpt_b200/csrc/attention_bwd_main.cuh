@@ -141,11 +141,11 @@ int launch_backward(void* dq, void* dk, void* dv, const void* dout, const void* 
 
     auto kq = attention_bwd_tc_kernel<T, D, MODE_DQ>;
     auto kkv = attention_bwd_tc_kernel<T, D, MODE_DKV>;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce attr_once;
+    if (attr_once.needed()) {
         CGPT_CUDA_TRY(cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
         CGPT_CUDA_TRY(cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
-        attr_done = true;
+        attr_once.done();
     }
     unsigned int* status = tc_status_device_ptr();
     if (status == nullptr) return CGPT_ERR_STATE;

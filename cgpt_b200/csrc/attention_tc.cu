@@ -339,10 +339,10 @@ int launch_forward(void* out, float* lse, const void* q, const void* k, const vo
     CGPT_TRY(make_bshd_map(&tk, k, dtype, dm.batch, dm.sk, dm.hkv, D));
     CGPT_TRY(make_bshd_map(&tv, v, dtype, dm.batch, dm.sk, dm.hkv, D));
     auto kernel = attention_forward_tc_kernel<T, D>;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce attr_once;
+    if (attr_once.needed()) {
         CGPT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
-        attr_done = true;
+        attr_once.done();
     }
     unsigned int* status = tc_status_device_ptr();
     if (status == nullptr) return CGPT_ERR_STATE;

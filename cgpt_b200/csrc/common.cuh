@@ -61,6 +61,18 @@ private:
     std::size_t held_ = 0;
 };
 
+// "Done once per device" flag for per-kernel attributes (cudaFuncSetAttribute applies to the current device only).
+// Usage: static PerDeviceOnce once; if (once.needed()) { ...set attributes...; once.done(); }
+struct PerDeviceOnce {
+    bool flags[64] = {};
+    int device = 0;
+    bool needed() {
+        if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) { device = 0; return true; }
+        return !flags[device];
+    }
+    void done() { flags[device] = true; }
+};
+
 // While alive, scratch_get calls of this thread are served from arena `lane` (1 = ops issued on the side stream).
 struct ScratchLane {
     explicit ScratchLane(int lane);

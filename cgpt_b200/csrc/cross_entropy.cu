@@ -142,11 +142,11 @@ template <typename T, bool STAGED, int VEC>
 int ce_launch(float* row_loss, void* grad, const void* logits, const std::uint32_t* targets, long long rows, long long vocab,
               float inv_total_rows, float gradient_scale, unsigned grid, std::size_t smem, cudaStream_t s) {
     if (STAGED) {
-        static bool attr_done = false;
-        if (!attr_done) {
+        static PerDeviceOnce attr_once;
+        if (attr_once.needed()) {
             CGPT_CUDA_TRY(cudaFuncSetAttribute(cross_entropy_kernel<T, STAGED, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                200 * 1024));
-            attr_done = true;
+            attr_once.done();
         }
     }
     cross_entropy_kernel<T, STAGED, VEC><<<grid, kCeThreads, smem, s>>>(row_loss, static_cast<T*>(grad), static_cast<const T*>(logits),

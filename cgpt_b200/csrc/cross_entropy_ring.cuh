@@ -185,11 +185,11 @@ template <typename T>
 int ce_ring_launch(float* row_loss, void* grad, const void* logits, const std::uint32_t* targets, long long rows, long long vocab,
                    float inv_total_rows, float gradient_scale, int stages, unsigned row_pitch, cudaStream_t s) {
     const std::size_t smem = static_cast<std::size_t>(stages) * row_pitch;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce attr_once;
+    if (attr_once.needed()) {
         CGPT_CUDA_TRY(cudaFuncSetAttribute(cross_entropy_ring_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(kRingSmemBudget)));
-        attr_done = true;
+        attr_once.done();
     }
     unsigned int* status = tc_status_device_ptr();
     if (status == nullptr) return CGPT_ERR_STATE;

@@ -406,11 +406,11 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
     }
     auto kernel = gemm_tcgen05_kernel<T, BN, A_MN, B_MN>;
     auto pkernel = gemm_tcgen05_persistent_kernel<T, BN, A_MN, B_MN>;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce attr_once;
+    if (attr_once.needed()) {
         CGPT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         CGPT_CUDA_TRY(cudaFuncSetAttribute(pkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-        attr_done = true;
+        attr_once.done();
     }
     int epi = splits > 1 ? kEpiPartial : (accumulate ? kEpiAccumulate : kEpiStore);
     {   // diagnosis only: CGPT_B200_GEMM_NOSTORE=1 drains the accumulator but skips the global stores
@@ -559,12 +559,14 @@ int linear_swiglu_dispatch(void* gate, void* up, void* act, const void* x, const
 }
 
 unsigned int* tc_status_device_ptr() {
-    static unsigned int* p = nullptr;   // one device per process
-    if (p == nullptr) {
+    static unsigned int* ptrs[64] = {};   // the symbol has one address per device
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
+    if (ptrs[device] == nullptr) {
         void* addr = nullptr;
-        if (cudaGetSymbolAddress(&addr, g_gemm_status) == cudaSuccess) p = static_cast<unsigned int*>(addr);
+        if (cudaGetSymbolAddress(&addr, g_gemm_status) == cudaSuccess) ptrs[device] = static_cast<unsigned int*>(addr);
     }
-    return p;
+    return ptrs[device];
 }
 
 int column_sum(void* out, const void* in, long long rows, long long cols, int accumulate, int dtype, cudaStream_t s) {

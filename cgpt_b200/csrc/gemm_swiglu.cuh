@@ -207,10 +207,10 @@ int launch_gemm_swiglu(T* gate, T* up, T* act, const T* x, const T* wg, const T*
     CGPT_TRY(make_tensor_map(&maps.up, dtype, up, 2, od, ost, out_box));
     CGPT_TRY(make_tensor_map(&maps.act, dtype, act, 2, od, ost, out_box));
     auto kernel = gemm_swiglu_persistent_kernel<T>;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce attr_once;
+    if (attr_once.needed()) {
         CGPT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-        attr_done = true;
+        attr_once.done();
     }
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + 127) / 128;
     const long long units = static_cast<long long>(tiles_m) * tiles_n;

@@ -86,9 +86,13 @@ class AdamWWorkspace:
     _keys: tuple = ()
 
     def __del__(self):
-        if self._handle is not None:
-            lib.cgpt_adamw_destroy(self._handle)
-            self._handle = None
+        # at interpreter shutdown the module globals may already be gone; the process is about to release everything
+        handle, self._handle = getattr(self, "_handle", None), None
+        if handle is not None and lib is not None:
+            try:
+                lib.cgpt_adamw_destroy(handle)
+            except Exception:
+                pass
 
 
 def _validate_entry(e: AdamWBatchEntry) -> None:
