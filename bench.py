@@ -173,7 +173,9 @@ def run_ours(args) -> None:
     from cgpt_b200.train import TrainStep
 
     opts = M.preset(PRESET)
-    ts = TrainStep(opts, BATCH, SEQ, seed=0, process_group=pg)
+    # CGPT_B200_OVERLAP_ALLREDUCE=1: eager step with the bucketed all-reduce overlapping the backward (N > 1 only)
+    overlap = os.environ.get("CGPT_B200_OVERLAP_ALLREDUCE", "0") == "1"
+    ts = TrainStep(opts, BATCH, SEQ, seed=0, process_group=pg, overlap_allreduce=overlap)
     rows = BATCH * SEQ
     gen = torch.Generator().manual_seed(1234 + rank)
     pool = 4

@@ -19,7 +19,7 @@ class TrainStep:
     def __init__(self, options: M.TransformerModelOptions, batch: int, seq: int, *, dtype=torch.float16, seed: int = 0,
                  loss_scale: float = 1024.0, adamw: O.AdamWOptions | None = None, process_group=None,
                  bucket_bytes: int = 48 << 20, use_graph: bool = True, cce_chunk_rows: int = 0, device="cuda",
-                 overlap_allreduce: bool | None = None):
+                 overlap_allreduce: bool = False):
         self.options, self.batch, self.seq, self.dtype = options, batch, seq, dtype
         self.rows = batch * seq
         self.pg = process_group
@@ -44,7 +44,7 @@ class TrainStep:
         self.graph = None
         # With more than one rank the bucketed all-reduce overlaps the backward: the step is then issued eagerly, piece by
         # piece (a captured graph would have to contain the collectives); one rank replays the captured graph.
-        self.overlap_allreduce = (self.world > 1) if overlap_allreduce is None else (overlap_allreduce and self.world > 1)
+        self.overlap_allreduce = bool(overlap_allreduce) and self.world > 1
         self.use_graph = use_graph and not self.overlap_allreduce
         self._buckets = self._make_buckets(bucket_bytes)
         self._reducer = dp.BucketReducer(self._buckets, self.pg) if self.overlap_allreduce else None

@@ -46,6 +46,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--validation-fraction", type=float, default=0.1)
     p.add_argument("--save-avg-loss", action="store_true")
     p.add_argument("--checkpoint-interval", type=int, default=0, help="also write a checkpoint every N steps (0 = only at the end)")
+    p.add_argument("--overlap-allreduce", action="store_true",
+                   help="ranks > 1: issue the step eagerly and start each gradient bucket's all-reduce during the backward")
     p.add_argument("--seed", type=int, default=0)
     return p
 
@@ -139,7 +141,8 @@ def main(argv=None) -> int:
 
     options = M.preset(args.model, vocabulary_size=args.vocab_size)
     adamw = O.AdamWOptions(args.learning_rate, 0.9, 0.95, 1e-8, 0.1, args.loss_scale, 1.0)   # train/train.cpp:434-441
-    ts = TrainStep(options, B, S, dtype=torch.float16, seed=args.seed, loss_scale=args.loss_scale, adamw=adamw, process_group=pg)
+    ts = TrainStep(options, B, S, dtype=torch.float16, seed=args.seed, loss_scale=args.loss_scale, adamw=adamw, process_group=pg,
+                   overlap_allreduce=args.overlap_allreduce)
     log(f"model {args.model}: {ts.storage.num_parameters() / 1e6:.1f}M parameters, ranks {world}, "
         f"global batch {B * world} x {S}, {total_steps} steps ({warmup} warm-up)")
     first_step = 0
