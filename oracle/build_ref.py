@@ -1,14 +1,14 @@
 """Builds the reference's own CPU operators into ``oracle/_ref/libcgpt_ref_cpu.so`` and its own CUDA operators, for
 sm_100a, into ``oracle/_ref/libcgpt_ref_cuda.so`` (TEST INFRASTRUCTURE).
 
-Sources are compiled where they lie under the reference checkout (default ``/root/reference``); nothing
+Sources are compiled where they lie under the reference checkout (``--reference`` or ``$CGPT_REFERENCE``); nothing
 is copied. The only file of this repository in the link is ``oracle/ref_wrap.cpp``, a flat C wrapper.
 The recipe replaces the reference's CMake build (which pins sm_86/sm_90a and needs CMake >= 4.3) with
 direct compiler calls and the flags of its ``CMakeLists.txt:57-66`` (``-O3 -mavx2 -mfma -mf16c``,
 OpenMP on), plus ``-include cstdint`` because ``include/core/dtype.h:12`` uses ``std::uint8_t`` without
 including ``<cstdint>``.
 
-Usage: ``python oracle/build_ref.py [--reference /root/reference]``. Does nothing (and says so) when the
+Usage: ``python oracle/build_ref.py [--reference <checkout>]``. Does nothing (and says so) when the
 reference checkout is absent, e.g. on a GPU box, where the prebuilt library is used.
 """
 from __future__ import annotations
