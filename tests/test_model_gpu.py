@@ -270,3 +270,31 @@ def test_large_config_shapes_step_is_finite_and_reproducible():
         del ts
         torch.cuda.empty_cache()
     assert out[0][0] == out[1][0] and torch.equal(out[0][1], out[1][1]) and torch.equal(out[0][2], out[1][2])
+
+
+def test_model_backward_in_steps_equals_whole():
+    """cgpt_model_backward_steps called piece by piece (final norm, each block, embedding) leaves exactly the gradients
+    of the single whole-model call."""
+    from cgpt_b200 import model as M
+    from cgpt_b200.train import TrainStep
+    opts = M.TransformerModelOptions(512, 3, M.TransformerBlockOptions(256, 512, 2, 1, 128, 128))
+    ids = torch.randint(0, 512, (2 * 64,), dtype=torch.int32)
+
+    def grads(stepwise):
+        ts = TrainStep(opts, 2, 64, seed=4, use_graph=False)
+        ts.token_ids.copy_(ids)
+        ts.targets.copy_(torch.roll(ids, -1))
+        st, ws, bw = ts.storage, ts.workspace, ts.backward_workspace
+        with torch.cuda.stream(ts.stream):
+            keep = [M.transformer_model_forward(None, ts.token_ids, 2, 64, st, ws, ts.cos, ts.sin, None, None, opts, scratch=bw)]
+            M.cut_cross_entropy_forward_backward(ts.loss, bw.grad_normalized, st.g_lm_head, ws.normalized, st.lm_head,
+                                                 ts.targets, ts.rows, None, 1024.0)
+            pieces = [(s, s + 1) for s in range(opts.num_layers + 2)] if stepwise else [None]
+            for p in pieces:
+                keep.append(M.transformer_model_backward(None, ts.token_ids, 2, 64, st, ws, bw, ts.cos, ts.sin, None, None, opts,
+                                                         steps=p))
+        ts.stream.synchronize()
+        return st.flat_gradients.clone()
+
+    whole, stepped = grads(False), grads(True)
+    assert float(whole.float().abs().max()) > 0 and torch.equal(whole, stepped)
