@@ -34,6 +34,7 @@ def time_gemms(train_step, steps: int = 2) -> dict:
     # time it waits for SMs held by the other branch's kernels
     check(lib.cgpt_b200_set_branch_streams(0), "set_branch_streams")
     check(lib.cgpt_b200_gemm_timing(1), "gemm_timing")
+    reducer, ts._reducer = getattr(ts, "_reducer", None), None    # this pass runs on one rank only: no collectives
     try:
         with torch.cuda.stream(ts.stream):
             for _ in range(steps):
@@ -42,6 +43,7 @@ def time_gemms(train_step, steps: int = 2) -> dict:
         ms, fl, n = C.c_double(0), C.c_double(0), C.c_uint64(0)
         check(lib.cgpt_b200_gemm_timing_read(C.byref(ms), C.byref(fl), C.byref(n)), "gemm_timing_read")
     finally:
+        ts._reducer = reducer
         check(lib.cgpt_b200_gemm_timing(0), "gemm_timing")
         check(lib.cgpt_b200_set_branch_streams(int(os.environ.get("CGPT_B200_BRANCH_STREAMS", "0") == "1")), "set_branch_streams")
     tokens = ts.batch * ts.seq
