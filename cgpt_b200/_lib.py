@@ -59,7 +59,7 @@ class AdamWOptions(C.Structure):
 BLOCK_PARAM_FIELDS = ("attention_norm", "q_projection", "k_projection", "q_norm", "k_norm", "v_projection",
                       "o_projection", "ffn_norm", "gate_proj", "up_proj", "down_proj")
 BLOCK_SAVED_FIELDS = ("norm", "query", "key", "value", "query_pre_norm", "key_pre_norm", "attention_output",
-                      "attention_logsumexp", "gate", "up", "activated")
+                      "attention_logsumexp", "gate", "up", "activated", "attention_norm_output")
 
 
 class BlockParams(C.Structure):

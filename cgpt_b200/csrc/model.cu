@@ -191,11 +191,13 @@ extern "C" int cgpt_block_forward(void* out, const void* in, const cgpt_block_pa
         ScratchLane lane(br.lane());
         CGPT_TRY(mlp_forward(in, w, sv, ws, m, dt, eps, br.side));
     }
-    // attention branch on the caller's stream; its norm output is not kept (sv->norm holds the FFN norm's)
-    CGPT_TRY(cgpt_rmsnorm_forward(ws.norm_f, in, w->attention_norm, m.rows, m.d, eps, dt, stream));
-    CGPT_TRY(cgpt_linear_forward(sv->query_pre_norm, ws.norm_f, w->q_projection, m.rows, m.d, m.qdim, dt, stream));
-    CGPT_TRY(cgpt_linear_forward(sv->key_pre_norm, ws.norm_f, w->k_projection, m.rows, m.d, m.kvdim, dt, stream));
-    CGPT_TRY(cgpt_linear_forward(sv->value, ws.norm_f, w->v_projection, m.rows, m.d, m.kvdim, dt, stream));
+    // attention branch on the caller's stream; its norm output is kept only if the caller gave a buffer for it
+    // (sv->norm holds the FFN norm's output, as in the reference)
+    void* norm_attn = sv->attention_norm_output != nullptr ? sv->attention_norm_output : ws.norm_f;
+    CGPT_TRY(cgpt_rmsnorm_forward(norm_attn, in, w->attention_norm, m.rows, m.d, eps, dt, stream));
+    CGPT_TRY(cgpt_linear_forward(sv->query_pre_norm, norm_attn, w->q_projection, m.rows, m.d, m.qdim, dt, stream));
+    CGPT_TRY(cgpt_linear_forward(sv->key_pre_norm, norm_attn, w->k_projection, m.rows, m.d, m.kvdim, dt, stream));
+    CGPT_TRY(cgpt_linear_forward(sv->value, norm_attn, w->v_projection, m.rows, m.d, m.kvdim, dt, stream));
     {   // per-head QK-norm then RoPE: one fused pass when the shape allows it, else the three separate ops
         int rc = cgpt_qknorm_rope_forward(sv->query, sv->key, sv->query_pre_norm, sv->key_pre_norm, w->q_norm, w->k_norm,
                                           cos_table, sin_table, batch, seq, m.hq, m.hkv, m.hd, cfg->rotary_dim,
@@ -252,8 +254,13 @@ extern "C" int cgpt_block_backward(void* grad_in, const void* grad_out, const vo
         }
         CGPT_TRY(rc);
     }
-    // the attention-norm output was overwritten by the FFN norm in the forward: recompute it (:725)
-    CGPT_TRY(cgpt_rmsnorm_forward(ws.norm_a, in, w->attention_norm, m.rows, m.d, eps, dt, stream));
+    // the attention-norm output: saved by the forward if the caller provided the buffer, else recomputed as the
+    // reference does (:725; its single norm buffer was overwritten by the FFN norm)
+    const void* norm_a = sv->attention_norm_output;
+    if (norm_a == nullptr) {
+        CGPT_TRY(cgpt_rmsnorm_forward(ws.norm_a, in, w->attention_norm, m.rows, m.d, eps, dt, stream));
+        norm_a = ws.norm_a;
+    }
     {   // d(attention norm output) = dQ Wq + dK Wk + dV Wv in one pass over the buffer (:726-744 runs three
         // GEMMs, the last two accumulating into it)
         const void* dys[3] = {ws.dq_pre, ws.dk_pre, ws.dv};
@@ -261,11 +268,11 @@ extern "C" int cgpt_block_backward(void* grad_in, const void* grad_out, const vo
         const size_t outs[3] = {m.qdim, m.kvdim, m.kvdim};
         CGPT_TRY(cgpt_linear_backward_input_fused(ws.d_attn_norm_in, dys, wts, outs, 3, m.rows, m.d, 0, dt, stream));
     }
-    CGPT_TRY(cgpt_linear_backward(nullptr, g->q_projection, nullptr, ws.dq_pre, ws.norm_a, nullptr, m.rows, m.d, m.qdim, 0, 0,
+    CGPT_TRY(cgpt_linear_backward(nullptr, g->q_projection, nullptr, ws.dq_pre, norm_a, nullptr, m.rows, m.d, m.qdim, 0, 0,
                                   0, dt, stream));
-    CGPT_TRY(cgpt_linear_backward(nullptr, g->k_projection, nullptr, ws.dk_pre, ws.norm_a, nullptr, m.rows, m.d, m.kvdim, 0, 0,
+    CGPT_TRY(cgpt_linear_backward(nullptr, g->k_projection, nullptr, ws.dk_pre, norm_a, nullptr, m.rows, m.d, m.kvdim, 0, 0,
                                   0, dt, stream));
-    CGPT_TRY(cgpt_linear_backward(nullptr, g->v_projection, nullptr, ws.dv, ws.norm_a, nullptr, m.rows, m.d, m.kvdim, 0, 0, 0,
+    CGPT_TRY(cgpt_linear_backward(nullptr, g->v_projection, nullptr, ws.dv, norm_a, nullptr, m.rows, m.d, m.kvdim, 0, 0, 0,
                                   dt, stream));
     // grad_in += d(attention_norm): needs the MLP branch's grad_in
     CGPT_TRY(br.join());

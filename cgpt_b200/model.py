@@ -79,7 +79,8 @@ def block_param_shapes(o: TransformerBlockOptions) -> dict:
 class TransformerBlockWorkspace:
     """Activations saved by the forward (include/core/transformer_block.h:65-93)."""
 
-    def __init__(self, options: TransformerBlockOptions, batch: int, seq: int, dtype=torch.float16, device="cuda"):
+    def __init__(self, options: TransformerBlockOptions, batch: int, seq: int, dtype=torch.float16, device="cuda",
+                 save_attention_norm: bool = True):
         o = options
         rows = batch * seq
         e = lambda *s: torch.empty(*s, dtype=dtype, device=device)
@@ -94,10 +95,13 @@ class TransformerBlockWorkspace:
         self.gate = e(rows, o.intermediate_size)
         self.up = e(rows, o.intermediate_size)
         self.activated = e(rows, o.intermediate_size)
+        # not in the reference's workspace (it recomputes the attention norm in the backward): rows*hidden elements
+        # per layer buy one RMSNorm pass per layer; None restores the recomputation
+        self.attention_norm_output = e(rows, o.hidden_size) if save_attention_norm else None
         self.batch, self.seq = batch, seq
 
     def c_struct(self) -> BlockSaved:
-        return BlockSaved(*[getattr(self, n).data_ptr() for n in BLOCK_SAVED_FIELDS])
+        return BlockSaved(*[(getattr(self, n).data_ptr() if getattr(self, n) is not None else None) for n in BLOCK_SAVED_FIELDS])
 
 
 class TransformerBlockBackwardWorkspace:

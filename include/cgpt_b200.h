@@ -365,6 +365,10 @@ typedef struct cgpt_block_saved {
     void* gate;                  /* [rows, intermediate] */
     void* up;                    /* [rows, intermediate] */
     void* activated;             /* [rows, intermediate] */
+    void* attention_norm_output; /* optional [rows, hidden]: output of the attention RMSNorm. The reference's
+                                    workspace has no such buffer and recomputes the norm in the backward
+                                    (src/core/transformer_block.cu:725); NULL keeps that behaviour, a buffer
+                                    trades rows*hidden elements per layer for one RMSNorm pass per layer */
 } cgpt_block_saved;
 
 typedef struct cgpt_model_config {
