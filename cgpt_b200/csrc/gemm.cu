@@ -361,6 +361,8 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
     using Cfg = GemmCfg<BN>;
     GemmOperands ops;
     ops.segments = segments;
+    ops.groups = 1;
+    ops.tile_end[0] = ops.tile_end[1] = ops.tile_end[2] = 0;
     int total_kb = 0;
     long long K = 0;   // summed: split heuristics and the FLOP count
     for (int i = 0; i < kMaxKSegments; ++i) {
@@ -426,7 +428,9 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
         const long long units = static_cast<long long>(tiles) * splits;
         const unsigned grid = static_cast<unsigned>(units < kNumSMs ? units : kNumSMs);
         // Plain stores of 16-bit output go through shared memory and TMA (needs a 16-byte aligned C and N % 8 == 0).
-        CUtensorMap tc = ta;
+        GemmOutputs outs;
+        outs.c[0] = outs.c[1] = outs.c[2] = ta;      // placeholders: only read by the TMA-store epilogue
+        CUtensorMap& tc = outs.c[0];
         if (epi == kEpiStore && aligned16(C) && N % 8 == 0) {
             const std::uint64_t dims_c[2] = {static_cast<std::uint64_t>(N), static_cast<std::uint64_t>(M)};
             const std::uint64_t st_c[1] = {static_cast<std::uint64_t>(N) * 2};
@@ -439,7 +443,8 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
             if (diag == 2) epi = kEpiStageOnly;
             if (diag == 3) epi = kEpiStoreTmaFixed;
         }
-        pkernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ops, tc, C, partial, M, N, total_kb, tiles_m, tiles_n, splits, kb_per_split, epi);
+        outs.c[1] = outs.c[2] = outs.c[0];
+        pkernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ops, outs, C, partial, M, N, total_kb, tiles_m, tiles_n, splits, kb_per_split, epi);
     }
     count_launch();
     CGPT_LAUNCH_CHECK();
@@ -476,6 +481,62 @@ int launch_tc_layout(T* C, const T* const* A, const T* const* B, const int* K, i
     CGPT_GEMM_CASE(1, 0)
 #undef CGPT_GEMM_CASE
     return CGPT_ERR_OPTION;
+}
+
+// Y_g[M, N_g] = A[M, K] * B_g[N_g, K]^T for up to three outputs that share A, as ONE launch: the N tiles of all groups
+// form one work list (better wave quantisation than three launches, A read through L2 by neighbouring CTAs).
+// Tensor-core path only (16-bit, aligned, N_g % 8 == 0); returns CGPT_ERR_UNSUPPORTED otherwise.
+template <typename T>
+int launch_tc_groups(T* const* Cs, const T* A, const T* const* Bs, const int* Ns, int groups, int M, int K, int dtype, cudaStream_t s) {
+    constexpr int BN = 256;
+    using Cfg = GemmCfg<BN>;
+    if (groups < 1 || groups > kMaxKSegments || !aligned16(A) || K % 8 != 0 || K < 32) return CGPT_ERR_UNSUPPORTED;
+    GemmOperands ops;
+    GemmOutputs outs;
+    ops.segments = 1;
+    ops.groups = groups;
+    const std::uint64_t a_dims[2] = {static_cast<std::uint64_t>(K), static_cast<std::uint64_t>(M)};
+    const std::uint64_t k_st[1] = {static_cast<std::uint64_t>(K) * 2};
+    const std::uint32_t a_box[2] = {BK, BM}, b_box[2] = {BK, BN}, c_box[2] = {64, BM};
+    int tiles_n = 0;
+    double flops = 0.0;
+    for (int i = 0; i < kMaxKSegments; ++i) {
+        const int g = i < groups ? i : 0;
+        if (!aligned16(Cs[g]) || !aligned16(Bs[g]) || Ns[g] % 8 != 0 || Ns[g] <= 0) return CGPT_ERR_UNSUPPORTED;
+        CGPT_TRY(make_tensor_map(&ops.a[i], dtype, A, 2, a_dims, k_st, a_box));
+        const std::uint64_t b_dims[2] = {static_cast<std::uint64_t>(K), static_cast<std::uint64_t>(Ns[g])};
+        CGPT_TRY(make_tensor_map(&ops.b[i], dtype, Bs[g], 2, b_dims, k_st, b_box));
+        const std::uint64_t c_dims[2] = {static_cast<std::uint64_t>(Ns[g]), static_cast<std::uint64_t>(M)};
+        const std::uint64_t c_st[1] = {static_cast<std::uint64_t>(Ns[g]) * 2};
+        CGPT_TRY(make_tensor_map(&outs.c[i], dtype, Cs[g], 2, c_dims, c_st, c_box));
+        if (i < groups) {
+            tiles_n += (Ns[g] + BN - 1) / BN;
+            flops += 2.0 * M * Ns[g] * K;
+        }
+        ops.tile_end[i] = tiles_n;
+        ops.kb_end[i] = (K + BK - 1) / BK;
+    }
+    const int tiles_m = (M + BM - 1) / BM;
+    const long long units = static_cast<long long>(tiles_m) * tiles_n;
+    if (units < kNumSMs) return CGPT_ERR_UNSUPPORTED;   // too small to be worth it: no split-K in this form
+    auto pkernel = gemm_tcgen05_persistent_kernel<T, BN, false, false>;
+    static PerDeviceOnce attr_once;
+    if (attr_once.needed()) {
+        CGPT_CUDA_TRY(cudaFuncSetAttribute(pkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        attr_once.done();
+    }
+    const bool timed = g_timing.enabled && g_timing.used + 2 <= g_timing.events.size();
+    if (timed) CGPT_CUDA_TRY(cudaEventRecord(g_timing.events[g_timing.used], s));
+    pkernel<<<kNumSMs, kGemmThreads, Cfg::kSmemBytes, s>>>(ops, outs, Cs[0], nullptr, M, Ns[0], (K + BK - 1) / BK, tiles_m, tiles_n, 1,
+                                                          (K + BK - 1) / BK, kEpiStoreTma);
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+    if (timed) {
+        CGPT_CUDA_TRY(cudaEventRecord(g_timing.events[g_timing.used + 1], s));
+        g_timing.used += 2;
+        g_timing.flops.push_back(flops);
+    }
+    return CGPT_OK;
 }
 
 }  // namespace
@@ -613,6 +674,34 @@ extern "C" int cgpt_linear_backward(void* dx, void* dw, void* db, const void* dy
         if (!valid_float_dtype(dtype) || T <= 0 || O <= 0) return CGPT_ERR_SHAPE;
         CGPT_TRY(column_sum(db, dy, T, O, accumulate_bias, dtype, s));
     }
+    return CGPT_OK;
+}
+
+extern "C" int cgpt_linear_forward_fused(void* const* y, const void* x, const void* const* w, const size_t* out_features,
+                                         size_t count, size_t rows, size_t in_features, int dtype, cgpt_stream_t stream) {
+    if (!y || !x || !w || !out_features) return CGPT_ERR_NULL;
+    if (count < 1 || count > static_cast<size_t>(kMaxKSegments)) return CGPT_ERR_SHAPE;
+    auto s = static_cast<cudaStream_t>(stream);
+    int ns[kMaxKSegments] = {0, 0, 0};
+    for (size_t i = 0; i < count; ++i) {
+        if (!y[i] || !w[i]) return CGPT_ERR_NULL;
+        if (out_features[i] == 0 || out_features[i] > 0x7fffffffull) return CGPT_ERR_SHAPE;
+        ns[i] = static_cast<int>(out_features[i]);
+    }
+    if (rows == 0 || in_features == 0 || rows > 0x7fffffffull || in_features > 0x7fffffffull) return CGPT_ERR_SHAPE;
+    int rc = CGPT_ERR_UNSUPPORTED;
+    if (dtype == CGPT_DTYPE_F16)
+        rc = launch_tc_groups<__half>(reinterpret_cast<__half* const*>(y), static_cast<const __half*>(x),
+                                      reinterpret_cast<const __half* const*>(w), ns, static_cast<int>(count), static_cast<int>(rows),
+                                      static_cast<int>(in_features), dtype, s);
+    else if (dtype == CGPT_DTYPE_BF16)
+        rc = launch_tc_groups<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16* const*>(y), static_cast<const __nv_bfloat16*>(x),
+                                             reinterpret_cast<const __nv_bfloat16* const*>(w), ns, static_cast<int>(count),
+                                             static_cast<int>(rows), static_cast<int>(in_features), dtype, s);
+    if (rc != CGPT_ERR_UNSUPPORTED) return rc;
+    for (size_t i = 0; i < count; ++i)
+        CGPT_TRY(gemm_dispatch(y[i], x, w[i], static_cast<long long>(rows), static_cast<long long>(out_features[i]),
+                               static_cast<long long>(in_features), 0, 0, 0, dtype, false, s));
     return CGPT_OK;
 }
 

@@ -62,11 +62,19 @@ struct GemmOperands {
     CUtensorMap b[kMaxKSegments];
     int kb_end[kMaxKSegments];
     int segments;
+    // Output groups (exclusive with K segments): several products that share A, each with its own B_g and C_g, run as
+    // one launch (Q, K and V projections of the same input). The N tiles of the groups are numbered consecutively;
+    // group g owns tiles [tile_end[g-1], tile_end[g]). groups == 1: the plain case.
+    int groups;
+    int tile_end[kMaxKSegments];
+};
+struct GemmOutputs {
+    CUtensorMap c[kMaxKSegments];   // TMA-store maps, one per output group
 };
 
 template <typename T, int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tcgen05_persistent_kernel(const __grid_constant__ GemmOperands ops, const __grid_constant__ CUtensorMap tmap_c,
+gemm_tcgen05_persistent_kernel(const __grid_constant__ GemmOperands ops, const __grid_constant__ GemmOutputs outs,
                                T* __restrict__ C, float* __restrict__ partial, int M, int N, int total_kb, int tiles_m,
                                int tiles_n, int splits, int kb_per_split, int epilogue) {
     using Cfg = GemmCfg<BN>;
@@ -122,8 +130,12 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ GemmOperands ops, const _
                     int seg = 0, kb_first = 0;
                     if (ops.segments > 1 && kb >= ops.kb_end[0]) { seg = 1; kb_first = ops.kb_end[0]; }
                     if (ops.segments > 2 && kb >= ops.kb_end[1]) { seg = 2; kb_first = ops.kb_end[1]; }
+                    int group = 0, tile_first = 0;
+                    if (ops.groups > 1 && tile_n >= ops.tile_end[0]) { group = 1; tile_first = ops.tile_end[0]; }
+                    if (ops.groups > 2 && tile_n >= ops.tile_end[1]) { group = 2; tile_first = ops.tile_end[1]; }
+                    const int tile_n_b = tile_n - tile_first;          // N tile inside the group's own B
                     const CUtensorMap* tmap_a = &ops.a[seg];
-                    const CUtensorMap* tmap_b = &ops.b[seg];
+                    const CUtensorMap* tmap_b = &ops.b[ops.groups > 1 ? group : seg];
                     const int k0 = (kb - kb_first) * BK;
                     if (!A_MN) {
                         tma_load_2d(a_dst, tmap_a, &full[s], k0, tile_m * BM);
@@ -132,10 +144,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ GemmOperands ops, const _
                         for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * (BK * 128), tmap_a, &full[s], tile_m * BM + j * 64, k0);
                     }
                     if (!B_MN) {
-                        tma_load_2d(b_dst, tmap_b, &full[s], k0, tile_n * BN);
+                        tma_load_2d(b_dst, tmap_b, &full[s], k0, tile_n_b * BN);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * (BK * 128), tmap_b, &full[s], tile_n * BN + j * 64, k0);
+                        for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * (BK * 128), tmap_b, &full[s], tile_n_b * BN + j * 64, k0);
                     }
                 }
             }
@@ -211,9 +223,12 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ GemmOperands ops, const _
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                     if (et == 0 && epilogue != kEpiStageOnly) {
                         const bool fixed = epilogue == kEpiStoreTmaFixed;   // diagnosis: every store lands on the same 16 KB
+                        int group = 0, tile_first = 0;
+                        if (ops.groups > 1 && tile_n >= ops.tile_end[0]) { group = 1; tile_first = ops.tile_end[0]; }
+                        if (ops.groups > 2 && tile_n >= ops.tile_end[1]) { group = 2; tile_first = ops.tile_end[1]; }
                         asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                                     ::"l"(reinterpret_cast<std::uint64_t>(&tmap_c)), "r"(smem_u32(buf_s)),
-                                       "r"(fixed ? 0 : tile_n * BN + c0), "r"(fixed ? 0 : tile_m * BM)
+                                     ::"l"(reinterpret_cast<std::uint64_t>(&outs.c[group])), "r"(smem_u32(buf_s)),
+                                       "r"(fixed ? 0 : (tile_n - tile_first) * BN + c0), "r"(fixed ? 0 : tile_m * BM)
                                      : "memory");
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }

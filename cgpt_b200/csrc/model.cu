@@ -195,9 +195,12 @@ extern "C" int cgpt_block_forward(void* out, const void* in, const cgpt_block_pa
     // (sv->norm holds the FFN norm's output, as in the reference)
     void* norm_attn = sv->attention_norm_output != nullptr ? sv->attention_norm_output : ws.norm_f;
     CGPT_TRY(cgpt_rmsnorm_forward(norm_attn, in, w->attention_norm, m.rows, m.d, eps, dt, stream));
-    CGPT_TRY(cgpt_linear_forward(sv->query_pre_norm, norm_attn, w->q_projection, m.rows, m.d, m.qdim, dt, stream));
-    CGPT_TRY(cgpt_linear_forward(sv->key_pre_norm, norm_attn, w->k_projection, m.rows, m.d, m.kvdim, dt, stream));
-    CGPT_TRY(cgpt_linear_forward(sv->value, norm_attn, w->v_projection, m.rows, m.d, m.kvdim, dt, stream));
+    {   // query, key and value projections of the same input as one launch (three in the reference, :496-510)
+        void* ys[3] = {sv->query_pre_norm, sv->key_pre_norm, sv->value};
+        const void* wts[3] = {w->q_projection, w->k_projection, w->v_projection};
+        const size_t outs[3] = {m.qdim, m.kvdim, m.kvdim};
+        CGPT_TRY(cgpt_linear_forward_fused(ys, norm_attn, wts, outs, 3, m.rows, m.d, dt, stream));
+    }
     {   // per-head QK-norm then RoPE: one fused pass when the shape allows it, else the three separate ops
         int rc = cgpt_qknorm_rope_forward(sv->query, sv->key, sv->query_pre_norm, sv->key_pre_norm, w->q_norm, w->k_norm,
                                           cos_table, sin_table, batch, seq, m.hq, m.hkv, m.hd, cfg->rotary_dim,

@@ -103,6 +103,25 @@ def linear_backward(grad_input, grad_weight, grad_bias, grad_output, input, weig
                                    int(o.accumulate_bias), dtype_code(input), stream_ptr(stream)), "linear_backward")
 
 
+def linear_forward_fused(outputs, input, weights, stream=None):
+    """outputs[i] = input @ weights[i].T for up to three projections of one input, as one launch
+    (cgpt_linear_forward_fused; the reference calls linear_forward once per projection)."""
+    import ctypes as C
+    n = len(outputs)
+    _require(1 <= n <= 3 and len(weights) == n, "linear_forward_fused: 1..3 projections")
+    _same_cuda_dtype("linear_forward_fused", input, *outputs, *weights)
+    in_f = input.shape[-1]
+    rows = input.numel() // in_f
+    for y, w in zip(outputs, weights):
+        _require(w.dim() == 2 and w.shape[1] == in_f and y.shape[-1] == w.shape[0] and y.numel() == rows * w.shape[0],
+                 "linear_forward_fused: incompatible shapes")
+    ys = (C.c_void_p * n)(*[ptr(t) for t in outputs])
+    ws = (C.c_void_p * n)(*[ptr(t) for t in weights])
+    outs = (C.c_size_t * n)(*[w.shape[0] for w in weights])
+    check(lib.cgpt_linear_forward_fused(ys, ptr(input), ws, outs, n, rows, in_f, dtype_code(input), stream_ptr(stream)),
+          "linear_forward_fused")
+
+
 def linear_swiglu_forward(gate, up, activated, input, gate_weight, up_weight, stream=None):
     """gate = input @ gate_weight.T, up = input @ up_weight.T, activated = swiglu(gate, up) in one launch
     (cgpt_linear_swiglu_forward; the reference's block forward calls linear_forward twice and swiglu_forward)."""

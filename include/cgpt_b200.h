@@ -99,6 +99,14 @@ int cgpt_linear_backward(void* dx, void* dw, void* db, const void* dy, const voi
                          size_t rows, size_t in_features, size_t out_features, int accumulate_input,
                          int accumulate_weight, int accumulate_bias, int dtype, cgpt_stream_t stream);
 
+/* `count` (1..3) projections of the same input as one launch: y_i[rows,out_i] = x[rows,in] W_i[out_i,in]^T.
+ * Replaces consecutive linear_forward calls on one input (reference src/core/transformer_block.cu:496-510: query, key
+ * and value projections): one work list over all output tiles fills the SMs better than three launches whose tile
+ * counts are not multiples of the SM count. Results are bit-identical to the separate calls. y, w: host arrays of
+ * `count` device pointers. Runs as separate calls when the tensor-core path does not apply (fp32, unaligned, tiny). */
+int cgpt_linear_forward_fused(void* const* y, const void* x, const void* const* w, const size_t* out_features,
+                              size_t count, size_t rows, size_t in_features, int dtype, cgpt_stream_t stream);
+
 /* Gate and up projections with the SwiGLU activation in the GEMM epilogue:
  *      gate = X Wg^T, up = X Wu^T, activated = gate / (1 + exp(-gate)) * up      (all [rows, intermediate]).
  * Replaces the sequence linear_forward, linear_forward, swiglu_forward of the block forward (reference

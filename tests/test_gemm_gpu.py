@@ -146,3 +146,21 @@ def test_linear_swiglu_forward(ops, dtype, rows, in_f, inter):
     assert_close(host(up), host(x.float() @ wu.float().t()), TOL[dtype], "up vs fp32")
     assert torch.equal(gate, g_ref) and torch.equal(up, u_ref), "projections differ from linear_forward"
     assert torch.equal(act, a_ref), "activation differs from swiglu_forward on the stored projections"
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,in_f,outs", [(32768, 1024, (1024, 256, 256)), (4096, 256, (256, 128, 128)), (1000, 136, (200, 72)),
+                                            (256, 128, (64,)), (20000, 512, (512, 512, 1024))])
+def test_linear_forward_fused(ops, dtype, rows, in_f, outs):
+    """Several projections of one input in one launch: bit-identical to the separate linear_forward calls."""
+    g = torch.Generator(device="cuda").manual_seed(rows + in_f + len(outs))
+    x = torch.randn(rows, in_f, generator=g, device="cuda").to(dtype)
+    ws = [(torch.randn(o, in_f, generator=g, device="cuda") * 0.05).to(dtype) for o in outs]
+    ys = [torch.full((rows, o), float("nan"), device="cuda", dtype=dtype) for o in outs]
+    ops.linear_forward_fused(ys, x, ws)
+    for y, w in zip(ys, ws):
+        ref = torch.empty_like(y)
+        ops.linear_forward(ref, x, w)
+        torch.cuda.synchronize()
+        assert torch.equal(y, ref), f"fused projection {tuple(w.shape)} differs from linear_forward"
+        assert_close(host(y[:512]), host(x[:512].float() @ w.float().t()), TOL[dtype], "fused projection vs fp32")
