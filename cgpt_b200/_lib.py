@@ -107,6 +107,7 @@ SIGNATURES = {
     "cgpt_linear_forward": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _i, _vp]),
     "cgpt_linear_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _i, _i, _i, _i, _vp]),
     "cgpt_linear_forward_fused": (_i, [C.POINTER(_vp), _vp, C.POINTER(_vp), C.POINTER(_sz), _sz, _sz, _sz, _i, _vp]),
+    "cgpt_linear_backward_weight_fused": (_i, [C.POINTER(_vp), C.POINTER(_vp), _vp, C.POINTER(_sz), _sz, _sz, _sz, _i, _i, _vp]),
     "cgpt_linear_swiglu_forward": (_i, [_vp] * 6 + [_sz] * 3 + [_i, _vp]),
     "cgpt_linear_backward_input_fused": (_i, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_sz), _sz, _sz, _sz, _i, _i, _vp]),
     "cgpt_attention_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _f, _i, _sz, _i, _i, _vp]),

@@ -252,13 +252,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 // out[m,n] = sum_s partial[s,m,n] (+ old out when accumulate), fixed order.
 template <typename T>
 __global__ void __launch_bounds__(256)
-splitk_reduce_kernel(T* __restrict__ out, const float* __restrict__ partial, long long mn, int splits, int accumulate) {
+splitk_reduce_kernel(T* __restrict__ out, const float* __restrict__ partial, long long mn, long long split_stride, int splits,
+                     int accumulate) {
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 4;
     for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < mn; i += stride) {
         if (i + 4 <= mn && (mn & 3) == 0) {
             float4 acc = *reinterpret_cast<const float4*>(partial + i);
             for (int s = 1; s < splits; ++s) {
-                const float4 p = *reinterpret_cast<const float4*>(partial + s * mn + i);
+                const float4 p = *reinterpret_cast<const float4*>(partial + s * split_stride + i);
                 acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
             }
             float v[4] = {acc.x, acc.y, acc.z, acc.w};
@@ -272,7 +273,7 @@ splitk_reduce_kernel(T* __restrict__ out, const float* __restrict__ partial, lon
         } else {
             for (long long j = i; j < mn && j < i + 4; ++j) {
                 float acc = 0.f;
-                for (int s = 0; s < splits; ++s) acc += partial[s * mn + j];
+                for (int s = 0; s < splits; ++s) acc += partial[s * split_stride + j];
                 if (accumulate) acc += to_f32<T>(out[j]);
                 out[j] = from_f32<T>(acc);
             }
@@ -362,6 +363,7 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
     GemmOperands ops;
     ops.segments = segments;
     ops.groups = 1;
+    ops.group_dim = 0;
     ops.tile_end[0] = ops.tile_end[1] = ops.tile_end[2] = 0;
     int total_kb = 0;
     long long K = 0;   // summed: split heuristics and the FLOP count
@@ -458,7 +460,7 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
         long long blocks = (mn / 4 + 255) / 256;
         if (blocks > kNumSMs * 8) blocks = kNumSMs * 8;
         if (blocks < 1) blocks = 1;
-        splitk_reduce_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, s>>>(C, partial, mn, splits, accumulate);
+        splitk_reduce_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, s>>>(C, partial, mn, mn, splits, accumulate);
         count_launch();
         CGPT_LAUNCH_CHECK();
     }
@@ -495,6 +497,7 @@ int launch_tc_groups(T* const* Cs, const T* A, const T* const* Bs, const int* Ns
     GemmOutputs outs;
     ops.segments = 1;
     ops.groups = groups;
+    ops.group_dim = 0;
     const std::uint64_t a_dims[2] = {static_cast<std::uint64_t>(K), static_cast<std::uint64_t>(M)};
     const std::uint64_t k_st[1] = {static_cast<std::uint64_t>(K) * 2};
     const std::uint32_t a_box[2] = {BK, BM}, b_box[2] = {BK, BN}, c_box[2] = {64, BM};
@@ -535,6 +538,100 @@ int launch_tc_groups(T* const* Cs, const T* A, const T* const* Bs, const int* Ns
         CGPT_CUDA_TRY(cudaEventRecord(g_timing.events[g_timing.used + 1], s));
         g_timing.used += 2;
         g_timing.flops.push_back(flops);
+    }
+    return CGPT_OK;
+}
+
+// dW_g[M_g, N] (+)= dY_g[K, M_g]^T X[K, N] for up to three weight gradients that share X, as ONE launch: the M tiles of
+// all groups form one work list (both operands MN-major, K = tokens). With few tiles K is split as in the plain
+// launcher: fp32 partials [split][sum of padded M_g][N], then one fixed-order reduce per group.
+template <typename T>
+int launch_tc_mgroups(T* const* Cs, const T* const* As, const T* B, const int* Ms, int groups, int N, int K, int accumulate,
+                      int dtype, cudaStream_t s) {
+    constexpr int BN = 256;
+    using Cfg = GemmCfg<BN>;
+    if (groups < 1 || groups > kMaxKSegments || !aligned16(B) || N % 8 != 0 || N < BN || K < 32) return CGPT_ERR_UNSUPPORTED;
+    GemmOperands ops;
+    GemmOutputs outs;
+    ops.segments = 1;
+    ops.groups = groups;
+    ops.group_dim = 1;
+    const std::uint64_t b_dims[2] = {static_cast<std::uint64_t>(N), static_cast<std::uint64_t>(K)};
+    const std::uint64_t b_st[1] = {static_cast<std::uint64_t>(N) * 2};
+    const std::uint32_t mn_box[2] = {64, BK}, c_box[2] = {64, BM};
+    int tiles_m = 0;
+    double flops = 0.0;
+    int m_first[kMaxKSegments] = {0, 0, 0};
+    for (int i = 0; i < kMaxKSegments; ++i) {
+        const int g = i < groups ? i : 0;
+        if (!aligned16(Cs[g]) || !aligned16(As[g]) || Ms[g] % 8 != 0 || Ms[g] <= 0) return CGPT_ERR_UNSUPPORTED;
+        const std::uint64_t a_dims[2] = {static_cast<std::uint64_t>(Ms[g]), static_cast<std::uint64_t>(K)};
+        const std::uint64_t a_st[1] = {static_cast<std::uint64_t>(Ms[g]) * 2};
+        CGPT_TRY(make_tensor_map(&ops.a[i], dtype, As[g], 2, a_dims, a_st, mn_box));
+        CGPT_TRY(make_tensor_map(&ops.b[i], dtype, B, 2, b_dims, b_st, mn_box));
+        const std::uint64_t c_dims[2] = {static_cast<std::uint64_t>(N), static_cast<std::uint64_t>(Ms[g])};
+        CGPT_TRY(make_tensor_map(&outs.c[i], dtype, Cs[g], 2, c_dims, b_st, c_box));
+        if (i < groups) {
+            m_first[i] = tiles_m * BM;
+            tiles_m += (Ms[g] + BM - 1) / BM;
+            flops += 2.0 * Ms[g] * N * K;
+        }
+        ops.tile_end[i] = tiles_m;
+        ops.kb_end[i] = (K + BK - 1) / BK;
+    }
+    const int tiles_n = (N + BN - 1) / BN;
+    const int total_kb = (K + BK - 1) / BK;
+    const int tiles = tiles_m * tiles_n;
+    int splits = 1;
+    if (tiles < kNumSMs) {
+        splits = kNumSMs / tiles;
+        const int max_by_k = total_kb / 8 > 0 ? total_kb / 8 : 1;
+        if (splits > max_by_k) splits = max_by_k;
+        if (splits > 32) splits = 32;
+        if (splits < 1) splits = 1;
+    }
+    if (accumulate && splits == 1) splits = total_kb >= 2 ? 2 : 1;   // the read-add-store of dW happens in the reduce kernel
+    if (accumulate && splits == 1) return CGPT_ERR_UNSUPPORTED;
+    const int kb_per_split = (total_kb + splits - 1) / splits;
+    splits = (total_kb + kb_per_split - 1) / kb_per_split;
+    const int m_pad = tiles_m * BM;
+    float* partial = nullptr;
+    if (splits > 1) {
+        void* scratch = nullptr;
+        CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(splits) * m_pad * N * sizeof(float), s));
+        partial = static_cast<float*>(scratch);
+    }
+    auto pkernel = gemm_tcgen05_persistent_kernel<T, BN, true, true>;
+    static PerDeviceOnce attr_once;
+    if (attr_once.needed()) {
+        CGPT_CUDA_TRY(cudaFuncSetAttribute(pkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        attr_once.done();
+    }
+    const long long units = static_cast<long long>(tiles) * splits;
+    const unsigned grid = static_cast<unsigned>(units < kNumSMs ? units : kNumSMs);
+    const bool timed = g_timing.enabled && g_timing.used + 2 <= g_timing.events.size();
+    if (timed) CGPT_CUDA_TRY(cudaEventRecord(g_timing.events[g_timing.used], s));
+    pkernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ops, outs, Cs[0], partial, m_pad, N, total_kb, tiles_m, tiles_n, splits,
+                                                       kb_per_split, splits > 1 ? kEpiPartial : kEpiStoreTma);
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+    if (timed) {
+        CGPT_CUDA_TRY(cudaEventRecord(g_timing.events[g_timing.used + 1], s));
+        g_timing.used += 2;
+        g_timing.flops.push_back(flops);
+    }
+    if (splits > 1) {
+        const long long split_stride = static_cast<long long>(m_pad) * N;
+        for (int g = 0; g < groups; ++g) {
+            const long long mn = static_cast<long long>(Ms[g]) * N;
+            long long blocks = (mn / 4 + 255) / 256;
+            if (blocks > kNumSMs * 8) blocks = kNumSMs * 8;
+            if (blocks < 1) blocks = 1;
+            splitk_reduce_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, s>>>(Cs[g], partial + static_cast<long long>(m_first[g]) * N,
+                                                                                 mn, split_stride, splits, accumulate);
+            count_launch();
+            CGPT_LAUNCH_CHECK();
+        }
     }
     return CGPT_OK;
 }
@@ -702,6 +799,35 @@ extern "C" int cgpt_linear_forward_fused(void* const* y, const void* x, const vo
     for (size_t i = 0; i < count; ++i)
         CGPT_TRY(gemm_dispatch(y[i], x, w[i], static_cast<long long>(rows), static_cast<long long>(out_features[i]),
                                static_cast<long long>(in_features), 0, 0, 0, dtype, false, s));
+    return CGPT_OK;
+}
+
+extern "C" int cgpt_linear_backward_weight_fused(void* const* dw, const void* const* dy, const void* x, const size_t* out_features,
+                                                 size_t count, size_t rows, size_t in_features, int accumulate_weight, int dtype,
+                                                 cgpt_stream_t stream) {
+    if (!dw || !dy || !x || !out_features) return CGPT_ERR_NULL;
+    if (count < 1 || count > static_cast<size_t>(kMaxKSegments)) return CGPT_ERR_SHAPE;
+    auto s = static_cast<cudaStream_t>(stream);
+    int ms[kMaxKSegments] = {0, 0, 0};
+    for (size_t i = 0; i < count; ++i) {
+        if (!dw[i] || !dy[i]) return CGPT_ERR_NULL;
+        if (out_features[i] == 0 || out_features[i] > 0x7fffffffull) return CGPT_ERR_SHAPE;
+        ms[i] = static_cast<int>(out_features[i]);
+    }
+    if (rows == 0 || in_features == 0 || rows > 0x7fffffffull || in_features > 0x7fffffffull) return CGPT_ERR_SHAPE;
+    int rc = CGPT_ERR_UNSUPPORTED;
+    if (dtype == CGPT_DTYPE_F16)
+        rc = launch_tc_mgroups<__half>(reinterpret_cast<__half* const*>(dw), reinterpret_cast<const __half* const*>(dy),
+                                       static_cast<const __half*>(x), ms, static_cast<int>(count), static_cast<int>(in_features),
+                                       static_cast<int>(rows), accumulate_weight, dtype, s);
+    else if (dtype == CGPT_DTYPE_BF16)
+        rc = launch_tc_mgroups<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16* const*>(dw), reinterpret_cast<const __nv_bfloat16* const*>(dy),
+                                              static_cast<const __nv_bfloat16*>(x), ms, static_cast<int>(count),
+                                              static_cast<int>(in_features), static_cast<int>(rows), accumulate_weight, dtype, s);
+    if (rc != CGPT_ERR_UNSUPPORTED) return rc;
+    for (size_t i = 0; i < count; ++i)   // dW_i = dY_i^T X
+        CGPT_TRY(gemm_dispatch(dw[i], dy[i], x, static_cast<long long>(out_features[i]), static_cast<long long>(in_features),
+                               static_cast<long long>(rows), 1, 1, accumulate_weight, dtype, false, s));
     return CGPT_OK;
 }
 

@@ -66,6 +66,7 @@ struct GemmOperands {
     // one launch (Q, K and V projections of the same input). The N tiles of the groups are numbered consecutively;
     // group g owns tiles [tile_end[g-1], tile_end[g]). groups == 1: the plain case.
     int groups;
+    int group_dim;                 // 0: groups split the N tiles (own B_g, C_g); 1: they split the M tiles (own A_g, C_g)
     int tile_end[kMaxKSegments];
 };
 struct GemmOutputs {
@@ -130,18 +131,20 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ GemmOperands ops, const _
                     int seg = 0, kb_first = 0;
                     if (ops.segments > 1 && kb >= ops.kb_end[0]) { seg = 1; kb_first = ops.kb_end[0]; }
                     if (ops.segments > 2 && kb >= ops.kb_end[1]) { seg = 2; kb_first = ops.kb_end[1]; }
+                    const int tile_g = ops.group_dim ? tile_m : tile_n;
                     int group = 0, tile_first = 0;
-                    if (ops.groups > 1 && tile_n >= ops.tile_end[0]) { group = 1; tile_first = ops.tile_end[0]; }
-                    if (ops.groups > 2 && tile_n >= ops.tile_end[1]) { group = 2; tile_first = ops.tile_end[1]; }
-                    const int tile_n_b = tile_n - tile_first;          // N tile inside the group's own B
-                    const CUtensorMap* tmap_a = &ops.a[seg];
+                    if (ops.groups > 1 && tile_g >= ops.tile_end[0]) { group = 1; tile_first = ops.tile_end[0]; }
+                    if (ops.groups > 2 && tile_g >= ops.tile_end[1]) { group = 2; tile_first = ops.tile_end[1]; }
+                    const int tile_n_b = ops.group_dim ? tile_n : tile_n - tile_first;   // N tile inside the group's own B
+                    const int tile_m_a = ops.group_dim ? tile_m - tile_first : tile_m;   // M tile inside the group's own A
+                    const CUtensorMap* tmap_a = &ops.a[ops.groups > 1 ? group : seg];
                     const CUtensorMap* tmap_b = &ops.b[ops.groups > 1 ? group : seg];
                     const int k0 = (kb - kb_first) * BK;
                     if (!A_MN) {
-                        tma_load_2d(a_dst, tmap_a, &full[s], k0, tile_m * BM);
+                        tma_load_2d(a_dst, tmap_a, &full[s], k0, tile_m_a * BM);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * (BK * 128), tmap_a, &full[s], tile_m * BM + j * 64, k0);
+                        for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * (BK * 128), tmap_a, &full[s], tile_m_a * BM + j * 64, k0);
                     }
                     if (!B_MN) {
                         tma_load_2d(b_dst, tmap_b, &full[s], k0, tile_n_b * BN);
@@ -223,12 +226,15 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ GemmOperands ops, const _
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                     if (et == 0 && epilogue != kEpiStageOnly) {
                         const bool fixed = epilogue == kEpiStoreTmaFixed;   // diagnosis: every store lands on the same 16 KB
+                        const int tile_g = ops.group_dim ? tile_m : tile_n;
                         int group = 0, tile_first = 0;
-                        if (ops.groups > 1 && tile_n >= ops.tile_end[0]) { group = 1; tile_first = ops.tile_end[0]; }
-                        if (ops.groups > 2 && tile_n >= ops.tile_end[1]) { group = 2; tile_first = ops.tile_end[1]; }
+                        if (ops.groups > 1 && tile_g >= ops.tile_end[0]) { group = 1; tile_first = ops.tile_end[0]; }
+                        if (ops.groups > 2 && tile_g >= ops.tile_end[1]) { group = 2; tile_first = ops.tile_end[1]; }
+                        const int cx = (ops.group_dim ? tile_n : tile_n - tile_first) * BN + c0;
+                        const int cy = (ops.group_dim ? tile_m - tile_first : tile_m) * BM;
                         asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                                      ::"l"(reinterpret_cast<std::uint64_t>(&outs.c[group])), "r"(smem_u32(buf_s)),
-                                       "r"(fixed ? 0 : (tile_n - tile_first) * BN + c0), "r"(fixed ? 0 : tile_m * BM)
+                                       "r"(fixed ? 0 : cx), "r"(fixed ? 0 : cy)
                                      : "memory");
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }

@@ -157,10 +157,12 @@ int mlp_backward(void* grad_in, const void* grad_out, const void* in, const cgpt
         const size_t outs[2] = {m.inter, m.inter};
         CGPT_TRY(cgpt_linear_backward_input_fused(ws.d_ffn_norm_in, dys, wts, outs, 2, m.rows, m.d, 0, dt, stream));
     }
-    CGPT_TRY(cgpt_linear_backward(nullptr, g->gate_proj, nullptr, ws.d_gate, sv->norm, nullptr, m.rows, m.d, m.inter, 0, 0, 0,
-                                  dt, stream));
-    CGPT_TRY(cgpt_linear_backward(nullptr, g->up_proj, nullptr, ws.d_up, sv->norm, nullptr, m.rows, m.d, m.inter, 0, 0, 0, dt,
-                                  stream));
+    {   // both weight gradients of the FFN input as one launch
+        void* dws[2] = {g->gate_proj, g->up_proj};
+        const void* dys[2] = {ws.d_gate, ws.d_up};
+        const size_t outs[2] = {m.inter, m.inter};
+        CGPT_TRY(cgpt_linear_backward_weight_fused(dws, dys, sv->norm, outs, 2, m.rows, m.d, 0, dt, stream));
+    }
     // grad_in = grad_out + d(ffn_norm)  (the reference's D2D copy + add_inplace, :678-681)
     return cgpt_rmsnorm_backward(grad_in, g->ffn_norm, ws.d_ffn_norm_in, in, w->ffn_norm, grad_out, nullptr, m.rows, m.d, eps,
                                  dt, stream);
@@ -271,12 +273,12 @@ extern "C" int cgpt_block_backward(void* grad_in, const void* grad_out, const vo
         const size_t outs[3] = {m.qdim, m.kvdim, m.kvdim};
         CGPT_TRY(cgpt_linear_backward_input_fused(ws.d_attn_norm_in, dys, wts, outs, 3, m.rows, m.d, 0, dt, stream));
     }
-    CGPT_TRY(cgpt_linear_backward(nullptr, g->q_projection, nullptr, ws.dq_pre, norm_a, nullptr, m.rows, m.d, m.qdim, 0, 0,
-                                  0, dt, stream));
-    CGPT_TRY(cgpt_linear_backward(nullptr, g->k_projection, nullptr, ws.dk_pre, norm_a, nullptr, m.rows, m.d, m.kvdim, 0, 0,
-                                  0, dt, stream));
-    CGPT_TRY(cgpt_linear_backward(nullptr, g->v_projection, nullptr, ws.dv, norm_a, nullptr, m.rows, m.d, m.kvdim, 0, 0, 0,
-                                  dt, stream));
+    {   // the three weight gradients of the attention input as one launch
+        void* dws[3] = {g->q_projection, g->k_projection, g->v_projection};
+        const void* dys[3] = {ws.dq_pre, ws.dk_pre, ws.dv};
+        const size_t outs[3] = {m.qdim, m.kvdim, m.kvdim};
+        CGPT_TRY(cgpt_linear_backward_weight_fused(dws, dys, norm_a, outs, 3, m.rows, m.d, 0, dt, stream));
+    }
     // grad_in += d(attention_norm): needs the MLP branch's grad_in
     CGPT_TRY(br.join());
     return cgpt_rmsnorm_backward(grad_in, g->attention_norm, ws.d_attn_norm_in, in, w->attention_norm, grad_in, nullptr,

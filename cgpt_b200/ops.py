@@ -122,6 +122,25 @@ def linear_forward_fused(outputs, input, weights, stream=None):
           "linear_forward_fused")
 
 
+def linear_backward_weight_fused(grad_weights, grad_outputs, input, stream=None, accumulate_weight: bool = False):
+    """grad_weights[i] (+)= grad_outputs[i].T @ input for up to three projections of one input, as one launch
+    (cgpt_linear_backward_weight_fused; the reference runs one linear_backward per projection)."""
+    import ctypes as C
+    n = len(grad_weights)
+    _require(1 <= n <= 3 and len(grad_outputs) == n, "linear_backward_weight_fused: 1..3 projections")
+    _same_cuda_dtype("linear_backward_weight_fused", input, *grad_weights, *grad_outputs)
+    in_f = input.shape[-1]
+    rows = input.numel() // in_f
+    for gw, dy in zip(grad_weights, grad_outputs):
+        _require(gw.dim() == 2 and gw.shape[1] == in_f and dy.shape[-1] == gw.shape[0] and dy.numel() == rows * gw.shape[0],
+                 "linear_backward_weight_fused: incompatible shapes")
+    gws = (C.c_void_p * n)(*[ptr(t) for t in grad_weights])
+    dys = (C.c_void_p * n)(*[ptr(t) for t in grad_outputs])
+    outs = (C.c_size_t * n)(*[gw.shape[0] for gw in grad_weights])
+    check(lib.cgpt_linear_backward_weight_fused(gws, dys, ptr(input), outs, n, rows, in_f, int(accumulate_weight),
+                                                dtype_code(input), stream_ptr(stream)), "linear_backward_weight_fused")
+
+
 def linear_swiglu_forward(gate, up, activated, input, gate_weight, up_weight, stream=None):
     """gate = input @ gate_weight.T, up = input @ up_weight.T, activated = swiglu(gate, up) in one launch
     (cgpt_linear_swiglu_forward; the reference's block forward calls linear_forward twice and swiglu_forward)."""

@@ -107,6 +107,16 @@ int cgpt_linear_backward(void* dx, void* dw, void* db, const void* dy, const voi
 int cgpt_linear_forward_fused(void* const* y, const void* x, const void* const* w, const size_t* out_features,
                               size_t count, size_t rows, size_t in_features, int dtype, cgpt_stream_t stream);
 
+/* Weight gradients of `count` (1..3) projections of the same input as one launch:
+ *      dW_i[out_i,in] (+)= dY_i[rows,out_i]^T X[rows,in].
+ * Replaces consecutive linear_backward calls that share `input` (reference src/core/transformer_block.cu:669-675 gate/up,
+ * :726-744 q/k/v): the output tiles of all products form one work list, so small products (key/value projections of a
+ * grouped-query model) no longer run as launches of their own, each with its own K split and reduction.
+ * dw, dy: host arrays of `count` device pointers. Runs as separate products when the tensor-core path does not apply. */
+int cgpt_linear_backward_weight_fused(void* const* dw, const void* const* dy, const void* x, const size_t* out_features,
+                                      size_t count, size_t rows, size_t in_features, int accumulate_weight, int dtype,
+                                      cgpt_stream_t stream);
+
 /* Gate and up projections with the SwiGLU activation in the GEMM epilogue:
  *      gate = X Wg^T, up = X Wu^T, activated = gate / (1 + exp(-gate)) * up      (all [rows, intermediate]).
  * Replaces the sequence linear_forward, linear_forward, swiglu_forward of the block forward (reference

@@ -164,3 +164,26 @@ def test_linear_forward_fused(ops, dtype, rows, in_f, outs):
         torch.cuda.synchronize()
         assert torch.equal(y, ref), f"fused projection {tuple(w.shape)} differs from linear_forward"
         assert_close(host(y[:512]), host(x[:512].float() @ w.float().t()), TOL[dtype], "fused projection vs fp32")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,in_f,outs", [(32768, 1024, (1024, 256, 256)), (8192, 1024, (2048, 2048)), (4096, 256, (256, 128, 128)),
+                                            (1000, 264, (200, 72)), (512, 512, (64,)), (20000, 512, (512, 384, 1024))])
+def test_linear_backward_weight_fused(ops, dtype, rows, in_f, outs):
+    """dW_i = dY_i^T X for several projections of one input in one launch, against the fp32 products, with and without
+    accumulation into dW."""
+    g = torch.Generator(device="cuda").manual_seed(rows + in_f + len(outs))
+    x = torch.randn(rows, in_f, generator=g, device="cuda").to(dtype)
+    dys = [(torch.randn(rows, o, generator=g, device="cuda") * 0.05).to(dtype) for o in outs]
+    want = [dy.float().t() @ x.float() for dy in dys]
+    gws = [torch.full((o, in_f), float("nan"), device="cuda", dtype=dtype) for o in outs]
+    ops.linear_backward_weight_fused(gws, dys, x)
+    torch.cuda.synchronize()
+    tol = 2 * TOL[dtype] if dtype != torch.float32 else 1e-4       # K = rows: long fp32 sums, one rounding
+    for gw, w in zip(gws, want):
+        assert_close(host(gw), host(w), tol, f"fused dW {dtype} {tuple(gw.shape)}")
+    base = [torch.randn(o, in_f, generator=g, device="cuda").to(dtype) for o in outs]
+    acc = [b.clone() for b in base]
+    ops.linear_backward_weight_fused(acc, dys, x, accumulate_weight=True)
+    for a, b, w in zip(acc, base, want):
+        assert_close(host(a), host(w + b.float()), tol, f"fused dW accumulate {dtype}")
