@@ -1,13 +1,13 @@
 // Kernel body and host launch of the tensor-core attention backward. Included by attention_bwd_tc.cu only.
 #pragma once
 
+// One CTA's work: work item `item` of the dQ kernel (MODE_DQ) or of the dK/dV kernel (MODE_DKV).
 template <typename T, int D, int MODE>
-__global__ void __launch_bounds__(kBwdThreads, 1)
-attention_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_constant__ CUtensorMap map_x2,
-                        const __grid_constant__ CUtensorMap map_y1, const __grid_constant__ CUtensorMap map_y2,
-                        T* __restrict__ out1, T* __restrict__ out2, const float* __restrict__ lse2_t,
-                        const float* __restrict__ delta_t, AttnDims dm, int accumulate, unsigned int* __restrict__ status,
-                        unsigned long long* trace) {
+__device__ __forceinline__ void bwd_cta(const CUtensorMap& map_x1, const CUtensorMap& map_x2, const CUtensorMap& map_y1,
+                                        const CUtensorMap& map_y2, T* __restrict__ out1, T* __restrict__ out2,
+                                        const float* __restrict__ lse2_t, const float* __restrict__ delta_t, const AttnDims& dm,
+                                        int accumulate, unsigned int* __restrict__ status, unsigned long long* trace, int item,
+                                        int items) {
     using L = BwdSmem<D>;
     extern __shared__ unsigned char bwd_smem_raw[];
     const std::uint32_t raw = smem_u32(bwd_smem_raw);
@@ -22,7 +22,7 @@ attention_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid
     bars.t_full = bars.uw_free + 2;             // [2]
     bars.w_full = bars.uw_free + 4;             // [2]
     bars.acc_done = bars.uw_free + 6;
-    bars.trace = (trace != nullptr && blockIdx.x == gridDim.x / 4) ? trace : nullptr;
+    bars.trace = (trace != nullptr && item == items / 4) ? trace : nullptr;
     std::uint32_t* tmem_slot = reinterpret_cast<std::uint32_t*>(bars.acc_done + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -30,8 +30,8 @@ attention_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid
     // the causal triangle fill the tail of the launch instead of a heavy tile starting last.
     const int heads_here = MODE == MODE_DQ ? dm.hq : dm.hkv;
     const int pairs = heads_here * dm.batch;
-    const int tile_rank = static_cast<int>(blockIdx.x) / pairs;           // 0 = most streaming tiles
-    const int pair = static_cast<int>(blockIdx.x) % pairs;
+    const int tile_rank = item / pairs;           // 0 = most streaming tiles
+    const int pair = item % pairs;
     BwdGeom g;
     g.b = pair / heads_here;
     g.ratio = dm.hq / dm.hkv;
@@ -102,6 +102,38 @@ attention_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid
     }
 }
 
+template <typename T, int D, int MODE>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attention_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_x1, const __grid_constant__ CUtensorMap map_x2,
+                        const __grid_constant__ CUtensorMap map_y1, const __grid_constant__ CUtensorMap map_y2,
+                        T* __restrict__ out1, T* __restrict__ out2, const float* __restrict__ lse2_t,
+                        const float* __restrict__ delta_t, AttnDims dm, int accumulate, unsigned int* __restrict__ status,
+                        unsigned long long* trace) {
+    bwd_cta<T, D, MODE>(map_x1, map_x2, map_y1, map_y2, out1, out2, lse2_t, delta_t, dm, accumulate, status, trace,
+                        static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
+}
+
+// dK/dV and dQ in ONE launch: the first items_kv CTAs are the (few, long) dK/dV items, the rest the (many, short) dQ
+// items, each list heaviest first. The short dQ items fill the SMs that the last wave of dK/dV items would leave idle,
+// and one launch tail replaces two.
+template <typename T, int D>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attention_bwd_tc_both_kernel(const __grid_constant__ CUtensorMap k128, const __grid_constant__ CUtensorMap v128,
+                             const __grid_constant__ CUtensorMap q64, const __grid_constant__ CUtensorMap do64,
+                             const __grid_constant__ CUtensorMap q128, const __grid_constant__ CUtensorMap do128,
+                             const __grid_constant__ CUtensorMap k64, const __grid_constant__ CUtensorMap v64, T* __restrict__ dq,
+                             T* __restrict__ dk, T* __restrict__ dv, const float* __restrict__ lse2_t,
+                             const float* __restrict__ delta_t, AttnDims dm, int items_kv, int accumulate,
+                             unsigned int* __restrict__ status) {
+    const int item = static_cast<int>(blockIdx.x);
+    if (item < items_kv) {
+        bwd_cta<T, D, MODE_DKV>(k128, v128, q64, do64, dk, dv, lse2_t, delta_t, dm, accumulate, status, nullptr, item, items_kv);
+    } else {
+        bwd_cta<T, D, MODE_DQ>(q128, do128, k64, v64, dq, static_cast<T*>(nullptr), lse2_t, delta_t, dm, accumulate, status, nullptr,
+                               item - items_kv, static_cast<int>(gridDim.x) - items_kv);
+    }
+}
+
 // 4D tensor map over a [batch, seq, heads, D] tensor: box = 64 columns x 1 head x `rows` positions.
 inline int make_bshd_map_rows(CUtensorMap* map, const void* base, int dtype, int batch, int seq, int heads, int d, int rows) {
     const std::uint64_t dims[4] = {static_cast<std::uint64_t>(d), static_cast<std::uint64_t>(heads), static_cast<std::uint64_t>(seq),
@@ -149,7 +181,24 @@ int launch_backward(void* dq, void* dk, void* dv, const void* dout, const void* 
     }
     unsigned int* status = tc_status_device_ptr();
     if (status == nullptr) return CGPT_ERR_STATE;
-    const dim3 grid_q(static_cast<unsigned>(((dm.sq + kRows - 1) / kRows) * dm.hq * dm.batch));
+    const int items_q = ((dm.sq + kRows - 1) / kRows) * dm.hq * dm.batch;
+    const int items_kv = ((dm.sk + kRows - 1) / kRows) * dm.hkv * dm.batch;
+    static const bool split_launches = [] { const char* e = std::getenv("CGPT_B200_ATTN_SPLIT"); return e && e[0] == '1'; }();
+    if (!split_launches && std::getenv("CGPT_B200_ATTN_TRACE") == nullptr) {
+        auto kboth = attention_bwd_tc_both_kernel<T, D>;
+        static PerDeviceOnce both_once;
+        if (both_once.needed()) {
+            CGPT_CUDA_TRY(cudaFuncSetAttribute(kboth, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
+            both_once.done();
+        }
+        kboth<<<static_cast<unsigned>(items_q + items_kv), kBwdThreads, L::kBytes, s>>>(
+            k128, v128, q64, do64, q128, do128, k64, v64, static_cast<T*>(dq), static_cast<T*>(dk), static_cast<T*>(dv), lse2_t, delta_t, dm,
+            items_kv, accumulate, status);
+        count_launch();
+        CGPT_LAUNCH_CHECK();
+        return CGPT_OK;
+    }
+    const dim3 grid_q(static_cast<unsigned>(items_q));
     // CGPT_B200_ATTN_TRACE=<device pointer of 2*64*8 uint64> records per-iteration timestamps of one CTA per kernel (diagnosis)
     unsigned long long* trace = nullptr;
     if (const char* e = std::getenv("CGPT_B200_ATTN_TRACE")) trace = reinterpret_cast<unsigned long long*>(std::strtoull(e, nullptr, 0));
