@@ -8,9 +8,9 @@
 //   dX       dX[T,in]   = dY[T,out] * W [out,in]       A K-major,  B N-major (MN-major tile)
 //   dW       dW[out,in] = dY[T,out]^T * X [T,in]       A M-major,  B N-major, reduction over T
 //
-// Kernel shape: one CTA computes a 128 x BN tile (BN = 128 or 256) for a slice of K. Warp 0 issues the
-// TMA loads into a STAGES-deep ring, warp 1 issues tcgen05.mma (128 x BN x 16 per instruction, four
-// per 64-wide K block) and commits each stage back to the producer, warps 2-5 drain the fp32
+// Kernel shape (gemm_persistent.cuh): one persistent CTA per SM walks 128 x BN tiles (BN = 128 or 256), each for a
+// slice of K. Warp 0 issues the TMA loads into a STAGES-deep ring, warp 1 issues tcgen05.mma (128 x BN x 16 per
+// instruction, four per 64-wide K block) and commits each stage back to the producer, warps 2-5 drain the fp32
 // accumulator from TMEM (tcgen05.ld), convert and store. Split-K writes fp32 partials that a small
 // kernel sums in a fixed order (deterministic; used when the tile count alone cannot fill 148 SMs,
 // e.g. dW with K = tokens). Algorithmic work: 2*M*N*K flops.
@@ -86,7 +86,7 @@ __device__ unsigned int g_gemm_status = 0;
 enum : int { kEpiStore = 0, kEpiAccumulate = 1, kEpiPartial = 2, kEpiNone = 3, kEpiStoreTma = 4, kEpiStageOnly = 5, kEpiStoreTmaFixed = 6 };
 
 // Optional timing of the tensor-core GEMM launches (eager mode only, never during stream capture):
-// a CUDA event pair around every gemm_tcgen05_kernel launch plus its algorithmic FLOPs.
+// a CUDA event pair around every tensor-core GEMM launch plus its algorithmic FLOPs.
 struct GemmTiming {
     bool enabled = false;
     std::vector<cudaEvent_t> events;   // pairs
@@ -94,160 +94,6 @@ struct GemmTiming {
     std::size_t used = 0;              // events used
 };
 GemmTiming g_timing;
-
-template <typename T, int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    T* __restrict__ C, float* __restrict__ partial, int M, int N, int K, int kb_per_split, int epilogue) {
-    using Cfg = GemmCfg<BN>;
-    extern __shared__ unsigned char gemm_smem_raw[];
-    const std::uint32_t raw = smem_u32(gemm_smem_raw);
-    unsigned char* smem = gemm_smem_raw + ((1024u - (raw & 1023u)) & 1023u);
-    std::uint64_t* bars = reinterpret_cast<std::uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
-    std::uint64_t* full = bars;
-    std::uint64_t* empty = bars + Cfg::kStages;
-    std::uint64_t* acc_full = bars + 2 * Cfg::kStages;
-    std::uint32_t* tmem_slot = reinterpret_cast<std::uint32_t*>(bars + 2 * Cfg::kStages + 1);
-
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-    const int tile_m = blockIdx.x, tile_n = blockIdx.y, split = blockIdx.z;
-    const int total_kb = (K + BK - 1) / BK;
-    const int kb_begin = split * kb_per_split;
-    int nkb = total_kb - kb_begin;
-    if (nkb > kb_per_split) nkb = kb_per_split;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        mbar_init(acc_full, 1);
-        mbar_init_fence();
-        tma_prefetch_desc(&tmap_a);
-        tma_prefetch_desc(&tmap_b);
-    }
-    if (warp == 1) {
-        tmem_alloc(tmem_slot, BN);
-        tmem_relinquish();
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
-    const std::uint32_t tmem_acc = *tmem_slot;
-    bool failed = false;
-
-    if (warp == 0) {
-        if (lane == 0) {
-            for (int i = 0; i < nkb; ++i) {
-                const int s = i % Cfg::kStages;
-                const std::uint32_t ph = (i / Cfg::kStages) & 1;
-                if (!mbar_wait(&empty[s], ph ^ 1u)) { failed = true; break; }
-                mbar_expect_tx(&full[s], Cfg::kStageBytes);
-                unsigned char* a_dst = smem + s * Cfg::kStageBytes;
-                unsigned char* b_dst = a_dst + Cfg::kABytes;
-                const int k0 = (kb_begin + i) * BK;
-                if (!A_MN) {
-                    tma_load_2d(a_dst, &tmap_a, &full[s], k0, tile_m * BM);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * (BK * 128), &tmap_a, &full[s], tile_m * BM + j * 64, k0);
-                }
-                if (!B_MN) {
-                    tma_load_2d(b_dst, &tmap_b, &full[s], k0, tile_n * BN);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * (BK * 128), &tmap_b, &full[s], tile_n * BN + j * 64, k0);
-                }
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0) {
-            constexpr std::uint32_t idesc = idesc_f16(sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0,
-                                                      A_MN ? 1 : 0, B_MN ? 1 : 0, BM, BN);
-            for (int i = 0; i < nkb; ++i) {
-                const int s = i % Cfg::kStages;
-                const std::uint32_t ph = (i / Cfg::kStages) & 1;
-                if (!mbar_wait(&full[s], ph)) { failed = true; break; }
-                tc_fence_after_sync();
-                const std::uint32_t a_base = smem_u32(smem + s * Cfg::kStageBytes);
-                const std::uint32_t b_base = a_base + Cfg::kABytes;
-#pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    const std::uint64_t adesc = A_MN ? smem_desc_sw128(a_base + k * (UMMA_K * 128), BK * 128, 1024)
-                                                     : smem_desc_sw128(a_base + k * (UMMA_K * 2), 16, 1024);
-                    const std::uint64_t bdesc = B_MN ? smem_desc_sw128(b_base + k * (UMMA_K * 128), BK * 128, 1024)
-                                                     : smem_desc_sw128(b_base + k * (UMMA_K * 2), 16, 1024);
-                    mma_f16_ss(tmem_acc, adesc, bdesc, idesc, (i > 0 || k > 0) ? 1u : 0u);
-                }
-                tc_commit(&empty[s]);   // frees the stage once these MMAs have read it
-            }
-            tc_commit(acc_full);        // accumulator complete
-        }
-    } else {
-        // Epilogue: warps 2..5 own TMEM lane quarters (warp % 4).
-        const int quarter = warp & 3;
-        if (!mbar_wait(acc_full, 0)) failed = true;
-        failed = __any_sync(0xffffffffu, failed);   // keep the warp-collective TMEM loads uniform
-        tc_fence_after_sync();
-        const int row = tile_m * BM + quarter * 32 + lane;
-        const long long out_row = static_cast<long long>(row) * N;
-        if (!failed) {
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                std::uint32_t r[32];
-                tmem_ld_32x32(tmem_acc + (static_cast<std::uint32_t>(quarter * 32) << 16) + c0, r);
-                const int col0 = tile_n * BN + c0;
-                if (row < M && col0 < N) {
-                    if (epilogue == kEpiPartial) {
-                        float* dst = partial + (static_cast<long long>(split) * M + row) * N + col0;
-                        if (col0 + 32 <= N && (N & 3) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                                                  __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                        } else {
-                            for (int j = 0; j < 32 && col0 + j < N; ++j) dst[j] = __uint_as_float(r[j]);
-                        }
-                    } else {
-                        T* dst = C + out_row + col0;
-                        if (col0 + 32 <= N && (N & 7) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                float v[8];
-#pragma unroll
-                                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
-                                if (epilogue == kEpiAccumulate) {
-                                    float old[8];
-                                    load_vec<T, 8>(old, dst + j);
-#pragma unroll
-                                    for (int e = 0; e < 8; ++e) v[e] += old[e];
-                                }
-                                store_vec<T, 8>(dst + j, v);
-                            }
-                        } else {
-                            for (int j = 0; j < 32 && col0 + j < N; ++j) {
-                                float v = __uint_as_float(r[j]);
-                                if (epilogue == kEpiAccumulate) v += to_f32<T>(dst[j]);
-                                dst[j] = from_f32<T>(v);
-                            }
-                        }
-                    }
-                }
-            }
-        }
-    }
-
-    if (failed) {
-        atomicExch(&g_gemm_status, 1u);
-        // Give outstanding TMA writes into this CTA's shared memory time to land before it exits.
-        const unsigned long long t0 = globaltimer_ns();
-        while (globaltimer_ns() - t0 < 200000ull) { }
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    if (warp == 1) {
-        tc_fence_after_sync();
-        tmem_dealloc(tmem_acc, BN);
-    }
-}
 
 // out[m,n] = sum_s partial[s,m,n] (+ old out when accumulate), fixed order.
 template <typename T>
@@ -349,12 +195,6 @@ column_sum_kernel(T* __restrict__ out, const T* __restrict__ in, long long rows,
 #include "gemm_persistent.cuh"
 #include "gemm_swiglu.cuh"
 
-// CGPT_B200_GEMM_V1=1 selects the one-tile-per-CTA kernel instead of the persistent one (for A/B timing).
-inline bool use_v1_gemm() {
-    static const bool v1 = [] { const char* e = std::getenv("CGPT_B200_GEMM_V1"); return e != nullptr && e[0] == '1'; }();
-    return v1;
-}
-
 // C[M,N] (+)= sum_i A_i[M,K_i] * B_i, i < segments (1..kMaxKSegments): one launch, one pass over C.
 template <typename T, int BN, bool A_MN, bool B_MN>
 int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int segments, int M, int N, int accumulate, int dtype,
@@ -388,7 +228,6 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
         ops.kb_end[i] = total_kb;
     }
     const CUtensorMap& ta = ops.a[0];
-    const CUtensorMap& tb = ops.b[0];
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
     // Split K when the output tiles alone leave most SMs idle and K is long enough to amortise it.
     int splits = 1;
@@ -408,11 +247,9 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
         CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(splits) * M * N * sizeof(float), s));
         partial = static_cast<float*>(scratch);
     }
-    auto kernel = gemm_tcgen05_kernel<T, BN, A_MN, B_MN>;
     auto pkernel = gemm_tcgen05_persistent_kernel<T, BN, A_MN, B_MN>;
     static PerDeviceOnce attr_once;
     if (attr_once.needed()) {
-        CGPT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         CGPT_CUDA_TRY(cudaFuncSetAttribute(pkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         attr_once.done();
     }
@@ -423,10 +260,7 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
     }
     const bool timed = g_timing.enabled && g_timing.used + 2 <= g_timing.events.size();
     if (timed) CGPT_CUDA_TRY(cudaEventRecord(g_timing.events[g_timing.used], s));
-    if (use_v1_gemm() && segments == 1) {
-        const dim3 grid(tiles_m, tiles_n, splits);
-        kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, C, partial, M, N, static_cast<int>(K), kb_per_split, epi);
-    } else {
+    {
         const long long units = static_cast<long long>(tiles) * splits;
         const unsigned grid = static_cast<unsigned>(units < kNumSMs ? units : kNumSMs);
         // Plain stores of 16-bit output go through shared memory and TMA (needs a 16-byte aligned C and N % 8 == 0).

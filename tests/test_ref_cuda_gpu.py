@@ -133,9 +133,9 @@ def test_attention(ops, b, s, hq, hkv, d):
         return
     # head_dim 64 takes the reference's scalar path, which sums dK/dV with fp16 atomicAdd of fp16-rounded partials
     # (src/ops/backward/attention_backward.cu:76-80,491-492): its own rounding noise grows with the number of query
-    # rows per key and is order dependent. Both are therefore measured against the fp32 restatement: ours must meet
-    # the 1e-2 bar and must not be further from it than the reference's kernels are; the two may differ by the
-    # reference's noise (3e-2).
+    # rows per key and differs from run to run (observed 1.5e-2 .. 3.7e-2 on identical inputs). Both are therefore
+    # measured against the fp32 restatement: ours must meet the 1e-2 bar and must not be further from it than the
+    # reference's kernels are; the direct comparison only guards against a gross mismatch (1e-1).
     from gpu_util import scaled_err
     from oracle import cgpt_oracle as O
     want = O.attention_backward(host(do), host(q), host(k), host(v), host(o0), host(l0), True, 0, 0.0)
@@ -143,4 +143,4 @@ def test_attention(ops, b, s, hq, hkv, d):
         ours, theirs = scaled_err(host(a), w), scaled_err(host(r), w)
         assert ours <= 1e-2, f"attention {name}: {ours:.3e} against the fp32 restatement"
         assert ours <= theirs + 2e-3, f"attention {name}: ours {ours:.3e}, reference kernels {theirs:.3e}"
-        assert_close(host(a), host(r), 3e-2, "attention " + name + " (reference scalar path)")
+        assert_close(host(a), host(r), 1e-1, "attention " + name + " (reference scalar path)")
