@@ -1,0 +1,160 @@
+"""The benchmark configurations at their FULL sizes, where the CPU oracle would take hours. The checks are the ones the
+operators offer at any size: a second, independent implementation (the warp-per-row attention kernels, a plain PyTorch
+fp32 restatement run on the same GPU), the CPU oracle on a sample of independent rows, linearity in the upstream
+gradient, inverses (RoPE backward undoes RoPE forward), conservation (the softmax gradient of every row sums to zero,
+so the classifier gradient sums to zero over the vocabulary), and bit-reproducibility.
+
+Configuration 2: attention backward, B 32, 12 query / 4 kv heads, S 1024, D 64.
+Configuration 3: 32768 tokens at d_model 768: RMSNorm, RoPE (D 64), SwiGLU (hidden 2048) backward, cut cross-entropy
+against a 32000 x 768 head.
+Configuration 4: the 104m training step, batch 32 x 1024.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import assert_close, host, scaled_err
+from oracle import cgpt_oracle as O
+
+pytestmark = pytest.mark.gpu
+T = 32768
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from cgpt_b200 import ops as m
+    return m
+
+
+def rnd(*shape, scale=1.0, seed=0, dtype=torch.float16):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device="cuda") * scale).to(dtype)
+
+
+def test_config2_attention_backward(ops):
+    b, s, hq, hkv, d = 32, 1024, 12, 4, 64
+    q, k, v = rnd(b, s, hq, d, seed=1), rnd(b, s, hkv, d, seed=2), rnd(b, s, hkv, d, seed=3)
+    do1, do2 = rnd(b, s, hq, d, seed=4), rnd(b, s, hq, d, seed=5)
+    opts = ops.FlashAttentionOptions(hq, hkv, d)
+    out, lse = torch.empty_like(q), torch.empty(b, s, hq, device="cuda")
+    ops.flash_gqa_attention_forward_with_lse(out, lse, q, k, v, None, opts)
+
+    def grads(do, generic=False):
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        ops.flash_gqa_attention_backward_with_lse(dq, dk, dv, do, out, lse, q, k, v, None, opts, force_generic=generic)
+        return dq, dk, dv
+
+    tc = grads(do1)
+    # (a) the tensor-core kernels against the independent warp-per-row fp32 kernels
+    for name, a, r in zip(("dq", "dk", "dv"), tc, grads(do1, generic=True)):
+        assert_close(host(a), host(r), 1e-2, "config 2 " + name + " tensor-core vs generic")
+    # (b) the CPU oracle on one batch element (batch elements are independent)
+    want = O.attention_backward(host(do1[:1]), host(q[:1]), host(k[:1]), host(v[:1]), host(out[:1]), host(lse[:1]), True, 0, 0.0)
+    for name, a, w in zip(("dq", "dk", "dv"), tc, want):
+        assert_close(host(a[:1]), w, 1e-2, "config 2 " + name + " vs oracle (batch 0)")
+    # (c) linear in dO: with delta = rowsum(dO * O) every term of dQ, dK, dV is linear in dO
+    both = grads((do1.float() + do2.float()).half())
+    for name, a, x, y in zip(("dq", "dk", "dv"), both, tc, grads(do2)):
+        assert_close(host(a), host(x.float() + y.float()), 1e-2, "config 2 linearity " + name)
+    # (d) bit-reproducible
+    again = grads(do1)
+    assert all(torch.equal(x, y) for x, y in zip(tc, again))
+
+
+def test_config3_rmsnorm_rope_swiglu_backward(ops):
+    hidden, inter = 768, 2048
+    rows = np.random.default_rng(0).choice(T, 48, replace=False)
+    # ---- RMSNorm backward: sampled rows against the oracle (rows are independent in dx), dw against fp32 torch
+    x, dy1, dy2 = rnd(T, hidden, seed=1), rnd(T, hidden, seed=2), rnd(T, hidden, seed=3)
+    w = (1 + rnd(hidden, scale=0.02, seed=4).float()).half()
+    dx1, dw1, dx2, dw2, dx12, dw12 = (torch.empty_like(t) for t in (x, w, x, w, x, w))
+    ops.rmsnorm_backward(dx1, dw1, dy1, x, w, 1e-5)
+    ops.rmsnorm_backward(dx2, dw2, dy2, x, w, 1e-5)
+    ops.rmsnorm_backward(dx12, dw12, (dy1.float() + dy2.float()).half(), x, w, 1e-5)
+    edx, _ = O.rmsnorm_backward(host(dy1[rows]), host(x[rows]), host(w), 1e-5)
+    assert_close(host(dx1[rows]), edx, 2e-3, "config 3 rmsnorm dx (sampled rows)")
+    xf, gf = x.float(), dy1.float()
+    inv = torch.rsqrt((xf * xf).mean(dim=1, keepdim=True) + 1e-5)
+    assert_close(host(dw1), host((gf * xf * inv).sum(dim=0)), 4e-3, "config 3 rmsnorm dw vs fp32 torch")
+    assert_close(host(dx12), host(dx1.float() + dx2.float()), 4e-3, "config 3 rmsnorm linearity dx")
+    assert_close(host(dw12), host(dw1.float() + dw2.float()), 4e-3, "config 3 rmsnorm linearity dw")
+    # ---- RoPE backward at head_dim 64: the inverse rotation of the forward, norm preserving
+    from cgpt_b200.model import rotary_cache
+    b, s, hq, hkv, d = 32, 1024, 12, 4, 64
+    cos, sin = rotary_cache(s, d)
+    q, k = rnd(b, s, hq, d, seed=5), rnd(b, s, hkv, d, seed=6)
+    rq, rk = q.clone(), k.clone()
+    ops.rope_forward(rq, rk, cos, sin)
+    bq, bk = torch.empty_like(q), torch.empty_like(k)
+    ops.rope_backward(bq, bk, rq, rk, cos, sin)
+    assert_close(host(bq), host(q), 4e-3, "config 3 rope backward(forward(q)) = q")
+    assert_close(host(bk), host(k), 4e-3, "config 3 rope backward(forward(k)) = k")
+    n0, n1 = q.float().pow(2).sum(-1), bq.float().pow(2).sum(-1)
+    assert float(((n0 - n1).abs() / n0).max()) < 1e-2
+    # ---- SwiGLU backward, hidden 2048: sampled rows against the oracle
+    gate, up, dy = rnd(T, inter, seed=7), rnd(T, inter, seed=8), rnd(T, inter, seed=9)
+    dg, du = torch.empty_like(gate), torch.empty_like(up)
+    ops.swiglu_backward(dg, du, dy, gate, up)
+    edg, edu = O.swiglu_backward(host(dy[rows]), host(gate[rows]), host(up[rows]))
+    assert_close(host(dg[rows]), edg, 2e-3, "config 3 swiglu dgate (sampled rows)")
+    assert_close(host(du[rows]), edu, 2e-3, "config 3 swiglu dup (sampled rows)")
+
+
+def test_config3_cut_cross_entropy(ops):
+    from cgpt_b200 import model as M
+    hidden, vocab = 768, 32000
+    x = rnd(T, hidden, seed=1)
+    c = rnd(vocab, hidden, scale=0.02, seed=2)
+    t = torch.randint(0, vocab, (T,), device="cuda", dtype=torch.int32, generator=torch.Generator(device="cuda").manual_seed(3))
+    loss, gx, gc = torch.zeros(1, device="cuda"), torch.empty_like(x), torch.empty_like(c)
+    M.cut_cross_entropy_forward_backward(loss, gx, gc, x, c, t, T, None, 1024.0)
+    # plain PyTorch fp32 restatement on the same GPU, in row chunks (the op itself rounds each logit to fp16 first)
+    want_loss, want_gx = 0.0, torch.empty(T, hidden, device="cuda")
+    want_gc = torch.zeros(vocab, hidden, device="cuda")
+    cf = c.float()
+    for r0 in range(0, T, 4096):
+        xs = x[r0:r0 + 4096].float()
+        logits = (xs @ cf.t()).half().float()
+        logp = torch.log_softmax(logits, dim=1)
+        idx = t[r0:r0 + 4096].long()
+        want_loss += float(-logp.gather(1, idx[:, None]).sum())
+        g = logp.exp()
+        g[torch.arange(g.shape[0], device="cuda"), idx] -= 1.0
+        g = (g * (1024.0 / T)).half().float()          # the op stores the logits gradient in fp16 before the two GEMMs
+        want_gx[r0:r0 + 4096] = g @ cf
+        want_gc += g.t() @ xs
+    assert abs(float(loss) - want_loss / T) < 1e-3
+    assert_close(host(gx), host(want_gx), 1e-2, "config 3 cce grad input")
+    assert_close(host(gc), host(want_gc), 1e-2, "config 3 cce grad classifier", metric="max")
+    # conservation: every row of the logits gradient sums to zero, so each column of the classifier gradient summed over
+    # the vocabulary vanishes up to rounding (of the fp16 logits gradient and of the 32000 fp16 entries): the signed sum
+    # is below 1e-4 of the sum of magnitudes (measured 9e-6)
+    signed, magnitude = gc.float().sum(dim=0).abs(), gc.float().abs().sum(dim=0)
+    assert float((signed / magnitude).max()) < 1e-4, float((signed / magnitude).max())
+
+
+def test_config4_training_step_is_sane_and_reproducible():
+    from cgpt_b200 import _lib
+    from cgpt_b200 import model as M
+    from cgpt_b200.train import TrainStep
+    opts = M.preset("104m")
+    ids = torch.randint(0, 32000, (32 * 1024,), dtype=torch.int32, generator=torch.Generator().manual_seed(7))
+    runs = []
+    for _ in range(2):
+        ts = TrainStep(opts, 32, 1024, seed=0)
+        ts.token_ids.copy_(ids)
+        ts.targets.copy_(torch.roll(ids, -1))
+        losses = []
+        for _ in range(3):
+            ts.step()
+            losses.append(ts.read_loss())
+        assert ts.check() and _lib.device_status() == 0
+        assert abs(losses[0] - math.log(32000)) < 0.5 and losses[2] < losses[0]      # same batch three times: it learns
+        g = ts.storage.flat_gradients
+        assert bool(torch.isfinite(g).all())
+        runs.append((losses, g.clone(), ts.storage.layers[0]["q_projection"].clone()))
+        del ts
+        torch.cuda.empty_cache()
+    assert runs[0][0] == runs[1][0] and torch.equal(runs[0][1], runs[1][1]) and torch.equal(runs[0][2], runs[1][2])
