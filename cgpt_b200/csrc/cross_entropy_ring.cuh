@@ -95,6 +95,7 @@ cross_entropy_ring_kernel(float* __restrict__ row_loss, T* grad, const T* logits
     std::uint32_t parity = 0;
     for (long long i = 0; i < my_rows; ++i) {
         const long long row = first + i * gridDim.x;
+        const std::uint32_t target = targets[row];   // issued before the wait: its latency hides behind the two row passes
         const int failed = __syncthreads_or(sm100::mbar_wait(&full[stage], parity) ? 0 : 1);
         if (failed) {
             if (threadIdx.x == 0) atomicExch(status, 4u);
@@ -130,7 +131,6 @@ cross_entropy_ring_kernel(float* __restrict__ row_loss, T* grad, const T* logits
         }
         const float denominator = ring_block_sum(local_sum, red);
         const float inv_denominator = __frcp_rn(denominator);
-        const std::uint32_t target = targets[row];
         const bool valid = target < static_cast<std::uint32_t>(vocab);
         if (threadIdx.x == 0)
             row_loss[row] = valid ? (__logf(denominator) + maximum - to_f32<T>(staged[target])) * inv_rows : 0.f;
