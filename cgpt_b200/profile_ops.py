@@ -1,6 +1,7 @@
 """`python -m cgpt_b200.profile_ops <op> [--iters N]`: launches one operator a few times on inputs larger
 than L2 but a few hundred MB at most, so that `ncu -k regex:<kernel>` captures of it end by themselves.
-Ops: gemm_fwd, gemm_dx, gemm_dw, attention_fwd, attention_bwd, rmsnorm_bwd, swiglu_bwd, adamw, cross_entropy.
+Ops: gemm_fwd, gemm_dx, gemm_dw, attention_fwd, attention_bwd, rmsnorm_bwd, swiglu_bwd, adamw, cross_entropy, qknorm_fwd,
+qknorm_bwd.
 Prints the CUDA-event time per launch (taken without a profiler attached it is the number to quote)."""
 from __future__ import annotations
 
@@ -80,6 +81,27 @@ def main() -> None:
         ms = _run(lambda: optim.adamw_step_many_async(ent, o, ws), a.iters)
         n = sum(sizes)
         print(f"adamw {n / 1e6:.1f}M params: {ms * 1e3:.1f} us, {30.0 * n / ms / 1e6:.0f} GB/s algorithmic (2+28 B/param)")
+    elif a.op in ("qknorm_fwd", "qknorm_bwd"):
+        from . import _lib, model
+        B, S, Hq, Hkv, D = 32, 1024, 8, 2, 128
+        q, k, gq, gk = h(B, S, Hq, D), h(B, S, Hkv, D), h(B, S, Hq, D), h(B, S, Hkv, D)
+        oq, ok = torch.empty_like(q), torch.empty_like(k)
+        wq, wk = torch.ones(D, device="cuda").half(), torch.ones(D, device="cuda").half()
+        dwq, dwk = torch.empty_like(wq), torch.empty_like(wk)
+        cos, sin = model.rotary_cache(S, D)
+        p = lambda t: t.data_ptr()
+        st = torch.cuda.current_stream().cuda_stream
+        if a.op == "qknorm_fwd":
+            fn = lambda: _lib.check(_lib.lib.cgpt_qknorm_rope_forward(p(oq), p(ok), p(q), p(k), p(wq), p(wk), p(cos), p(sin), B, S, Hq,
+                                                                      Hkv, D, D, 0, S, 1e-5, 0, st), "qknorm_rope_forward")
+            nbytes = 2 * (q.numel() + k.numel()) * 2
+        else:
+            fn = lambda: _lib.check(_lib.lib.cgpt_qknorm_rope_backward(p(oq), p(ok), p(dwq), p(dwk), p(gq), p(gk), p(q), p(k), p(wq),
+                                                                       p(wk), p(cos), p(sin), B, S, Hq, Hkv, D, D, 0, S, 1e-5, 0, st),
+                                    "qknorm_rope_backward")
+            nbytes = 3 * (q.numel() + k.numel()) * 2
+        ms = _run(fn, a.iters)
+        print(f"{a.op} B{B} S{S} {Hq}/{Hkv} D{D}: {ms * 1e3:.1f} us, {nbytes / ms / 1e6:.0f} GB/s algorithmic")
     else:
         raise SystemExit(f"unknown op {a.op}")
 
