@@ -273,6 +273,12 @@ def run_ours(args) -> None:
         except Exception as exc:  # the bench line must still be printed
             line["roofline"] = {"bound": "tensor", "achieved": None, "peak": None, "unit": "TFLOP/s", "frac": None,
                                 "traffic": None, "error": repr(exc)}
+        try:   # the metric's second half: standalone attention backward, configuration 2 and the 104m layer shape
+            ab = [profiling.time_attention_backward(32, 1024, 12, 4, 64), profiling.time_attention_backward(32, 1024, 8, 2, 128)]
+            burst = measured_peaks().get("bf16_tflops")
+            line["attention_backward"] = [dict(a, frac_of_measured_burst_peak=(a["tflops"] / burst if burst else None)) for a in ab]
+        except Exception as exc:
+            line["attention_backward"] = {"error": repr(exc)}
         try:
             line["cpu_baseline"] = {k: v for k, v in cpu_baseline(None).items() if k != "seconds_per_pass"} if world == 1 else None
         except Exception as exc:

@@ -40,12 +40,14 @@ class TransformerModelOptions:
 
 
 def preset(name: str, vocabulary_size: int = 32000) -> TransformerModelOptions:
-    """Model presets of the reference trainer (train/train.cpp:140-149) plus the tiny CPU-runnable model."""
+    """Model presets of the reference trainer (train/train.cpp:140-149) plus the tiny CPU-runnable model and a 1.3B one."""
     if name == "104m":
         b = TransformerBlockOptions(1024, 2048, 8, 2, 128, 128)
         return TransformerModelOptions(vocabulary_size, 8, b)
     if name == "small":
         return TransformerModelOptions(vocabulary_size, 4, TransformerBlockOptions(512, 1024, 4, 1, 128, 128))
+    if name == "1.3b":   # the scaled-up configuration: 24 layers, d 2048, 16/4 heads of 128, SwiGLU 5632
+        return TransformerModelOptions(vocabulary_size, 24, TransformerBlockOptions(2048, 5632, 16, 4, 128, 128))
     if name == "tiny":
         return TransformerModelOptions(vocabulary_size, 2, TransformerBlockOptions(256, 688, 4, 2, 64, 64))
     raise ValueError(f"unknown preset {name}")

@@ -29,6 +29,8 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("op")
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--attention-shape", choices=["104m", "d64"], default="104m",
+                    help="attention ops: 8/2 heads of 128 (the 104m layer) or 12/4 heads of 64")
     a = ap.parse_args()
     h = lambda *s: torch.randn(*s, device="cuda").half()
     T, d, I = 32768, 1024, 2048
@@ -41,7 +43,7 @@ def main() -> None:
         ms = _run(fn, a.iters)
         print(f"{a.op} {T}x{I}x{d}: {ms * 1e3:.1f} us, {2.0 * T * d * I / ms / 1e9:.1f} TFLOP/s")
     elif a.op in ("attention_fwd", "attention_bwd"):
-        B, S, Hq, Hkv, D = 32, 1024, 8, 2, 128
+        B, S, Hq, Hkv, D = (32, 1024, 8, 2, 128) if a.attention_shape == "104m" else (32, 1024, 12, 4, 64)
         q, k, v, do = h(B, S, Hq, D), h(B, S, Hkv, D), h(B, S, Hkv, D), h(B, S, Hq, D)
         o, lse = torch.empty_like(q), torch.empty(B, S, Hq, device="cuda")
         opts = ops.FlashAttentionOptions(Hq, Hkv, D)
@@ -83,7 +85,7 @@ def main() -> None:
         print(f"adamw {n / 1e6:.1f}M params: {ms * 1e3:.1f} us, {30.0 * n / ms / 1e6:.0f} GB/s algorithmic (2+28 B/param)")
     elif a.op in ("qknorm_fwd", "qknorm_bwd"):
         from . import _lib, model
-        B, S, Hq, Hkv, D = 32, 1024, 8, 2, 128
+        B, S, Hq, Hkv, D = (32, 1024, 8, 2, 128) if a.attention_shape == "104m" else (32, 1024, 12, 4, 64)
         q, k, gq, gk = h(B, S, Hq, D), h(B, S, Hkv, D), h(B, S, Hq, D), h(B, S, Hkv, D)
         oq, ok = torch.empty_like(q), torch.empty_like(k)
         wq, wk = torch.ones(D, device="cuda").half(), torch.ones(D, device="cuda").half()

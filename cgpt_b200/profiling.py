@@ -52,6 +52,36 @@ def time_gemms(train_step, steps: int = 2) -> dict:
             "launches": int(n.value) // steps, "gemm_flops": fl.value / steps, "model_flops": model}
 
 
+def time_attention_backward(batch: int, seq: int, q_heads: int, kv_heads: int, head_dim: int, iters: int = 10) -> dict:
+    """Standalone causal GQA attention backward (flash_gqa_attention_backward_with_lse) on seeded N(0,1) fp16 inputs, O and
+    the logsumexp taken from the forward on the same inputs. Time: CUDA events around `iters` back-to-back calls after 3
+    warm-up calls; a call's inputs and outputs exceed L2. FLOPs: 5 products of 2*S*S*D per (batch, query head), causal
+    half; the recomputation the kernels do beyond those 5 is not credited."""
+    from . import ops
+    g = torch.Generator(device="cuda").manual_seed(2)
+    n = lambda *s: torch.randn(*s, generator=g, device="cuda").half()
+    q, k, v = n(batch, seq, q_heads, head_dim), n(batch, seq, kv_heads, head_dim), n(batch, seq, kv_heads, head_dim)
+    do = n(batch, seq, q_heads, head_dim)
+    o, lse = torch.empty_like(q), torch.empty(batch, seq, q_heads, device="cuda")
+    opts = ops.FlashAttentionOptions(q_heads, kv_heads, head_dim)
+    ops.flash_gqa_attention_forward_with_lse(o, lse, q, k, v, None, opts)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    run = lambda: ops.flash_gqa_attention_backward_with_lse(dq, dk, dv, do, o, lse, q, k, v, None, opts)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    flops = 5.0 * 2.0 * seq * seq * head_dim * batch * q_heads / 2.0
+    return {"shape": f"B{batch} S{seq} Hq{q_heads}/Hkv{kv_heads} D{head_dim} fp16 causal", "us": ms * 1e3,
+            "tflops": flops / ms / 1e9, "flops": flops}
+
+
 def main() -> None:
     """`python -m cgpt_b200.profiling [--steps K] [--warmup W] [--preset 104m] [--batch 32] [--seq 1024]`:
     runs eager (no CUDA graph) training steps so that a profiler sees every kernel launch of a step; prints the

@@ -42,7 +42,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--min-learning-rate", type=float, default=3.0e-5)
     p.add_argument("--warmup-steps", type=int, default=0, help="0 = 2%% of the run")
     p.add_argument("--loss-scale", type=float, default=1024.0)
-    p.add_argument("--model", default="small", help="preset: 104m, small, tiny")
+    p.add_argument("--model", default="small", help="preset: 104m, small, tiny, 1.3b")
     p.add_argument("--validation-fraction", type=float, default=0.1)
     p.add_argument("--save-avg-loss", action="store_true")
     p.add_argument("--checkpoint-interval", type=int, default=0, help="also write a checkpoint every N steps (0 = only at the end)")
