@@ -8,6 +8,7 @@ Configuration 2: attention backward, B 32, 12 query / 4 kv heads, S 1024, D 64.
 Configuration 3: 32768 tokens at d_model 768: RMSNorm, RoPE (D 64), SwiGLU (hidden 2048) backward, cut cross-entropy
 against a 32000 x 768 head.
 Configuration 4: the 104m training step, batch 32 x 1024.
+Configuration 5: the 1.3B training step (24 layers, d_model 2048, 16/4 heads of 128, SwiGLU 5632), batch 8 x 4096.
 """
 import math
 
@@ -158,3 +159,33 @@ def test_config4_training_step_is_sane_and_reproducible():
         del ts
         torch.cuda.empty_cache()
     assert runs[0][0] == runs[1][0] and torch.equal(runs[0][1], runs[1][1]) and torch.equal(runs[0][2], runs[1][2])
+
+
+def test_config5_training_step_1_3b():
+    """All 24 layers at batch 8 x 4096 on one GPU: the loss starts near ln(vocab), falls when the same batch is seen
+    again, gradients are finite, the optimizer does not skip, no kernel reports a timeout, and the whole job (weights,
+    fp32 optimizer state, saved activations of 24 layers, scratch) stays well inside one GPU's memory."""
+    from cgpt_b200 import _lib
+    from cgpt_b200 import model as M
+    from cgpt_b200.train import TrainStep
+    free, _ = torch.cuda.mem_get_info()
+    if free < 90e9:
+        pytest.skip("needs about 70 GB of free device memory")
+    torch.cuda.empty_cache()
+    torch.cuda.reset_peak_memory_stats()
+    opts = M.preset("1.3b")
+    ts = TrainStep(opts, 8, 4096, seed=0)
+    assert ts.storage.num_parameters() == 1147772928
+    ids = torch.randint(0, 32000, (8 * 4096,), dtype=torch.int32, generator=torch.Generator().manual_seed(9))
+    ts.token_ids.copy_(ids)
+    ts.targets.copy_(torch.roll(ids, -1))
+    losses = []
+    for _ in range(3):
+        ts.step()
+        losses.append(ts.read_loss())
+    assert ts.check() and _lib.device_status() == 0
+    assert abs(losses[0] - math.log(32000)) < 1.0 and losses[2] < losses[0], losses
+    assert bool(torch.isfinite(ts.storage.flat_gradients).all())
+    assert torch.cuda.max_memory_allocated() < 100e9
+    del ts
+    torch.cuda.empty_cache()
