@@ -2,6 +2,37 @@
 // Included by attention_bwd_tc.cu only.
 #pragma once
 
+// One thread's 32 columns of a tile: P = 2^(S*scale2 - lse2) (0 where masked), W = P * (dP*scale - delta*scale), both packed
+// to the storage dtype. Straight-line per variant: the masked form (tiles on the diagonal or past the end) pays a compare
+// and a select per element, the common form nothing. dKV reads the streaming rows' statistics (lse2 and delta*scale, 32
+// floats each at st and st + kCols) as 16-byte shared-memory loads; dQ has them in registers.
+template <typename T, int MODE, bool MASK>
+__device__ __forceinline__ void bwd_tile_math(const std::uint32_t* t1, const std::uint32_t* t2, std::uint32_t* pu, std::uint32_t* pw,
+                                              const float* st, float my_lse2, float my_delta_s, float scale2, float scale, int thr) {
+#pragma unroll
+    for (int j4 = 0; j4 < 32; j4 += 4) {
+        float lse2[4] = {my_lse2, my_lse2, my_lse2, my_lse2}, dls[4] = {my_delta_s, my_delta_s, my_delta_s, my_delta_s};
+        if (MODE == MODE_DKV) {
+            const float4 a = *reinterpret_cast<const float4*>(st + j4), b = *reinterpret_cast<const float4*>(st + kCols + j4);
+            lse2[0] = a.x; lse2[1] = a.y; lse2[2] = a.z; lse2[3] = a.w;
+            dls[0] = b.x; dls[1] = b.y; dls[2] = b.z; dls[3] = b.w;
+        }
+        float p[4], ds[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int j = j4 + e;
+            float pe = fast_exp2(fmaf(__uint_as_float(t1[j]), scale2, -lse2[e]));
+            if (MASK) pe = (MODE == MODE_DQ ? j <= thr : j >= thr) ? pe : 0.f;
+            p[e] = pe;
+            ds[e] = pe * fmaf(__uint_as_float(t2[j]), scale, -dls[e]);
+        }
+        pu[j4 >> 1] = pack2<T>(p[0], p[1]);
+        pu[(j4 >> 1) + 1] = pack2<T>(p[2], p[3]);
+        pw[j4 >> 1] = pack2<T>(ds[0], ds[1]);
+        pw[(j4 >> 1) + 1] = pack2<T>(ds[2], ds[3]);
+    }
+}
+
 template <typename T, int D, int MODE>
 __device__ __forceinline__ bool bwd_compute(unsigned char* smem, const BwdBars& bars, const BwdGeom& g, const AttnDims& dm,
                                             std::uint32_t tmem, const float* __restrict__ lse2_t,
@@ -27,8 +58,10 @@ __device__ __forceinline__ bool bwd_compute(unsigned char* smem, const BwdBars& 
         limit = dm.causal ? dm.offset + x_idx : dm.sk - 1;
         if (limit > dm.sk - 1) limit = dm.sk - 1;
     }
+    const float my_delta_s = my_delta * dm.scale;
     bool failed = false;
 
+    constexpr int kYStages = L::kStages;
     int ys = 0;                 // ring stage of the streaming tile = it % kYStages
     std::uint32_t ypar = 0;     // its phase = (it / kYStages) & 1
     for (int it = 0; it < g.n_it; ++it) {
@@ -36,17 +69,15 @@ __device__ __forceinline__ bool bwd_compute(unsigned char* smem, const BwdBars& 
         const std::uint32_t par = (it >> 1) & 1;
         int head, y0;
         bwd_stream_coords<MODE>(g, it, &head, &y0);
-        // U/W buffer s was last read by the accumulating MMAs of tile it-2
-        if (!mbar_wait(&bars.uw_free[s], par ^ 1u)) failed = true;
-        if (!failed && !mbar_wait(&bars.t_full[s], par)) failed = true;
+        if (!mbar_wait(&bars.t_full[s], par)) failed = true;
         if (MODE == MODE_DKV && !failed && !mbar_wait(&bars.stat_full[ys], ypar)) failed = true;
         failed = __any_sync(0xffffffffu, failed);
         if (failed) break;
         if (threadIdx.x == 0) bwd_trace(bars, it, 3);
         tc_fence_after_sync();
         const float* st = reinterpret_cast<const float*>(smem + L::kStats) + ys * 2 * kCols;
-        unsigned char* u_row = smem + L::kU + s * kRows * 128 + row * 128;
-        unsigned char* w_row = smem + L::kW + s * kRows * 128 + row * 128;
+        unsigned char* u_row = smem + L::kU + row * 128;
+        unsigned char* w_row = smem + L::kW + row * 128;
         // does any element of this tile need the visibility test?
         bool need_mask;
         if (MODE == MODE_DQ) need_mask = (y0 + kCols > dm.sk) || (dm.causal && y0 + kCols - 1 > dm.offset + g.x0);
@@ -56,28 +87,14 @@ __device__ __forceinline__ bool bwd_compute(unsigned char* smem, const BwdBars& 
             std::uint32_t t1[32], t2[32];
             tmem_ld_32x32_x2(tmem + s * kCols + lane_base + c0, t1, tmem + 128 + s * kCols + lane_base + c0, t2);
             std::uint32_t pu[16], pw[16];
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-                float p[2], ds[2];
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int col = y0 + c0 + j + e;
-                    float lse2, delta;
-                    bool visible = true;
-                    if (MODE == MODE_DQ) {
-                        lse2 = my_lse2; delta = my_delta;
-                        if (need_mask) visible = col <= limit;
-                    } else {
-                        lse2 = st[c0 + j + e]; delta = st[kCols + c0 + j + e];
-                        if (need_mask) visible = x_idx <= dm.offset + col;
-                    }
-                    const float pe = fast_exp2(fmaf(__uint_as_float(t1[j + e]), scale2, -lse2));   // 2^(s*scale2 - lse2)
-                    p[e] = visible ? pe : 0.f;
-                    ds[e] = p[e] * (__uint_as_float(t2[j + e]) - delta) * dm.scale;
-                }
-                pu[j >> 1] = pack2<T>(p[0], p[1]);
-                pw[j >> 1] = pack2<T>(ds[0], ds[1]);
-            }
+            // column j of this thread's 32 is visible iff j <= thr (dQ: key <= limit) or j >= thr (dKV: query >= key - offset)
+            const int thr = MODE == MODE_DQ ? limit - y0 - c0 : x_idx - dm.offset - y0 - c0;
+            if (need_mask) bwd_tile_math<T, MODE, true>(t1, t2, pu, pw, st + c0, my_lse2, my_delta_s, scale2, dm.scale, thr);
+            else bwd_tile_math<T, MODE, false>(t1, t2, pu, pw, st + c0, my_lse2, my_delta_s, scale2, dm.scale, thr);
+            // U and W are single buffers, last read by the accumulating MMAs of tile it-1 (completion it-1 of uw_free;
+            // for it = 0 the wait on the barrier's initial phase returns at once)
+            failed = __any_sync(0xffffffffu, !mbar_wait(bars.uw_free, (static_cast<std::uint32_t>(it) & 1u) ^ 1u));
+            if (failed) break;
             const int c16 = c0 >> 3;
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) {

@@ -11,17 +11,24 @@ __device__ __forceinline__ void bwd_cta(const CUtensorMap& map_x1, const CUtenso
     using L = BwdSmem<D>;
     extern __shared__ unsigned char bwd_smem_raw[];
     const std::uint32_t raw = smem_u32(bwd_smem_raw);
-    unsigned char* smem = bwd_smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+    const std::uint32_t pad = (1024u - (raw & 1023u)) & 1023u;
+    if (pad > static_cast<std::uint32_t>(L::kAlignSlack)) {   // uniform over the CTA; nothing is allocated or armed yet
+        if (threadIdx.x == 0) atomicExch(status, 2u);
+        return;
+    }
+    unsigned char* smem = bwd_smem_raw + pad;
     std::uint64_t* bar = reinterpret_cast<std::uint64_t*>(smem + L::kBars);
     BwdBars bars;
     bars.x_full = bar + 0;
+    constexpr int kYStages = L::kStages;
     bars.y_full = bar + 1;                      // [kYStages]
     bars.stat_full = bar + 1 + kYStages;        // [kYStages]
     bars.y_free = bar + 1 + 2 * kYStages;       // [kYStages]
-    bars.uw_free = bar + 1 + 3 * kYStages;      // [2]
-    bars.t_full = bars.uw_free + 2;             // [2]
-    bars.w_full = bars.uw_free + 4;             // [2]
-    bars.acc_done = bars.uw_free + 6;
+    bars.uw_free = bar + 1 + 3 * kYStages;      // [1]
+    bars.t_full = bars.uw_free + 1;             // [2]
+    bars.w_full = bars.uw_free + 3;             // [2]
+    bars.acc_done = bars.uw_free + 5;
+    static_assert((1 + 3 * kYStages + 6) * 8 + 4 <= 256, "barrier area");
     bars.trace = (trace != nullptr && item == items / 4) ? trace : nullptr;
     std::uint32_t* tmem_slot = reinterpret_cast<std::uint32_t*>(bars.acc_done + 1);
 
@@ -66,8 +73,8 @@ __device__ __forceinline__ void bwd_cta(const CUtensorMap& map_x1, const CUtenso
             mbar_init(&bars.stat_full[s], 32);
             mbar_init(&bars.y_free[s], 1);
         }
+        mbar_init(bars.uw_free, 1);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&bars.uw_free[s], 1);
             mbar_init(&bars.t_full[s], 1);
             mbar_init(&bars.w_full[s], 2 * kRows);
         }

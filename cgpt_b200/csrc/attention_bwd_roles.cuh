@@ -49,6 +49,22 @@ __device__ __forceinline__ bool bwd_producer(unsigned char* smem, const BwdBars&
             tma_load_4d(smem + L::kX2 + c * kRows * 128, map_x2, bars.x_full, c * 64, xh, g.x0, g.b);
         }
     }
+    constexpr int kYStages = L::kStages;
+    // MODE_DKV: the statistics of tile it + 1 (lse2 and delta * scale of its 64 queries, two per lane) are fetched into
+    // registers while this warp waits for tile it's ring stage, so the loads' latency never stalls the TMA issue
+    float next_lse2[2] = {1.0e30f, 1.0e30f}, next_delta[2] = {0.f, 0.f};
+    auto fetch_stats = [&](int it) {
+        int head, row0;
+        bwd_stream_coords<MODE>(g, it, &head, &row0);
+        const long long base = (static_cast<long long>(g.b) * dm.hq + head) * dm.sq;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int q = row0 + lane + 32 * u;
+            next_lse2[u] = q < dm.sq ? lse2_t[base + q] : 1.0e30f;          // rows past the end: P = 0
+            next_delta[u] = q < dm.sq ? delta_t[base + q] * dm.scale : 0.f;  // the compute warps use delta * scale
+        }
+    };
+    if (MODE == MODE_DKV) fetch_stats(0);
     int s = 0;                  // ring stage = it % kYStages
     std::uint32_t par = 0;      // its phase = (it / kYStages) & 1
     for (int it = 0; it < g.n_it; ++it) {
@@ -67,16 +83,15 @@ __device__ __forceinline__ bool bwd_producer(unsigned char* smem, const BwdBars&
             }
         }
         if (MODE == MODE_DKV) {
-            // per-query statistics of the streaming tile: lse2 (+1e30 for rows past the end -> P = 0) and delta
+            // per-query statistics of the streaming tile, fetched one iteration ago
             float* st = reinterpret_cast<float*>(smem + L::kStats) + s * 2 * kCols;
-            const long long base = (static_cast<long long>(g.b) * dm.hq + head) * dm.sq;
 #pragma unroll
-            for (int j = lane; j < kCols; j += 32) {
-                const int q = row0 + j;
-                st[j] = q < dm.sq ? lse2_t[base + q] : 1.0e30f;
-                st[kCols + j] = q < dm.sq ? delta_t[base + q] : 0.f;
+            for (int u = 0; u < 2; ++u) {
+                st[lane + 32 * u] = next_lse2[u];
+                st[kCols + lane + 32 * u] = next_delta[u];
             }
             mbar_arrive(&bars.stat_full[s]);
+            if (it + 1 < g.n_it) fetch_stats(it + 1);
         }
         if (++s == kYStages) { s = 0; par ^= 1u; }
     }
@@ -95,7 +110,6 @@ __device__ __forceinline__ bool bwd_mma_issuer(unsigned char* smem, const BwdBar
     constexpr std::uint32_t idesc_t = idesc_f16(fmt, 0, 0, kRows, kCols);   // T = X Y^T: both K-major
     constexpr std::uint32_t idesc_acc = idesc_f16(fmt, 0, 1, kRows, D);     // acc += U/W (K-major) * Y (N-major)
     constexpr std::uint32_t kYStage16 = (2 * L::kYBytes) >> 4;              // ring stage stride in descriptor units
-    constexpr std::uint32_t kUW16 = (kRows * 128) >> 4;
     const std::uint32_t tmem_acc1 = tmem + 256, tmem_acc2 = tmem + 256 + D;
     const std::uint64_t dx1 = smem_desc_sw128(smem_u32(smem + L::kX1), 16, 1024);
     const std::uint64_t dx2 = smem_desc_sw128(smem_u32(smem + L::kX2), 16, 1024);
@@ -137,14 +151,14 @@ __device__ __forceinline__ bool bwd_mma_issuer(unsigned char* smem, const BwdBar
         const int s = it & 1;
         int ys_next = ys + 1;
         std::uint32_t ypar_next = ypar;
-        if (ys_next == kYStages) { ys_next = 0; ypar_next ^= 1u; }
+        if (ys_next == L::kStages) { ys_next = 0; ypar_next ^= 1u; }
         if (it + 1 < g.n_it && !issue_t(it + 1, ys_next, ypar_next)) return false;
         if (!mbar_wait(&bars.w_full[s], (it >> 1) & 1)) return false;
         bwd_trace(bars, it, 2);
         tc_fence_after_sync();
         const std::uint32_t acc = it > 0 ? 1u : 0u;
         const std::uint64_t y1 = dy1n + ys * kYStage16, y2 = dy2n + ys * kYStage16;
-        const std::uint64_t du = du0 + s * kUW16, dw = dw0 + s * kUW16;
+        const std::uint64_t du = du0, dw = dw0;
 #pragma unroll
         for (int k = 0; k < kCols / 16; ++k) {
             // A: [128 rows][64] K-major, one swizzle atom wide (32 B per K step); B: streaming tile as N-major:
@@ -160,7 +174,7 @@ __device__ __forceinline__ bool bwd_mma_issuer(unsigned char* smem, const BwdBar
             }
         }
         tc_commit(&bars.y_free[ys]);     // the streaming tile's ring stage may be refilled ...
-        tc_commit(&bars.uw_free[s]);     // ... and the U/W buffer rewritten once these MMAs have read them
+        tc_commit(bars.uw_free);         // ... and the U/W buffer rewritten once these MMAs have read them
         ys = ys_next;
         ypar = ypar_next;
     }

@@ -39,24 +39,32 @@ using namespace sm100;
 
 constexpr int kRows = 128;   // stationary tile rows = TMEM lanes
 constexpr int kCols = 64;    // streaming tile rows = columns of T1/T2
-constexpr int kYStages = 3;  // depth of the streaming-tile ring: the TMA latency of tile it+1 hides behind tiles it-1 and it
 constexpr int kBwdThreads = 320;   // warps 0-7 compute (two warpgroups, each half of the tile's columns), 8 TMA, 9 MMA
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int MODE_DQ = 0, MODE_DKV = 1;
 
+// The streaming-tile ring is as deep as shared memory allows: a tile's TMA load takes about 1.2 us under load, a tile's
+// MMAs about half of that, and a stage is only released when the accumulating MMAs of its tile have completed, so three
+// stages left the MMA thread waiting on every load. U and W are single buffers: the accumulating MMAs of tile it-1 are
+// long done by the time the compute warps have worked through tile it's arithmetic and want to store.
 template <int D> struct BwdSmem {
+    static constexpr int kStages = D == 128 ? 4 : 6;
     static constexpr int kChunks = D / 64;
     static constexpr int kXBytes = kChunks * kRows * 128;     // one stationary tile
     static constexpr int kYBytes = kChunks * kCols * 128;     // one streaming tile
     static constexpr int kX1 = 0;
     static constexpr int kX2 = kX1 + kXBytes;
-    static constexpr int kY = kX2 + kXBytes;                  // [kYStages][Y1 | Y2]
-    static constexpr int kU = kY + kYStages * 2 * kYBytes;    // [2] x [128 rows][128 B]
-    static constexpr int kW = kU + 2 * kRows * 128;           // [2] x [128 rows][128 B]
-    static constexpr int kStats = kW + 2 * kRows * 128;       // [kYStages][2][64] fp32
-    static constexpr int kBars = kStats + kYStages * 2 * kCols * 4;
-    static constexpr int kBytes = kBars + 256 + 1024;
-    static_assert(kBytes <= 232448, "attention backward shared memory exceeds the 227 KB a CTA may use");
+    static constexpr int kY = kX2 + kXBytes;                  // [kStages][Y1 | Y2]
+    static constexpr int kU = kY + kStages * 2 * kYBytes;     // [128 rows][128 B]
+    static constexpr int kW = kU + kRows * 128;               // [128 rows][128 B]
+    static constexpr int kStats = kW + kRows * 128;           // [kStages][2][64] fp32
+    static constexpr int kBars = kStats + kStages * 2 * kCols * 4;
+    static constexpr int kLimit = 232448;                     // the 227 KB a CTA may use
+    // room to round the dynamic shared-memory base up to 1024 bytes (the 128B swizzle's atom); the kernel checks at run
+    // time that the base needs no more than this and reports through the status word otherwise
+    static constexpr int kAlignSlack = kLimit - (kBars + 256) < 1024 ? kLimit - (kBars + 256) : 1024;
+    static constexpr int kBytes = kBars + 256 + kAlignSlack;
+    static_assert(kAlignSlack >= 0, "attention backward shared memory exceeds the 227 KB a CTA may use");
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {

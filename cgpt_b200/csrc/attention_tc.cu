@@ -84,11 +84,12 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     std::uint64_t* q_full = bars + 0;
     std::uint64_t* k_full = bars + 1;    // [2]
     std::uint64_t* v_full = bars + 3;    // [2]
-    std::uint64_t* kv_empty = bars + 5;  // [2]
-    std::uint64_t* s_full = bars + 7;    // [2]
-    std::uint64_t* p_full = bars + 9;
-    std::uint64_t* pv_full = bars + 10;
-    std::uint32_t* tmem_slot = reinterpret_cast<std::uint32_t*>(bars + 11);
+    std::uint64_t* k_empty = bars + 5;   // [2] a K stage is free once the S product of its tile has completed ...
+    std::uint64_t* v_empty = bars + 7;   // [2] ... a V stage only after the PV product, about one tile period later
+    std::uint64_t* s_full = bars + 9;    // [2]
+    std::uint64_t* p_full = bars + 11;
+    std::uint64_t* pv_full = bars + 12;
+    std::uint32_t* tmem_slot = reinterpret_cast<std::uint32_t*>(bars + 13);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q_tiles = (dm.sq + kTile - 1) / kTile;
@@ -107,7 +108,7 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < 2; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); mbar_init(&s_full[s], 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1); mbar_init(&s_full[s], 1); }
         mbar_init(p_full, 2 * kTile);
         mbar_init(pv_full, 1);
         mbar_init_fence();
@@ -129,13 +130,22 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
             mbar_expect_tx(q_full, L::kTileBytes);
 #pragma unroll
             for (int c = 0; c < L::kChunks; ++c) tma_load_4d(smem + L::kQ + c * kTile * 128, &tmap_q, q_full, c * 64, h, q0, b);
-            for (int i = 0; i < n_kv; ++i) {
+            // Loads go out in the order their stages come free: K(i+1) (after S(i-1)) before V(i) (after PV(i-2)), so
+            // the K tile the next S product needs is in flight a whole tile period before the MMA thread asks for it.
+            auto load_k = [&](int i) -> bool {
                 const int s = i & 1;
-                if (!mbar_wait(&kv_empty[s], ((i >> 1) & 1) ^ 1u)) { failed = true; break; }
+                if (!mbar_wait(&k_empty[s], ((i >> 1) & 1) ^ 1u)) return false;
                 mbar_expect_tx(&k_full[s], L::kTileBytes);
 #pragma unroll
                 for (int c = 0; c < L::kChunks; ++c)
                     tma_load_4d(smem + L::kK + s * L::kTileBytes + c * kTile * 128, &tmap_k, &k_full[s], c * 64, kvh, i * kTile, b);
+                return true;
+            };
+            if (!load_k(0)) failed = true;
+            for (int i = 0; i < n_kv && !failed; ++i) {
+                const int s = i & 1;
+                if (i + 1 < n_kv && !load_k(i + 1)) { failed = true; break; }
+                if (!mbar_wait(&v_empty[s], ((i >> 1) & 1) ^ 1u)) { failed = true; break; }
                 mbar_expect_tx(&v_full[s], L::kTileBytes);
 #pragma unroll
                 for (int c = 0; c < L::kChunks; ++c)
@@ -163,6 +173,7 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                     mma_f16_ss(tmem_s, q_desc + off16, k_desc + off16, idesc_s, k > 0 ? 1u : 0u);
                 }
                 tc_commit(&s_full[i & 1]);
+                tc_commit(&k_empty[i & 1]);
             };
             if (!mbar_wait(q_full, 0) || !mbar_wait(&k_full[0], 0)) failed = true;
             if (!failed) {
@@ -183,7 +194,7 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                         mma_f16_ss(tmem_pv, p_desc + a_off16, v_desc + ((k * (16 * 128)) >> 4), idesc_pv, k > 0 ? 1u : 0u);
                     }
                     tc_commit(pv_full);
-                    tc_commit(&kv_empty[i & 1]);
+                    tc_commit(&v_empty[i & 1]);
                 }
             }
         }
@@ -203,6 +214,22 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         for (int d = 0; d < DH; ++d) o_reg[d] = 0.f;
         float m_run = kMaskValue, l_run = 0.f;
         unsigned char* p_smem = smem + L::kP + half * (kTile * 128);   // this half's 64-column swizzle atom
+        // The PV product of tile i is folded into the output registers one step late, after pass 1 of tile i + 1: the
+        // product then runs on the tensor core while these warps take the next tile's row maxima, instead of being
+        // waited for. O = O * alpha_i + PV_i with alpha_i the rescale factor computed for tile i.
+        float alpha_prev = 1.f;
+        auto fold_pv = [&](int i) {
+            if (!mbar_wait(pv_full, i & 1)) { failed = true; return; }
+            tc_fence_after_sync();
+#pragma unroll
+            for (int c0 = 0; c0 < DH; c0 += 32) {
+                std::uint32_t r[32];
+                tmem_ld_32x32(tmem_pv + lane_base + half * DH + c0, r);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o_reg[c0 + j] = fmaf(o_reg[c0 + j], alpha_prev, __uint_as_float(r[j]));
+            }
+            tc_fence_before_sync();
+        };
         for (int i = 0; i < n_kv; ++i) {
             if (!failed && !mbar_wait(&s_full[i & 1], (i >> 1) & 1)) failed = true;
             const int kv0 = i * kTile + half * 64;                    // first key of this thread's columns
@@ -237,6 +264,9 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
             if (*fail_flag != 0) { failed = true; break; }             // uniform over the 256 threads
             const float m_new = fmaxf(m_run, fmaxf(m_part, *other_slot));
             const float alpha = fast_exp2(m_run - m_new);
+            // tile i-1's product: folded now; its completion also says that the P buffer may be rewritten below. A wait
+            // that gave up is reported at the next exchange (the stores below then go to a buffer nobody reads in time).
+            if (i > 0) fold_pv(i - 1);
             // pass 2: p = 2^(s * scale2 - m) -> shared memory (K-major A operand of the PV product), partial row sum
             float row_sum = 0.f;
             const float neg_m = -m_new;
@@ -276,17 +306,9 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
             mbar_arrive(p_full);
             l_run = l_run * alpha + row_sum;
             m_run = m_new;
-            if (!mbar_wait(pv_full, i & 1)) { failed = true; continue; }   // reported at the next exchange
-            tc_fence_after_sync();
-#pragma unroll
-            for (int c0 = 0; c0 < DH; c0 += 32) {
-                std::uint32_t r[32];
-                tmem_ld_32x32(tmem_pv + lane_base + half * DH + c0, r);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) o_reg[c0 + j] = fmaf(o_reg[c0 + j], alpha, __uint_as_float(r[j]));
-            }
-            tc_fence_before_sync();
+            alpha_prev = alpha;
         }
+        if (!failed && n_kv > 0) fold_pv(n_kv - 1);
         // total row sum = the two halves' partial sums (same order in both threads)
         if (failed) *fail_flag = 1;
         float* l_slots = xchg + 4 * kTile;   // own region: the per-tile slots may still be read by the partner
