@@ -162,7 +162,6 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
             constexpr std::uint32_t kStage16 = L::kTileBytes >> 4;
             const std::uint64_t q_desc = smem_desc_sw128(smem_u32(smem + L::kQ), 16, 1024);
             const std::uint64_t k_desc0 = smem_desc_sw128(smem_u32(smem + L::kK), 16, 1024);
-            const std::uint64_t p_desc = smem_desc_sw128(smem_u32(smem + L::kP), 16, 1024);
             const std::uint64_t v_desc0 = smem_desc_sw128(smem_u32(smem + L::kV), kTile * 128, 1024);
             auto issue_s = [&](int i) {
                 const std::uint64_t k_desc = k_desc0 + (i & 1) * kStage16;
@@ -188,10 +187,13 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                     if (!mbar_wait(&v_full[i & 1], (i >> 1) & 1) || !mbar_wait(p_full, i & 1)) { failed = true; break; }
                     tc_fence_after_sync();
                     const std::uint64_t v_desc = v_desc0 + (i & 1) * kStage16;
+                    const std::uint32_t tmem_p = tmem + (i & 1) * 128;   // P over the tile's own score buffer
 #pragma unroll
                     for (int k = 0; k < kTile / 16; ++k) {
-                        const std::uint32_t a_off16 = ((k >> 2) * (kTile * 128) + (k & 3) * 32) >> 4;
-                        mma_f16_ss(tmem_pv, p_desc + a_off16, v_desc + ((k * (16 * 128)) >> 4), idesc_pv, k > 0 ? 1u : 0u);
+                        // keys 16k..16k+15 = 8 packed columns; the two softmax warpgroups wrote keys 0-63 at columns
+                        // [0,32) and keys 64-127 at columns [64,96)
+                        const std::uint32_t a_col = (k >> 2) * 64 + (k & 3) * 8;
+                        mma_f16_ts(tmem_pv, tmem_p + a_col, v_desc + ((k * (16 * 128)) >> 4), idesc_pv, k > 0 ? 1u : 0u);
                     }
                     tc_commit(pv_full);
                     tc_commit(&v_empty[i & 1]);
@@ -213,7 +215,6 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
 #pragma unroll
         for (int d = 0; d < DH; ++d) o_reg[d] = 0.f;
         float m_run = kMaskValue, l_run = 0.f;
-        unsigned char* p_smem = smem + L::kP + half * (kTile * 128);   // this half's 64-column swizzle atom
         // The PV product of tile i is folded into the output registers one step late, after pass 1 of tile i + 1: the
         // product then runs on the tensor core while these warps take the next tile's row maxima, instead of being
         // waited for. O = O * alpha_i + PV_i with alpha_i the rescale factor computed for tile i.
@@ -295,14 +296,12 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                         packed[j >> 1] = pack2<T>(pa, pb);
                     }
                 }
-                const int c16 = c0 >> 3;
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4)
-                    *reinterpret_cast<uint4*>(p_smem + swz(row, c16 + q4)) =
-                        make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                // P goes back into TMEM over this thread's own, already read, score columns: 16 packed words per chunk at
+                // columns [c0/2, c0/2 + 16) of the thread's 64-column range. The PV product reads its A operand from there.
+                tmem_st_32x16(tmem_s + (c0 >> 1), packed);
             }
-            tc_fence_before_sync();      // TMEM reads of S done before the MMA warp may overwrite this buffer
-            fence_proxy_async_smem();    // P visible to the tensor core's (async proxy) reads
+            tmem_st_wait();
+            tc_fence_before_sync();      // P written, S read: the MMA warp may use P and later overwrite this buffer
             mbar_arrive(p_full);
             l_run = l_run * alpha + row_sum;
             m_run = m_new;
