@@ -76,8 +76,6 @@ __device__ __forceinline__ bool bwd_compute(unsigned char* smem, const BwdBars& 
         if (threadIdx.x == 0) bwd_trace(bars, it, 3);
         tc_fence_after_sync();
         const float* st = reinterpret_cast<const float*>(smem + L::kStats) + ys * 2 * kCols;
-        unsigned char* u_row = smem + L::kU + row * 128;
-        unsigned char* w_row = smem + L::kW + row * 128;
         // does any element of this tile need the visibility test?
         bool need_mask;
         if (MODE == MODE_DQ) need_mask = (y0 + kCols > dm.sk) || (dm.causal && y0 + kCols - 1 > dm.offset + g.x0);
@@ -91,21 +89,14 @@ __device__ __forceinline__ bool bwd_compute(unsigned char* smem, const BwdBars& 
             const int thr = MODE == MODE_DQ ? limit - y0 - c0 : x_idx - dm.offset - y0 - c0;
             if (need_mask) bwd_tile_math<T, MODE, true>(t1, t2, pu, pw, st + c0, my_lse2, my_delta_s, scale2, dm.scale, thr);
             else bwd_tile_math<T, MODE, false>(t1, t2, pu, pw, st + c0, my_lse2, my_delta_s, scale2, dm.scale, thr);
-            // U and W are single buffers, last read by the accumulating MMAs of tile it-1 (completion it-1 of uw_free;
-            // for it = 0 the wait on the barrier's initial phase returns at once)
-            failed = __any_sync(0xffffffffu, !mbar_wait(bars.uw_free, (static_cast<std::uint32_t>(it) & 1u) ^ 1u));
-            if (failed) break;
-            const int c16 = c0 >> 3;
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-                const std::uint32_t off = static_cast<std::uint32_t>(((c16 + q4) ^ (row & 7)) << 4);
-                if (MODE == MODE_DKV)
-                    *reinterpret_cast<uint4*>(u_row + off) = make_uint4(pu[4 * q4], pu[4 * q4 + 1], pu[4 * q4 + 2], pu[4 * q4 + 3]);
-                *reinterpret_cast<uint4*>(w_row + off) = make_uint4(pw[4 * q4], pw[4 * q4 + 1], pw[4 * q4 + 2], pw[4 * q4 + 3]);
-            }
+            // U (P^T) and W (dS or dS^T) go back into TMEM over this thread's own, already read, columns of T1 and T2:
+            // 16 packed words at columns [c0, c0 + 16) of the tile's buffer. The accumulating products read them from
+            // there as their A operands, so neither the stores nor the operand reads touch shared memory.
+            if (MODE == MODE_DKV) tmem_st_32x16(tmem + s * kCols + lane_base + c0, pu);
+            tmem_st_32x16(tmem + 128 + s * kCols + lane_base + c0, pw);
         }
+        tmem_st_wait();
         tc_fence_before_sync();
-        fence_proxy_async_smem();
         mbar_arrive(&bars.w_full[s]);
         if (threadIdx.x == 0) bwd_trace(bars, it, 4);
         if (++ys == kYStages) { ys = 0; ypar ^= 1u; }

@@ -118,8 +118,6 @@ __device__ __forceinline__ bool bwd_mma_issuer(unsigned char* smem, const BwdBar
     const std::uint64_t dy2k = smem_desc_sw128(y_base + L::kYBytes, 16, 1024);
     const std::uint64_t dy1n = smem_desc_sw128(y_base, kCols * 128, 1024);              // as N-major B of the accumulations
     const std::uint64_t dy2n = smem_desc_sw128(y_base + L::kYBytes, kCols * 128, 1024);
-    const std::uint64_t du0 = smem_desc_sw128(smem_u32(smem + L::kU), 16, 1024);
-    const std::uint64_t dw0 = smem_desc_sw128(smem_u32(smem + L::kW), 16, 1024);
 
     // T1/T2 of tile `it` whose streaming pair sits in ring stage ys (phase ypar)
     auto issue_t = [&](int it, int ys, std::uint32_t ypar) -> bool {
@@ -158,23 +156,24 @@ __device__ __forceinline__ bool bwd_mma_issuer(unsigned char* smem, const BwdBar
         tc_fence_after_sync();
         const std::uint32_t acc = it > 0 ? 1u : 0u;
         const std::uint64_t y1 = dy1n + ys * kYStage16, y2 = dy2n + ys * kYStage16;
-        const std::uint64_t du = du0, dw = dw0;
+        const std::uint32_t u_tmem = tmem + s * kCols, w_tmem = tmem + 128 + s * kCols;   // over T1 / T2 of this tile
 #pragma unroll
         for (int k = 0; k < kCols / 16; ++k) {
-            // A: [128 rows][64] K-major, one swizzle atom wide (32 B per K step); B: streaming tile as N-major:
-            // 16 rows of 128 B per K step, 64-column chunks of D kCols*128 bytes apart.
+            // A: TMEM, lanes = stationary rows, 16 streaming rows (one K step) = 8 packed columns; the two compute
+            // warpgroups wrote streaming rows 0-31 at columns [0,16) and rows 32-63 at columns [32,48).
+            // B: streaming tile as N-major: 16 rows of 128 B per K step, 64-column chunks of D kCols*128 bytes apart.
+            const std::uint32_t a_col = (k >> 1) * 32 + (k & 1) * 8;
             if (MODE == MODE_DKV) {
-                mma_f16_ss(tmem_acc1, desc_advance(du, k * 32), desc_advance(y2, k * (16 * 128)), idesc_acc,
+                mma_f16_ts(tmem_acc1, u_tmem + a_col, desc_advance(y2, k * (16 * 128)), idesc_acc,
                            k > 0 ? 1u : acc);                                            // dV += P^T dO
-                mma_f16_ss(tmem_acc2, desc_advance(dw, k * 32), desc_advance(y1, k * (16 * 128)), idesc_acc,
+                mma_f16_ts(tmem_acc2, w_tmem + a_col, desc_advance(y1, k * (16 * 128)), idesc_acc,
                            k > 0 ? 1u : acc);                                            // dK += dS^T Q
             } else {
-                mma_f16_ss(tmem_acc1, desc_advance(dw, k * 32), desc_advance(y1, k * (16 * 128)), idesc_acc,
+                mma_f16_ts(tmem_acc1, w_tmem + a_col, desc_advance(y1, k * (16 * 128)), idesc_acc,
                            k > 0 ? 1u : acc);                                            // dQ += dS K
             }
         }
         tc_commit(&bars.y_free[ys]);     // the streaming tile's ring stage may be refilled ...
-        tc_commit(bars.uw_free);         // ... and the U/W buffer rewritten once these MMAs have read them
         ys = ys_next;
         ypar = ypar_next;
     }

@@ -17,8 +17,8 @@
 // Both kernels are one template. A "stationary" pair of [128, D] tiles (X1, X2) stays in shared memory,
 // a "streaming" pair of [64, D] tiles (Y1, Y2) runs through a 3-stage TMA ring:
 //     T1 = X1 Y1^T, T2 = X2 Y2^T            two 128x64 fp32 tiles in TMEM (double-buffered)
-//     threads (one per TMEM lane = stationary row) turn T1/T2 into 16-bit tiles U (P^T) and W (dS or dS^T)
-//     in 128B-swizzled shared memory (K-major A operands)
+//     threads (two per TMEM lane = stationary row) turn T1/T2 into 16-bit tiles U (P^T) and W (dS or dS^T),
+//     written back into TMEM over the columns of T1/T2 they were computed from (A operands read from TMEM)
 //     acc1 += U Y2, acc2 += W Y1 (dKV)   or   acc1 += W Y1 (dQ)      accumulators stay in TMEM
 // The streaming tiles serve twice from the same bytes: as K-major B operands of T1/T2 and as N-major
 // ("MN-major") B operands of the accumulating products.
@@ -45,8 +45,7 @@ constexpr int MODE_DQ = 0, MODE_DKV = 1;
 
 // The streaming-tile ring is as deep as shared memory allows: a tile's TMA load takes about 1.2 us under load, a tile's
 // MMAs about half of that, and a stage is only released when the accumulating MMAs of its tile have completed, so three
-// stages left the MMA thread waiting on every load. U and W are single buffers: the accumulating MMAs of tile it-1 are
-// long done by the time the compute warps have worked through tile it's arithmetic and want to store.
+// stages left the MMA thread waiting on every load. U and W never touch shared memory (they live in TMEM, over T1 / T2).
 template <int D> struct BwdSmem {
     static constexpr int kStages = D == 128 ? 4 : 6;
     static constexpr int kChunks = D / 64;
@@ -55,9 +54,7 @@ template <int D> struct BwdSmem {
     static constexpr int kX1 = 0;
     static constexpr int kX2 = kX1 + kXBytes;
     static constexpr int kY = kX2 + kXBytes;                  // [kStages][Y1 | Y2]
-    static constexpr int kU = kY + kStages * 2 * kYBytes;     // [128 rows][128 B]
-    static constexpr int kW = kU + kRows * 128;               // [128 rows][128 B]
-    static constexpr int kStats = kW + kRows * 128;           // [kStages][2][64] fp32
+    static constexpr int kStats = kY + kStages * 2 * kYBytes; // [kStages][2][64] fp32
     static constexpr int kBars = kStats + kStages * 2 * kCols * 4;
     static constexpr int kLimit = 232448;                     // the 227 KB a CTA may use
     // room to round the dynamic shared-memory base up to 1024 bytes (the 128B swizzle's atom); the kernel checks at run
