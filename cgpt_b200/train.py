@@ -15,6 +15,17 @@ from . import model as M
 from . import optim as O
 
 
+class PendingLoss:
+    """A loss value on its way to the host (TrainStep.read_loss_async). At most 4 may be outstanding."""
+
+    def __init__(self, host: torch.Tensor, done: torch.cuda.Event):
+        self._host, self._done = host, done
+
+    def value(self) -> float:
+        self._done.synchronize()
+        return float(self._host[0])
+
+
 class TrainStep:
     def __init__(self, options: M.TransformerModelOptions, batch: int, seq: int, *, dtype=torch.float16, seed: int = 0,
                  loss_scale: float = 1024.0, adamw: O.AdamWOptions | None = None, process_group=None,
@@ -49,6 +60,7 @@ class TrainStep:
         self._buckets = self._make_buckets(bucket_bytes)
         self._reducer = dp.BucketReducer(self._buckets, self.pg) if self.overlap_allreduce else None
         self._keep = None
+        self._loss_ring = None
 
     # ------------------------------------------------------------------------------------------ pieces
     def _make_buckets(self, bucket_bytes: int):
@@ -125,6 +137,20 @@ class TrainStep:
         """Device -> host read of the last step's loss (synchronises the step's stream)."""
         self.stream.synchronize()
         return float(self.loss.item())
+
+    def read_loss_async(self) -> "PendingLoss":
+        """Enqueues the device -> host copy of the last step's loss into pinned memory on the step's stream and returns
+        at once; `PendingLoss.value()` waits for that copy only. A training loop that logs the loss of step i after it
+        has enqueued step i + 1 never drains the stream."""
+        if self._loss_ring is None:
+            self._loss_ring = [(torch.empty(1, dtype=torch.float32).pin_memory(), torch.cuda.Event()) for _ in range(4)]
+            self._loss_reads = 0
+        host, done = self._loss_ring[self._loss_reads % len(self._loss_ring)]
+        self._loss_reads += 1
+        with torch.cuda.stream(self.stream):
+            host.copy_(self.loss, non_blocking=True)
+            done.record(self.stream)
+        return PendingLoss(host, done)
 
     def check(self) -> bool:
         with torch.cuda.stream(self.stream):

@@ -53,3 +53,33 @@ def test_loss_on_random_tokens_stays_at_entropy(tmp_path, capsys):
     text = capsys.readouterr().out
     losses = [float(l.split(" loss ")[1].split()[0]) for l in text.splitlines() if l.startswith("step ") and "/" in l.split()[1]]
     assert len(losses) == 4 and all(abs(x - math.log(4096)) < 0.35 for x in losses), text
+
+
+def test_asynchronous_loss_read_equals_synchronous_read():
+    """TrainStep.read_loss_async: the pinned copies, consumed one step late as a logging loop does, hold exactly the
+    values a synchronous read after each step returns."""
+    import torch
+    from cgpt_b200 import model as M
+    from cgpt_b200.train import TrainStep
+    opts = M.TransformerModelOptions(512, 2, M.TransformerBlockOptions(256, 512, 2, 1, 128, 128))
+    ids = torch.randint(0, 512, (6, 2 * 64), dtype=torch.int32, generator=torch.Generator().manual_seed(3)).pin_memory()
+    targets = torch.roll(ids, -1, dims=1).contiguous().pin_memory()
+
+    def run(asynchronous):
+        ts = TrainStep(opts, 2, 64, seed=5)
+        out, pending = [], None
+        for i in range(6):
+            ts.upload_batch(ids[i], targets[i])      # on the step's stream: ordered after the previous step
+            ts.step()
+            if asynchronous:
+                handle = ts.read_loss_async()
+                if pending is not None:
+                    out.append(pending.value())
+                pending = handle
+            else:
+                out.append(ts.read_loss())
+        if asynchronous:
+            out.append(pending.value())
+        return out
+
+    assert run(True) == run(False)
