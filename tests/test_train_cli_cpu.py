@@ -87,3 +87,21 @@ def test_checkpoint_round_trip(tmp_path):
     c = M.ModelStorage(M.preset("tiny", vocabulary_size=32), torch.float16, seed=1, device="cpu")
     with pytest.raises(ValueError):
         checkpoint.load_model(str(tmp_path), c)
+
+
+def test_presets_have_the_documented_sizes():
+    """Parameter counts of the presets (tied embedding, 11 tensors per block, final norm): 104m = 104,090,624 and the
+    1.3B configuration = 1,147,772,928; model FLOPs per token of the 104m step as quoted for the benchmark."""
+    import math
+    from cgpt_b200 import model as M, profiling
+
+    def count(o):
+        per_block = sum(math.prod(s) for s in M.block_param_shapes(o.block_options).values())
+        return o.vocabulary_size * o.block_options.hidden_size + o.num_layers * per_block + o.block_options.hidden_size
+
+    assert count(M.preset("104m")) == 104_090_624
+    assert count(M.preset("1.3b")) == 1_147_772_928
+    o = M.preset("104m")
+    assert profiling.model_flops_per_token(o) + profiling.attention_flops_per_token(o, 1024) == 683_147_264
+    with pytest.raises(ValueError):
+        M.preset("no-such-model")
