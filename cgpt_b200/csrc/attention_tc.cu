@@ -71,6 +71,21 @@ template <> __device__ __forceinline__ std::uint32_t pack2<__nv_bfloat16>(float 
     return *reinterpret_cast<std::uint32_t*>(&h);
 }
 
+// 2^x for x <= 0 on the FMA and integer pipes: x = n + f with n = round(x) (read from the low mantissa bits of
+// x + 1.5 * 2^23) and f in [-0.5, 0.5]; 2^f by a degree-3 polynomial (maximum relative error 7.5e-5, below the 4.9e-4 of the
+// fp16 rounding P gets anyway); n is added to the exponent field. Pass 2 of the softmax is bound by the MUFU pipe
+// (16 results per clock per SM against 128 FMAs), so a share of the exponentials is moved off it.
+constexpr int kPolyEvery = 4;   // one pair in kPolyEvery uses the polynomial
+__device__ __forceinline__ float poly_exp2(float x) {
+    x = fmaxf(x, -125.0f);
+    const float t = x + 12582912.0f;
+    const float f = x - (t - 12582912.0f);
+    float p = fmaf(f, 0.055171459913253784f, 0.2426108568906784f);
+    p = fmaf(p, f, 0.6932609677314758f);
+    p = fmaf(p, f, 0.9999281167984009f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -290,8 +305,12 @@ attention_forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; j += 2) {
-                        const float pa = fast_exp2(fmaf(__uint_as_float(r[j]), scale2, neg_m));
-                        const float pb = fast_exp2(fmaf(__uint_as_float(r[j + 1]), scale2, neg_m));
+                        // every kPolyEvery-th pair takes its exponentials from the FMA pipe instead of the MUFU pipe
+                        const float xa = fmaf(__uint_as_float(r[j]), scale2, neg_m);
+                        const float xb = fmaf(__uint_as_float(r[j + 1]), scale2, neg_m);
+                        const bool poly = ((j >> 1) % kPolyEvery) == kPolyEvery - 1;
+                        const float pa = poly ? poly_exp2(xa) : fast_exp2(xa);
+                        const float pb = poly ? poly_exp2(xb) : fast_exp2(xb);
                         row_sum += pa + pb;
                         packed[j >> 1] = pack2<T>(pa, pb);
                     }
