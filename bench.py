@@ -39,7 +39,7 @@ PUBLISHED_TOKENS_PER_S = 151400.0   # reference README.md:168 (4.62 steps/s at 3
 
 
 # DRAM bytes of one launch of the dominant kernel, from an ncu capture of its most frequent large shape in the step
-# (profiles/gemm_tcgen05_persistent_32768x2048x1024.md): dram__bytes_read.sum 71.3 MB + dram__bytes_write.sum 77.3 MB.
+# (python -m cgpt_b200.profile_ops gemm_fwd under ncu): dram__bytes_read.sum 71.3 MB + dram__bytes_write.sum 77.3 MB.
 GEMM_TRAFFIC_BYTES = 148.6e6
 GEMM_TRAFFIC_NOTE = ("ncu, one launch of the 32768x2048x1024 forward GEMM (algorithmic A+B+C = 205.5 MB; part of C is still "
                      "in L2 when the kernel ends); the step's 116 launches have other shapes, none re-reads its operands from DRAM")

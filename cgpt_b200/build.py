@@ -1,7 +1,8 @@
 """Builds ``cgpt_b200/libcgpt_b200.so`` (sm_100a only) from ``cgpt_b200/csrc`` with nvcc.
 
 Run as ``python -m cgpt_b200.build`` (add ``--force`` to rebuild everything, ``--verbose`` to see
-``-Xptxas -v`` register/shared-memory reports). Objects are cached under ``build/obj`` and rebuilt
+``-Xptxas -v`` register/shared-memory reports, ``--diagnosis`` to compile in the environment-driven diagnosis
+switches, which the normal build leaves out). Objects are cached under ``build/obj`` and rebuilt
 when the source or any header under ``csrc``/``include`` is newer. No GPU is needed to build.
 """
 from __future__ import annotations
@@ -42,8 +43,10 @@ def _headers_mtime() -> float:
     return newest
 
 
-def _compile(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:
+def _compile(nvcc: str, src: Path, obj: Path, verbose: bool, diagnosis: bool = False) -> str:
     cmd = [nvcc, *ARCH_FLAGS, *COMMON, "-I", str(ROOT / "include"), "-c", str(src), "-o", str(obj)]
+    if diagnosis:
+        cmd[1:1] = ["-DCGPT_B200_DIAGNOSIS"]
     if verbose:
         cmd[1:1] = ["-Xptxas", "-v"]
     proc = subprocess.run(cmd, capture_output=True, text=True)
@@ -52,7 +55,8 @@ def _compile(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:
     return proc.stderr if verbose else ""
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, diagnosis: bool = False) -> Path:
+    force = force or diagnosis
     nvcc = _nvcc()
     OBJ.mkdir(parents=True, exist_ok=True)
     sources = sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cpp")))
@@ -70,7 +74,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if jobs:
         workers = min(len(jobs), os.cpu_count() or 4)
         with concurrent.futures.ThreadPoolExecutor(max_workers=workers) as pool:
-            futures = {pool.submit(_compile, nvcc, s, o, verbose): s for s, o in jobs}
+            futures = {pool.submit(_compile, nvcc, s, o, verbose, diagnosis): s for s, o in jobs}
             for fut in concurrent.futures.as_completed(futures):
                 report = fut.result()
                 if report:
@@ -89,8 +93,10 @@ def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--diagnosis", action="store_true",
+                    help="define CGPT_B200_DIAGNOSIS (rebuild with --force afterwards to return to the normal library)")
     args = ap.parse_args()
-    print(build(force=args.force, verbose=args.verbose))
+    print(build(force=args.force, verbose=args.verbose, diagnosis=args.diagnosis))
 
 
 if __name__ == "__main__":

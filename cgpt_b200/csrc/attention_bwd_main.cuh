@@ -190,8 +190,8 @@ int launch_backward(void* dq, void* dk, void* dv, const void* dout, const void* 
     if (status == nullptr) return CGPT_ERR_STATE;
     const int items_q = ((dm.sq + kRows - 1) / kRows) * dm.hq * dm.batch;
     const int items_kv = ((dm.sk + kRows - 1) / kRows) * dm.hkv * dm.batch;
-    static const bool split_launches = [] { const char* e = std::getenv("CGPT_B200_ATTN_SPLIT"); return e && e[0] == '1'; }();
-    if (!split_launches && std::getenv("CGPT_B200_ATTN_TRACE") == nullptr) {
+    static const bool split_launches = [] { const char* e = diagnosis_env("CGPT_B200_ATTN_SPLIT"); return e && e[0] == '1'; }();
+    if (!split_launches && diagnosis_env("CGPT_B200_ATTN_TRACE") == nullptr) {
         auto kboth = attention_bwd_tc_both_kernel<T, D>;
         static PerDeviceOnce both_once;
         if (both_once.needed()) {
@@ -206,9 +206,10 @@ int launch_backward(void* dq, void* dk, void* dv, const void* dout, const void* 
         return CGPT_OK;
     }
     const dim3 grid_q(static_cast<unsigned>(items_q));
-    // CGPT_B200_ATTN_TRACE=<device pointer of 2*64*8 uint64> records per-iteration timestamps of one CTA per kernel (diagnosis)
+    // Diagnosis builds only: CGPT_B200_ATTN_TRACE=<device pointer of 2*64*8 uint64> records per-iteration timestamps of one
+    // CTA per kernel. The shipped build never takes a pointer from the environment.
     unsigned long long* trace = nullptr;
-    if (const char* e = std::getenv("CGPT_B200_ATTN_TRACE")) trace = reinterpret_cast<unsigned long long*>(std::strtoull(e, nullptr, 0));
+    if (const char* e = diagnosis_env("CGPT_B200_ATTN_TRACE")) trace = reinterpret_cast<unsigned long long*>(std::strtoull(e, nullptr, 0));
     kq<<<grid_q, kBwdThreads, L::kBytes, s>>>(q128, do128, k64, v64, static_cast<T*>(dq), static_cast<T*>(nullptr), lse2_t, delta_t, dm,
                                               accumulate, status, trace);
     count_launch();

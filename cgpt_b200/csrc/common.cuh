@@ -7,6 +7,7 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <cstdlib>
 
 #include "../../include/cgpt_b200.h"
 
@@ -38,6 +39,18 @@ inline bool valid_float_dtype(int dtype) {
     return dtype == CGPT_DTYPE_F16 || dtype == CGPT_DTYPE_BF16 || dtype == CGPT_DTYPE_F32;
 }
 inline std::size_t dtype_size(int dtype) { return dtype == CGPT_DTYPE_F32 ? 4 : 2; }
+
+// Diagnosis switches (kernel variants that skip stores, trace buffers, forced fall-backs) are read from the environment
+// only in a library built with -DCGPT_B200_DIAGNOSIS. The shipped build does not define it: there the switches do not
+// exist, so no environment variable can change a result or hand a kernel a pointer.
+inline const char* diagnosis_env(const char* name) {
+#ifdef CGPT_B200_DIAGNOSIS
+    return std::getenv(name);
+#else
+    (void)name;
+    return nullptr;
+#endif
+}
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<std::uintptr_t>(p) & 15u) == 0; }
 

@@ -169,7 +169,7 @@ cross_entropy_ring_kernel(float* __restrict__ row_loss, T* grad, const T* logits
 template <typename T>
 int ring_stages(long long vocab, const void* logits, const void* grad, unsigned* row_pitch) {
     static const bool enabled = [] {
-        const char* e = std::getenv("CGPT_B200_CE_RING");   // "0" keeps the plain staged kernel (diagnosis)
+        const char* e = diagnosis_env("CGPT_B200_CE_RING");   // diagnosis builds: "0" keeps the plain staged kernel
         return !(e != nullptr && e[0] == '0');
     }();
     if (!enabled || sizeof(T) != 2 || vocab % 8 != 0 || vocab > kRingMaxVocab || !aligned16(logits) || !aligned16(grad)) return 0;

@@ -254,8 +254,8 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
         attr_once.done();
     }
     int epi = splits > 1 ? kEpiPartial : (accumulate ? kEpiAccumulate : kEpiStore);
-    {   // diagnosis only: CGPT_B200_GEMM_NOSTORE=1 drains the accumulator but skips the global stores
-        static const int nostore = [] { const char* e = std::getenv("CGPT_B200_GEMM_NOSTORE"); return e ? std::atoi(e) : 0; }();
+    {   // diagnosis builds only: CGPT_B200_GEMM_NOSTORE=1 drains the accumulator but skips the global stores
+        static const int nostore = [] { const char* e = diagnosis_env("CGPT_B200_GEMM_NOSTORE"); return e ? std::atoi(e) : 0; }();
         if (nostore == 1) epi = kEpiNone;
     }
     const bool timed = g_timing.enabled && g_timing.used + 2 <= g_timing.events.size();
@@ -273,9 +273,9 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
             const std::uint32_t box_c[2] = {64, BM};
             CGPT_TRY(make_tensor_map(&tc, dtype, C, 2, dims_c, st_c, box_c));
             epi = kEpiStoreTma;
-            // diagnosis only: CGPT_B200_GEMM_NOSTORE=2 stages the tile in shared memory but never issues the TMA store
+            // diagnosis builds only: CGPT_B200_GEMM_NOSTORE=2 stages the tile in shared memory but never issues the TMA store
             // and =3 issues every TMA store to the first 16 KB of C (same store mechanics, no memory-system load)
-            static const int diag = [] { const char* e = std::getenv("CGPT_B200_GEMM_NOSTORE"); return e ? std::atoi(e) : 0; }();
+            static const int diag = [] { const char* e = diagnosis_env("CGPT_B200_GEMM_NOSTORE"); return e ? std::atoi(e) : 0; }();
             if (diag == 2) epi = kEpiStageOnly;
             if (diag == 3) epi = kEpiStoreTmaFixed;
         }
@@ -679,7 +679,12 @@ extern "C" int cgpt_linear_backward_input_fused(void* dx, const void* const* dy,
     if (!dx || !dy || !w || !out_features) return CGPT_ERR_NULL;
     if (count < 1 || count > static_cast<size_t>(kMaxKSegments)) return CGPT_ERR_SHAPE;
     long long ks[kMaxKSegments] = {0, 0, 0};
-    for (size_t i = 0; i < count; ++i) ks[i] = static_cast<long long>(out_features[i]);
+    for (size_t i = 0; i < count; ++i) {
+        if (!dy[i] || !w[i]) return CGPT_ERR_NULL;
+        if (out_features[i] == 0 || out_features[i] > 0x7fffffffull) return CGPT_ERR_SHAPE;
+        ks[i] = static_cast<long long>(out_features[i]);
+    }
+    if (rows == 0 || in_features == 0 || rows > 0x7fffffffull || in_features > 0x7fffffffull) return CGPT_ERR_SHAPE;
     // dX = sum_i dY_i * W_i: A_i = dY_i [rows, out_i] (K-major), B_i = W_i [out_i, in] read as [K, N]
     return gemm_dispatch_segments(dx, dy, w, ks, static_cast<int>(count), static_cast<long long>(rows),
                                   static_cast<long long>(in_features), 0, 1, accumulate_input, dtype, false,

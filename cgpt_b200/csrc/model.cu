@@ -132,8 +132,8 @@ int mlp_forward(const void* in, const cgpt_block_params* w, const cgpt_block_sav
     CGPT_TRY(cgpt_rmsnorm_forward(sv->norm, in, w->ffn_norm, m.rows, m.d, eps, dt, stream));
     // gate, up and the activation (two GEMMs and an activation pass in the reference, :566-579). The one-launch form
     // (cgpt_linear_swiglu_forward, same results bit for bit) measured 300 us against 292 us for the three launches at
-    // the 104m shape, so the block uses it only on request: CGPT_B200_FUSED_SWIGLU=1.
-    static const bool fused_swiglu = [] { const char* e = std::getenv("CGPT_B200_FUSED_SWIGLU"); return e && e[0] == '1'; }();
+    // the 104m shape, so the block uses it only in diagnosis builds with CGPT_B200_FUSED_SWIGLU=1.
+    static const bool fused_swiglu = [] { const char* e = diagnosis_env("CGPT_B200_FUSED_SWIGLU"); return e && e[0] == '1'; }();
     if (fused_swiglu) {
         CGPT_TRY(cgpt_linear_swiglu_forward(sv->gate, sv->up, sv->activated, sv->norm, w->gate_proj, w->up_proj, m.rows, m.d,
                                             m.inter, dt, stream));

@@ -107,10 +107,10 @@ rmsnorm_forward_kernel(T* __restrict__ y, const T* __restrict__ x, const T* __re
 
 template <typename T, int VEC, int CPT>
 __global__ void __launch_bounds__(kThreads)
-rmsnorm_backward_kernel(T* __restrict__ dx, float* __restrict__ dw_partial,
+rmsnorm_backward_kernel(T* dx, float* __restrict__ dw_partial,   // dx may alias res_a / res_b (element-wise in place)
                         const T* __restrict__ dy, const T* __restrict__ x,
-                        const T* __restrict__ w, const T* __restrict__ res_a,
-                        const T* __restrict__ res_b, long long rows, int hidden, float epsilon,
+                        const T* __restrict__ w, const T* res_a,
+                        const T* res_b, long long rows, int hidden, float epsilon,
                         int wpr) {
     __shared__ float red[kWarps * 2];
     const int tpr = wpr * 32;
@@ -233,11 +233,11 @@ struct Plan {
     int vec, cpt, wpr;
 };
 
-// 16-byte chunks a thread should hold before a row is spread over more warps (CGPT_B200_RMS_CPT = 1, 2 or 4 overrides).
+// 16-byte chunks a thread should hold before a row is spread over more warps (diagnosis builds: CGPT_B200_RMS_CPT = 1, 2 or 4 overrides).
 // More chunks per thread = more loads in flight per thread but more registers (fewer resident CTAs).
 inline int chunks_per_thread_target() {
     static const int v = [] {
-        const char* e = std::getenv("CGPT_B200_RMS_CPT");
+        const char* e = diagnosis_env("CGPT_B200_RMS_CPT");
         const int x = e ? std::atoi(e) : 1;
         return (x == 1 || x == 2 || x == 4) ? x : 1;
     }();

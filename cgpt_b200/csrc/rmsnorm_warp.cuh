@@ -97,9 +97,9 @@ rmsnorm_forward_warp_kernel(T* __restrict__ y, const T* __restrict__ x, const T*
 // dx = dy*w*inv - x*c (+ residuals), per-CTA dw partial row in dw_partial[blockIdx.x][hidden].
 template <typename T, int CPT>
 __global__ void __launch_bounds__(kThreads, 2)
-rmsnorm_backward_warp_kernel(T* __restrict__ dx, float* __restrict__ dw_partial, const T* __restrict__ dy,
-                             const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ res_a,
-                             const T* __restrict__ res_b, long long rows, int hidden, float epsilon) {
+rmsnorm_backward_warp_kernel(T* dx, float* __restrict__ dw_partial, const T* __restrict__ dy,   // dx may alias res_a / res_b
+                             const T* __restrict__ x, const T* __restrict__ w, const T* res_a,
+                             const T* res_b, long long rows, int hidden, float epsilon) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long warp_id = static_cast<long long>(blockIdx.x) * kWarps + warp;
     const long long warps_total = static_cast<long long>(gridDim.x) * kWarps;
@@ -222,10 +222,10 @@ dw_reduce_wide_kernel(T* __restrict__ dw, const float* __restrict__ partial, int
     }
 }
 
-// CGPT_B200_RMS_WARP=0 routes these shapes through the general kernels instead (diagnosis).
+// Diagnosis builds only: CGPT_B200_RMS_WARP=0 routes these shapes through the general kernels instead.
 inline bool applicable(std::size_t hidden, int vec, std::size_t elem_size) {
     static const bool enabled = [] {
-        const char* e = std::getenv("CGPT_B200_RMS_WARP");
+        const char* e = diagnosis_env("CGPT_B200_RMS_WARP");
         return !(e != nullptr && e[0] == '0');
     }();
     return enabled && elem_size == 2 && vec == 8 && hidden >= 256 && hidden <= 1024;

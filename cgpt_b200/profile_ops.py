@@ -1,7 +1,7 @@
 """`python -m cgpt_b200.profile_ops <op> [--iters N]`: launches one operator a few times on inputs larger
 than L2 but a few hundred MB at most, so that `ncu -k regex:<kernel>` captures of it end by themselves.
-Ops: gemm_fwd, gemm_dx, gemm_dw, attention_fwd, attention_bwd, rmsnorm_bwd, swiglu_bwd, adamw, cross_entropy, qknorm_fwd,
-qknorm_bwd.
+Ops: gemm_fwd, gemm_dx, gemm_dw, attention_fwd, attention_bwd, rmsnorm_bwd, swiglu_bwd, rope_bwd, embedding_bwd, adamw,
+cross_entropy, qknorm_fwd, qknorm_bwd.
 Prints the CUDA-event time per launch (taken without a profiler attached it is the number to quote)."""
 from __future__ import annotations
 
@@ -66,6 +66,21 @@ def main() -> None:
         dg, du = torch.empty_like(g), torch.empty_like(g)
         ms = _run(lambda: ops.swiglu_backward(dg, du, dy, g, u), a.iters)
         print(f"swiglu_bwd {T}x{I}: {ms * 1e3:.1f} us, {5.0 * T * I * 2 / ms / 1e6:.0f} GB/s algorithmic")
+    elif a.op == "rope_bwd":
+        from . import model
+        B, S, Hq, Hkv, D = (32, 1024, 8, 2, 128) if a.attention_shape == "104m" else (32, 1024, 12, 4, 64)
+        gq, gk = h(B, S, Hq, D), h(B, S, Hkv, D)
+        dq, dk = torch.empty_like(gq), torch.empty_like(gk)
+        cos, sin = model.rotary_cache(S, D)
+        ms = _run(lambda: ops.rope_backward(dq, dk, gq, gk, cos, sin), a.iters)
+        print(f"rope_bwd B{B} S{S} {Hq}/{Hkv} D{D}: {ms * 1e3:.1f} us, {2.0 * (gq.numel() + gk.numel()) * 2 / ms / 1e6:.0f} GB/s algorithmic")
+    elif a.op == "embedding_bwd":
+        V = 32000
+        dy, ids = h(T, d), torch.randint(0, V, (T,), device="cuda", dtype=torch.int32)
+        gw = torch.empty(V, d, device="cuda", dtype=torch.float16)
+        ms = _run(lambda: ops.embedding_backward(gw, dy, ids, T), a.iters)
+        print(f"embedding_bwd {T} tokens x {d} into {V} rows: {ms * 1e3:.1f} us (sort + owner-row kernel), "
+              f"{(T * d * 2 + V * d * 2 + 4 * T) / ms / 1e6:.0f} GB/s algorithmic")
     elif a.op == "cross_entropy":
         rows, V = 8192, 32000
         z, t = h(rows, V), torch.randint(0, V, (rows,), device="cuda", dtype=torch.int32)

@@ -85,7 +85,7 @@ def time_attention_backward(batch: int, seq: int, q_heads: int, kv_heads: int, h
 def main() -> None:
     """`python -m cgpt_b200.profiling [--steps K] [--warmup W] [--preset 104m] [--batch 32] [--seq 1024]`:
     runs eager (no CUDA graph) training steps so that a profiler sees every kernel launch of a step; prints the
-    mean step time. Used for the launch lists and ncu captures summarised under profiles/."""
+    mean step time. Used for launch lists and profiler captures of the step."""
     import argparse
 
     from . import model as M

@@ -61,6 +61,14 @@ class TrainStep:
         self._reducer = dp.BucketReducer(self._buckets, self.pg) if self.overlap_allreduce else None
         self._keep = None
         self._loss_ring = None
+        self.adopt_default_stream_work()
+
+    def adopt_default_stream_work(self) -> None:
+        """Makes the step's stream wait for everything enqueued so far on torch's current stream. Weights, optimizer
+        state and buffers are created (and checkpoints loaded, token ids written by tests) on the current stream, while
+        the step runs on its own non-blocking stream: without this edge the first step could formally start before those
+        kernels and copies have landed. Call it again after writing any of the step's tensors from another stream."""
+        self.stream.wait_stream(torch.cuda.current_stream())
 
     # ------------------------------------------------------------------------------------------ pieces
     def _make_buckets(self, bucket_bytes: int):
@@ -153,5 +161,13 @@ class TrainStep:
         return PendingLoss(host, done)
 
     def check(self) -> bool:
+        """Synchronises the step's stream, refreshes the host-side step counters of the optimizer states and returns
+        False if a step since the last check was skipped for non-finite gradients. Raises if a tensor-core kernel's
+        bounded wait ran out (device status word): its outputs are then incomplete and training must not go on."""
+        from ._lib import device_status
         with torch.cuda.stream(self.stream):
-            return O.adamw_check(self.adamw_workspace)
+            ok = O.adamw_check(self.adamw_workspace)
+        status = device_status()
+        if status != 0:
+            raise RuntimeError(f"cgpt_b200: a kernel gave up a bounded wait (device status {status}); results are incomplete")
+        return ok

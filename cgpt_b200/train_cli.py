@@ -153,6 +153,7 @@ def main(argv=None) -> int:
         else:   # the reference's resume: fresh optimizer state from the loaded weights
             for (p, _), st in zip(ts.storage.parameters_and_gradients(), ts.states):
                 st.master_parameter.copy_(p.float())
+        ts.adopt_default_stream_work()      # the loads above ran on torch's current stream
         log(f"loaded {args.load_dir}, resuming at step {first_step}")
 
     # The step is asynchronous: the host runs several steps ahead of the GPU, so a pinned staging buffer may only be
@@ -185,6 +186,11 @@ def main(argv=None) -> int:
         return float(mean.item())
 
     def save(step: int) -> None:
+        # The step just enqueued (graph replay, all-reduce, AdamW) runs on ts.stream while the copies below run on torch's
+        # current stream: drain the step first, on every rank, and let check() refresh the optimizer's host-side step
+        # counters, which the checkpoint stores (they are otherwise only refreshed at the logging points).
+        ts.stream.synchronize()
+        ts.check()
         if rank == 0:
             checkpoint.save_model(args.output_dir, ts.storage)
             checkpoint.save_optimizer(args.output_dir, ts.storage, ts.states, {"step": step})
@@ -197,9 +203,14 @@ def main(argv=None) -> int:
 
     step, t0, tokens_seen, window_loss, window_n = first_step, time.time(), 0, 0.0, 0
     epoch_rng = np.random.default_rng(42)
+    # A resumed run continues where the saved one stopped: the permutations of the completed epochs are drawn and
+    # dropped, and the batches of the current epoch that were already consumed are skipped.
+    for _ in range(first_step // batches_per_epoch):
+        epoch_rng.permutation(split.train.shape[0])
+    skip = first_step % batches_per_epoch
     while step < total_steps:
         order = epoch_rng.permutation(split.train.shape[0])
-        for b in range(batches_per_epoch):
+        for b in range(skip, batches_per_epoch):
             if step >= total_steps:
                 break
             stage(split.train[order[b * B * world:(b + 1) * B * world]])

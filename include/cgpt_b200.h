@@ -173,7 +173,8 @@ int cgpt_attention_backward(void* dq, void* dk, void* dv, const void* dout, cons
  *      dx = dy*w*inv - x*c (+ residual_a + residual_b when given);  dw = sum_rows dy*x*inv.
  * residual_a / residual_b (may be NULL) are [rows, hidden] tensors added to dx in fp32 before the
  * single rounding: they fold the reference's `add_inplace` passes
- * (src/core/transformer_block.cu:678-681,747) into this kernel.
+ * (src/core/transformer_block.cu:678-681,747) into this kernel. dx may be the same buffer as residual_a or
+ * residual_b (each element is read before it is written, by the same thread); it may not alias dy or x.
  * ---------------------------------------------------------------------------------------------- */
 int cgpt_rmsnorm_forward(void* y, const void* x, const void* w, size_t rows, size_t hidden,
                          float epsilon, int dtype, cgpt_stream_t stream);

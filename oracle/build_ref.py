@@ -134,7 +134,7 @@ def build_cuda(reference: Path, force: bool = False) -> Path | None:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
-    ap.add_argument("--reference", default=os.environ.get("CGPT_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("CGPT_REFERENCE", str(HERE.parent.parent / "reference")))
     ap.add_argument("--force", action="store_true")
     args = ap.parse_args()
     print(build(Path(args.reference), args.force))

@@ -113,7 +113,7 @@ def _tiny(M, vocab=32000):
 
 
 def test_model_forward_backward_tiny(M):
-    """BASELINE config 1: tiny model, batch 2 x seq 128, full backward through the CCE loss."""
+    """The reference's CPU-runnable tiny model, batch 2 x seq 128, full backward through the CCE loss."""
     from cgpt_b200.train import TrainStep
     o = _tiny(M)
     batch, seq = 2, 128
