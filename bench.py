@@ -133,17 +133,90 @@ def cpu_baseline(threads: int | None, batch: int = 2, seq: int = 256, repeats: i
 
 
 def run_reference(args) -> None:
+    """The reference arm: the reference's own CPU implementation of the path. It has no CPU training step, so what runs is
+    its CPU forward + cross-entropy loss of the same 104m model on a bounded sample (2 x 256 tokens per pass); the line says
+    so in `config.workload`, and a whole 32 x 1024 step is NOT timed: `ms_per_step` is null and the extrapolated figure is
+    labelled as such."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun exports OMP_NUM_THREADS=1 to its ranks; the arm is meant to use every host core it can
+    threads = os.cpu_count() or 1
     steps = max(1, min(args.steps, 3))
-    base = cpu_baseline(None, batch=2, seq=256, repeats=steps)
-    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": None if base["value"] is None else 1000.0 * BATCH * SEQ / base["value"],
+    sample_batch, sample_seq = 2, 256
+    base = cpu_baseline(threads, batch=sample_batch, seq=sample_seq, repeats=steps)
+    config = workload_config(args.gpus)
+    config["workload"] = (f"reference CPU path of the same 104m model: forward + cross-entropy loss only, {sample_batch} x {sample_seq} tokens "
+                          f"per pass, {steps} passes (the reference has no CPU backward/optimizer step; GPU arm: " + config["workload"] + ")")
+    config["sample_tokens_per_pass"] = sample_batch * sample_seq
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+            "warmup": 0, "ms_per_step": None,
+            "ms_per_32x1024_step_extrapolated": None if base["value"] is None else 1000.0 * BATCH * SEQ / base["value"],
+            "ms_per_pass": None if base.get("seconds_per_pass") is None else 1000.0 * base["seconds_per_pass"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(args.gpus), "cpu_baseline": {k: v for k, v in base.items() if k != "seconds_per_pass"},
+            "config": config, "cpu_baseline": {k: v for k, v in base.items() if k != "seconds_per_pass"},
             "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)
+
+
+def reference_gpu_step(args) -> dict:
+    """Informational: the reference's own training step on this GPU -- its trainer's tensors and calls
+    (transformer_model_forward -> cross_entropy_forward_backward -> transformer_model_backward replayed from its CudaGraph,
+    then adamw_step_many_async; train/train.cpp:536-556), its kernels rebuilt for sm_100a and cuBLASLt for the linears --
+    on the same 104m shape and batch, timed with CUDA events; and its attention backward alone. Runs in a child process so
+    that its 20 GB of buffers and its own failure modes stay out of the measured process."""
+    code = (
+        "import json, sys, torch\n"
+        "sys.path.insert(0, %r)\n"
+        "from oracle import ref_cuda as R\n"
+        "from cgpt_b200 import model as M\n"
+        "B, S, steps = %d, %d, %d\n"
+        "o = M.preset('104m'); b = o.block_options\n"
+        "cos, sin = M.rotary_cache(S, b.rotary_dim)\n"
+        "ref = R.RefModel(o.vocabulary_size, o.num_layers, b.hidden_size, b.intermediate_size, b.num_query_heads, b.num_kv_heads,\n"
+        "                 b.head_dim, b.rotary_dim, b.rms_epsilon, B, S, cos, sin)\n"
+        "ref.init(0)\n"
+        "g = torch.Generator(device='cuda').manual_seed(1)\n"
+        "ids = torch.randint(0, o.vocabulary_size, (B * S,), generator=g, device='cuda', dtype=torch.int32)\n"
+        "tg = torch.randint(0, o.vocabulary_size, (B * S,), generator=g, device='cuda', dtype=torch.int32)\n"
+        "st = torch.cuda.Stream()\n"
+        "def step():\n"
+        "    ref.step(ids, tg, 1024.0, graph=True); ref.adamw(3e-4, 0.9, 0.95, 1e-8, 0.1, 1024.0, 1.0)\n"
+        "with torch.cuda.stream(st):\n"
+        "    for _ in range(3): step()\n"
+        "    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)\n"
+        "    e0.record(st)\n"
+        "    for _ in range(steps): step()\n"
+        "    e1.record(st)\n"
+        "    st.synchronize()\n"
+        "    ms = e0.elapsed_time(e1) / steps\n"
+        "    loss = ref.loss(); ok, n = ref.check()\n"
+        "out = {'ms_per_step': ms, 'tokens_per_s': B * S / ms * 1e3, 'steps': steps, 'loss': loss, 'optimizer_ok': ok}\n"
+        "ref.close()\n"
+        "def attn(Hq, Hkv, D, iters):\n"
+        "    h = lambda *s: torch.randn(*s, device='cuda').half()\n"
+        "    q, k, v, do = h(B, S, Hq, D), h(B, S, Hkv, D), h(B, S, Hkv, D), h(B, S, Hq, D)\n"
+        "    o_, lse = torch.empty_like(q), torch.empty(B, S, Hq, device='cuda')\n"
+        "    R.attention_forward(o_, lse, q, k, v)\n"
+        "    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)\n"
+        "    R.attention_backward(dq, dk, dv, do, o_, lse, q, k, v); torch.cuda.synchronize()\n"
+        "    a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)\n"
+        "    a.record()\n"
+        "    for _ in range(iters): R.attention_backward(dq, dk, dv, do, o_, lse, q, k, v)\n"
+        "    b_.record(); torch.cuda.synchronize()\n"
+        "    us = a.elapsed_time(b_) / iters * 1e3\n"
+        "    return {'shape': f'B{B} S{S} {Hq}/{Hkv} D{D}', 'us': us, 'tflops': 2.5 * 4.0 * S * S * D * Hq * B / 2 / us / 1e6}\n"
+        "out['attention_backward'] = [attn(8, 2, 128, 5), attn(12, 4, 64, 2)]\n"
+        "print('REFERENCE_GPU ' + json.dumps(out))\n"
+    ) % (str(ROOT), BATCH, SEQ, max(3, min(args.steps, 10)))
+    proc = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=900)
+    for ln in proc.stdout.splitlines():
+        if ln.startswith("REFERENCE_GPU "):
+            out = json.loads(ln[len("REFERENCE_GPU "):])
+            out["what"] = ("the reference's trainer step (CUDA graph of forward + cross-entropy on materialised fp16 logits + backward, then its "
+                           "181-launch AdamW) with its own kernels rebuilt for sm_100a and cuBLASLt, same model, batch and GPU; informational")
+            return out
+    return {"error": (proc.stderr or proc.stdout)[-400:], "rc": proc.returncode}
 
 
 # ------------------------------------------------------------------------------------------------ our arm
@@ -173,8 +246,9 @@ def run_ours(args) -> None:
     from cgpt_b200.train import TrainStep
 
     opts = M.preset(PRESET)
-    # CGPT_B200_OVERLAP_ALLREDUCE=1: eager step with the bucketed all-reduce overlapping the backward (N > 1 only)
-    overlap = os.environ.get("CGPT_B200_OVERLAP_ALLREDUCE", "0") == "1"
+    # N > 1: the bucketed all-reduce overlaps the backward inside the captured graph; CGPT_B200_OVERLAP_ALLREDUCE=0 issues all
+    # buckets after the backward instead (still inside the graph)
+    overlap = os.environ.get("CGPT_B200_OVERLAP_ALLREDUCE", "1") == "1"
     ts = TrainStep(opts, BATCH, SEQ, seed=0, process_group=pg, overlap_allreduce=overlap)
     rows = BATCH * SEQ
     gen = torch.Generator().manual_seed(1234 + rank)
@@ -287,8 +361,19 @@ def run_ours(args) -> None:
             line["attention_backward"] = [dict(a, frac_of_measured_burst_peak=(a["tflops"] / burst if burst else None)) for a in ab]
         except Exception as exc:
             line["attention_backward"] = {"error": repr(exc)}
+        try:   # the loss layer on its own at 32768 tokens x d 768 x vocab 32000 (three products credited)
+            line["cce"] = profiling.time_cut_cross_entropy(32768, 768, 32000)
+            burst = measured_peaks().get("bf16_tflops")
+            line["cce"]["frac_of_measured_burst_peak"] = line["cce"]["tflops"] / burst if burst else None
+        except Exception as exc:
+            line["cce"] = {"error": repr(exc)}
+        if world == 1:
+            try:   # informational: the reference's own CUDA step (its kernels rebuilt for sm_100a + cuBLASLt) on this GPU
+                line["reference_gpu"] = reference_gpu_step(args)
+            except Exception as exc:
+                line["reference_gpu"] = {"error": repr(exc)}
         try:
-            line["cpu_baseline"] = {k: v for k, v in cpu_baseline(None).items() if k != "seconds_per_pass"} if world == 1 else None
+            line["cpu_baseline"] = {k: v for k, v in cpu_baseline(os.cpu_count()).items() if k != "seconds_per_pass"} if world == 1 else None
         except Exception as exc:
             line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "reference", "sample": repr(exc)}
         print(json.dumps(line), flush=True)
@@ -300,7 +385,7 @@ def run_ours(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     args = ap.parse_args()

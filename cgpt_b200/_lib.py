@@ -129,6 +129,7 @@ SIGNATURES = {
     "cgpt_adamw_create": (_i, [C.POINTER(_vp), C.POINTER(AdamWTensor), _sz, _u64, _vp]),
     "cgpt_adamw_destroy": (_i, [_vp]),
     "cgpt_adamw_step": (_i, [_vp, C.POINTER(AdamWOptions), _vp]),
+    "cgpt_adamw_step_device_lr": (_i, [_vp, C.POINTER(AdamWOptions), _vp, _vp]),
     "cgpt_adamw_check": (_i, [_vp, C.POINTER(_u64), C.POINTER(_i), _vp]),
     "cgpt_adamw_last_stats": (_i, [_vp, C.POINTER(_f), C.POINTER(_f), _vp]),
 }

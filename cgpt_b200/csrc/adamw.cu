@@ -197,8 +197,10 @@ __device__ __forceinline__ void update_chunk(T* __restrict__ p, const T* __restr
 
 __global__ void __launch_bounds__(kAdamThreads)
 adamw_update_kernel(const DevTensor* __restrict__ tensors, const Chunk* __restrict__ chunks, unsigned int n_chunks,
-                    Hyper h, const unsigned int* __restrict__ state, const float* __restrict__ scalars) {
+                    Hyper h, const unsigned int* __restrict__ state, const float* __restrict__ scalars,
+                    const float* __restrict__ lr_device) {
     if (state[0] != 0u) return;  // non-finite gradients: the whole step is skipped
+    if (lr_device != nullptr) h.lr = *lr_device;   // the step's learning rate as a device scalar (captured graphs)
     const float bc1 = scalars[0], bc2 = scalars[1], clip = scalars[2];
     for (unsigned int c = blockIdx.x; c < n_chunks; c += gridDim.x) {
         const Chunk ch = chunks[c];
@@ -299,7 +301,22 @@ extern "C" int cgpt_adamw_create(cgpt_adamw_workspace** out, const cgpt_adamw_te
     return CGPT_OK;
 }
 
+namespace {
+int adamw_step_impl(cgpt_adamw_workspace* ws, const cgpt_adamw_options* o, const float* lr_device, cgpt_stream_t stream);
+}
+
 extern "C" int cgpt_adamw_step(cgpt_adamw_workspace* ws, const cgpt_adamw_options* o, cgpt_stream_t stream) {
+    return adamw_step_impl(ws, o, nullptr, stream);
+}
+
+extern "C" int cgpt_adamw_step_device_lr(cgpt_adamw_workspace* ws, const cgpt_adamw_options* o, const float* learning_rate_device,
+                                         cgpt_stream_t stream) {
+    if (!learning_rate_device) return CGPT_ERR_NULL;
+    return adamw_step_impl(ws, o, learning_rate_device, stream);
+}
+
+namespace {
+int adamw_step_impl(cgpt_adamw_workspace* ws, const cgpt_adamw_options* o, const float* lr_device, cgpt_stream_t stream) {
     if (!ws || !o) return CGPT_ERR_NULL;
     // Same validation as the reference's validate_options (src/optim/adamw.cu:28-45).
     if (!(o->learning_rate >= 0.f) || !(o->beta1 >= 0.f && o->beta1 < 1.f) || !(o->beta2 >= 0.f && o->beta2 < 1.f) ||
@@ -316,11 +333,12 @@ extern "C" int cgpt_adamw_step(cgpt_adamw_workspace* ws, const cgpt_adamw_option
     CGPT_LAUNCH_CHECK();
     const Hyper h{o->beta1, o->beta2, o->learning_rate, o->epsilon, o->weight_decay, o->loss_scale};
     adamw_update_kernel<<<ws->grid, kAdamThreads, 0, s>>>(ws->d_tensors, ws->d_chunks, ws->n_chunks, h, ws->d_state,
-                                                         ws->d_scalars);
+                                                         ws->d_scalars, lr_device);
     count_launch();
     CGPT_LAUNCH_CHECK();
     return CGPT_OK;
 }
+}  // namespace
 
 extern "C" int cgpt_adamw_check(cgpt_adamw_workspace* ws, uint64_t* step_out, int* non_finite_out,
                                 cgpt_stream_t stream) {

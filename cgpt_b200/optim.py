@@ -111,9 +111,10 @@ def _validate_entry(e: AdamWBatchEntry) -> None:
             raise _lib.CgptInvalidArgument("adamw_step: tensors must be contiguous")
 
 
-def adamw_step_many_async(entries, options: AdamWOptions, workspace: AdamWWorkspace, stream=None) -> None:
-    """One fused optimizer step over all entries (include/optim/adamw.h:101-105)."""
-    options.validate()
+def adamw_bind(entries, workspace: AdamWWorkspace, stream=None) -> list:
+    """Binds the workspace to the entry list (device tables, step counter seeded from the states) without taking a step;
+    adamw_step_many_async does it on first use (src/optim/adamw.cu:283-305). Allocates: call it outside stream capture.
+    Returns the validated entry list; raises if the workspace is already bound to a different list."""
     entries = list(entries)
     if not entries:
         raise _lib.CgptInvalidArgument("adamw_step_many_async: empty parameter list")
@@ -140,7 +141,23 @@ def adamw_step_many_async(entries, options: AdamWOptions, workspace: AdamWWorksp
         raise _lib.CgptInvalidArgument("adamw_step_many_async: workspace entries changed")
     elif any(a is not b.state for a, b in zip(workspace._states, entries)) or keys != workspace._keys:
         raise _lib.CgptInvalidArgument("adamw_step_many_async: workspace states changed")
+    return entries
+
+
+def adamw_step_many_async(entries, options: AdamWOptions, workspace: AdamWWorkspace, stream=None,
+                          learning_rate_device: torch.Tensor | None = None) -> None:
+    """One fused optimizer step over all entries (include/optim/adamw.h:101-105). With `learning_rate_device` (an fp32
+    CUDA tensor of one element) the update reads the learning rate from it when it runs instead of taking
+    options.learning_rate at launch: the form that can be captured into a CUDA graph and replayed under a schedule."""
+    options.validate()
+    adamw_bind(entries, workspace, stream)
     copts = options._c()
+    if learning_rate_device is not None:
+        if not (learning_rate_device.is_cuda and learning_rate_device.dtype == torch.float32 and learning_rate_device.numel() == 1):
+            raise _lib.CgptInvalidArgument("adamw_step_many_async: learning_rate_device must be one fp32 CUDA element")
+        check(lib.cgpt_adamw_step_device_lr(workspace._handle, C.byref(copts), learning_rate_device.data_ptr(), stream_ptr(stream)),
+              "adamw_step_many_async")
+        return
     check(lib.cgpt_adamw_step(workspace._handle, C.byref(copts), stream_ptr(stream)), "adamw_step_many_async")
 
 

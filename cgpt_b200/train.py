@@ -1,10 +1,13 @@
 """One training step (forward + cut-cross-entropy loss + backward + AdamW), optionally data-parallel.
 
 Follows the reference trainer's step (train/train.cpp:427-457, 532-556): fp16 weights and activations,
-fp32 master weights, static loss scale, forward+loss+backward captured once into a CUDA graph and
-replayed, AdamW launched after it with the step's learning rate. Differences: the loss layer is the
-cut-cross-entropy op (no [tokens, vocab] logits), and with more than one rank the gradients are
-averaged with bucketed NCCL all-reduces between the backward and the optimizer.
+fp32 master weights, static loss scale, the step captured once into a CUDA graph and replayed.
+Differences: the loss layer is the cut-cross-entropy op (no [tokens, vocab] logits); the captured graph
+holds the WHOLE step, optimizer included (the learning rate is a device scalar written before each
+replay; the reference launches its optimizer outside its graph because the rate is a kernel argument,
+train/train.cpp:554-556); and with more than one rank the graph also holds the bucketed NCCL all-reduces,
+each started on the communication stream as soon as the backward has finished the gradients of its
+bucket, so they overlap the rest of the backward, and joined before the optimizer.
 """
 from __future__ import annotations
 
@@ -30,7 +33,7 @@ class TrainStep:
     def __init__(self, options: M.TransformerModelOptions, batch: int, seq: int, *, dtype=torch.float16, seed: int = 0,
                  loss_scale: float = 1024.0, adamw: O.AdamWOptions | None = None, process_group=None,
                  bucket_bytes: int = 48 << 20, use_graph: bool = True, cce_chunk_rows: int = 0, device="cuda",
-                 overlap_allreduce: bool = False):
+                 overlap_allreduce: bool = True):
         self.options, self.batch, self.seq, self.dtype = options, batch, seq, dtype
         self.rows = batch * seq
         self.pg = process_group
@@ -53,14 +56,19 @@ class TrainStep:
         self.adamw_workspace = O.AdamWWorkspace()
         self.stream = torch.cuda.Stream(device=device)
         self.graph = None
-        # With more than one rank the bucketed all-reduce overlaps the backward: the step is then issued eagerly, piece by
-        # piece (a captured graph would have to contain the collectives); one rank replays the captured graph.
+        # With more than one rank the backward is issued piece by piece and every bucket's all-reduce starts as soon as
+        # its gradients are final (overlap_allreduce=False issues all of them after the backward instead). Either way the
+        # collectives are part of the captured graph.
         self.overlap_allreduce = bool(overlap_allreduce) and self.world > 1
-        self.use_graph = use_graph and not self.overlap_allreduce
+        self.use_graph = use_graph
         self._buckets = self._make_buckets(bucket_bytes)
         self._reducer = dp.BucketReducer(self._buckets, self.pg) if self.overlap_allreduce else None
         self._keep = None
         self._loss_ring = None
+        # the step's learning rate as a device scalar, fed from a small ring of pinned host values
+        self.learning_rate_device = torch.full((1,), float(self.adamw_options.learning_rate), dtype=torch.float32, device=device)
+        self._lr_ring = [(torch.empty(1, dtype=torch.float32).pin_memory(), torch.cuda.Event()) for _ in range(8)]
+        self._lr_writes = 0
         self.adopt_default_stream_work()
 
     def adopt_default_stream_work(self) -> None:
@@ -109,23 +117,46 @@ class TrainStep:
             return
         dp.allreduce_buckets(self._buckets, group=self.pg)
 
+    def _write_learning_rate(self, value: float) -> None:
+        """Pinned host value -> device scalar on the step's stream (4 bytes; the slot is reused only after its copy ran)."""
+        host, copied = self._lr_ring[self._lr_writes % len(self._lr_ring)]
+        if self._lr_writes >= len(self._lr_ring):
+            copied.synchronize()
+        self._lr_writes += 1
+        host[0] = value
+        self.learning_rate_device.copy_(host, non_blocking=True)
+        copied.record(self.stream)
+
+    def enqueue_full_step(self) -> None:
+        """The whole step on the current stream (capturable): model step, gradient all-reduce, AdamW with the learning
+        rate read from the device scalar."""
+        self.enqueue_model_step()
+        self._allreduce_gradients()
+        O.adamw_step_many_async(self.entries, self.adamw_options, self.adamw_workspace, learning_rate_device=self.learning_rate_device)
+
     def step(self, learning_rate: float | None = None) -> None:
         """One optimizer step on the batch currently in token_ids/targets. Asynchronous."""
         if learning_rate is not None:
             self.adamw_options.learning_rate = learning_rate
         with torch.cuda.stream(self.stream):
+            self._write_learning_rate(float(self.adamw_options.learning_rate))
             if self.use_graph:
                 if self.graph is None:
-                    self.enqueue_model_step()          # eager warm-up sizes the library's scratch arena
+                    # Eager warm-up: sizes the library's scratch arena, binds the optimizer workspace and opens NCCL's
+                    # channels. It must not change the training state, so it runs the model step and the collectives but
+                    # not the optimizer (a gradient all-reduce of a repeated batch is harmless: the step that follows
+                    # recomputes every gradient).
+                    self.enqueue_model_step()
+                    self._allreduce_gradients()
+                    O.adamw_bind(self.entries, self.adamw_workspace)
                     self.stream.synchronize()
                     self.graph = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(self.graph, stream=self.stream):
-                        self.enqueue_model_step()
+                    # thread-local capture mode: NCCL's watchdog thread may query events while this thread captures
+                    with torch.cuda.graph(self.graph, stream=self.stream, capture_error_mode="thread_local"):
+                        self.enqueue_full_step()
                 self.graph.replay()
             else:
-                self.enqueue_model_step()
-            self._allreduce_gradients()
-            O.adamw_step_many_async(self.entries, self.adamw_options, self.adamw_workspace)
+                self.enqueue_full_step()
 
     def validation_loss(self) -> float:
         """Loss of the batch currently in token_ids/targets without an optimizer step (train/train.cpp:490-530 runs

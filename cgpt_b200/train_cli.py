@@ -46,8 +46,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--validation-fraction", type=float, default=0.1)
     p.add_argument("--save-avg-loss", action="store_true")
     p.add_argument("--checkpoint-interval", type=int, default=0, help="also write a checkpoint every N steps (0 = only at the end)")
-    p.add_argument("--overlap-allreduce", action="store_true",
-                   help="ranks > 1: issue the step eagerly and start each gradient bucket's all-reduce during the backward")
+    p.add_argument("--overlap-allreduce", action=argparse.BooleanOptionalAction, default=True,
+                   help="ranks > 1: start each gradient bucket's all-reduce during the backward, inside the captured graph "
+                        "(--no-overlap-allreduce: all buckets after the backward)")
     p.add_argument("--seed", type=int, default=0)
     return p
 

@@ -320,6 +320,12 @@ int cgpt_adamw_create(cgpt_adamw_workspace** out, const cgpt_adamw_tensor* tenso
 int cgpt_adamw_destroy(cgpt_adamw_workspace* ws);
 int cgpt_adamw_step(cgpt_adamw_workspace* ws, const cgpt_adamw_options* options,
                     cgpt_stream_t stream);
+/* The same step with the learning rate read from a device scalar (fp32 [1]) when the update kernel runs, instead of
+ * options->learning_rate: the three launches can then sit inside a captured CUDA graph while the schedule changes the
+ * rate every step by writing the scalar (a 4-byte copy enqueued before the replay). The reference launches its optimizer
+ * outside its graph for exactly this reason (train/train.cpp:554-556: the rate is a by-value kernel argument). */
+int cgpt_adamw_step_device_lr(cgpt_adamw_workspace* ws, const cgpt_adamw_options* options,
+                              const float* learning_rate_device, cgpt_stream_t stream);
 int cgpt_adamw_check(cgpt_adamw_workspace* ws, uint64_t* step_out, int* non_finite_out,
                      cgpt_stream_t stream);
 /* Reads back the statistics of the last step (sum of squared unscaled gradients, clip factor).

@@ -35,15 +35,39 @@ CPU_SOURCES = [
 ]
 CUDA_SOURCES = ["src/core/tensor.cu", "src/optim/adamw.cu"]  # host code paths only are exercised
 
-# The reference's GPU operators (everything on the path except the cuBLASLt-based linear files), for the second
-# library oracle/_ref/libcgpt_ref_cuda.so: the reference's own kernels, rebuilt for sm_100a.
+# The reference's GPU code on the path, for the second library oracle/_ref/libcgpt_ref_cuda.so: its own operators, block,
+# model, optimizer and graph wrapper, rebuilt for sm_100a. src/ops/linear.cu goes in as a build-time copy (below).
 LIB_CUDA = OUT / "libcgpt_ref_cuda.so"
 GPU_SOURCES = [
     "src/core/tensor.cu", "src/ops/attention.cu", "src/ops/cross_entropy.cu", "src/ops/cut_cross_entropy.cu",
     "src/ops/embedding.cu", "src/ops/rmsnorm.cu", "src/ops/rope.cu", "src/ops/softmax.cu", "src/ops/swiglu.cu",
     "src/ops/backward/attention_backward.cu", "src/ops/backward/embedding_backward.cu",
     "src/ops/backward/rmsnorm_backward.cu", "src/ops/backward/rope_backward.cu", "src/ops/backward/swiglu_backward.cu",
+    "src/ops/backward/linear_backward.cu", "src/core/transformer_block.cu", "src/core/transformer_model.cu",
+    "src/core/kv_cache.cu", "src/core/cuda_graph.cu", "src/core/weight_initialization.cu", "src/optim/adamw.cu",
 ]
+# src/ops/linear.cu stops nvcc 12.9's front end with an internal error at the declaration
+# `std::vector<cublasLtMatmulHeuristicResult_t> heuristics(max_algorithms);` (linear.cu:271). The build writes a copy under
+# oracle/_ref/ in which that vector is a C array (two textual edits, :271 and :282) and compiles the copy; the checkout is
+# not touched and the copy is never committed.
+LINEAR_SOURCE = "src/ops/linear.cu"
+LINEAR_EDITS = [
+    ("std::vector<cublasLtMatmulHeuristicResult_t> heuristics(max_algorithms);",
+     "cublasLtMatmulHeuristicResult_t heuristics[max_algorithms];"),
+    ("heuristics.data(),", "heuristics,"),
+]
+WRAPPERS = ["ref_wrap_cuda.cpp", "ref_wrap_model.cpp"]
+
+
+def patched_linear(reference: Path) -> Path:
+    text = (reference / LINEAR_SOURCE).read_text()
+    for old, new in LINEAR_EDITS:
+        if text.count(old) != 1:
+            raise RuntimeError(f"{LINEAR_SOURCE}: expected exactly one occurrence of {old!r}")
+        text = text.replace(old, new)
+    out = OUT / "linear_patched.cu"
+    out.write_text(text)
+    return out
 # per-file options of the reference's CMakeLists.txt:54
 FAST_MATH = {"src/ops/cross_entropy.cu", "src/ops/softmax.cu"}
 
@@ -95,8 +119,8 @@ def build(reference: Path, force: bool = False) -> Path | None:
 
 def build_cuda(reference: Path, force: bool = False) -> Path | None:
     """The reference's CUDA operators + oracle/ref_wrap_cuda.cpp -> oracle/_ref/libcgpt_ref_cuda.so (sm_100a)."""
-    wrap = HERE / "ref_wrap_cuda.cpp"
-    inputs = [reference / s for s in GPU_SOURCES + CPU_SOURCES] + [wrap]
+    wraps = [HERE / w for w in WRAPPERS]
+    inputs = [reference / s for s in GPU_SOURCES + CPU_SOURCES + [LINEAR_SOURCE]] + wraps + [Path(__file__)]
     if LIB_CUDA.exists() and not force and all(LIB_CUDA.stat().st_mtime > p.stat().st_mtime for p in inputs):
         return LIB_CUDA
     inc = ["-I", str(reference / "include"), "-I", str(reference / "include" / "core"), "-I", "/usr/local/cuda/include"]
@@ -109,13 +133,18 @@ def build_cuda(reference: Path, force: bool = False) -> Path | None:
         obj = OUT / ("gpu_" + rel.replace("/", "_") + ".o")
         objects.append(obj)
         jobs.append([*nvcc, *(["--use_fast_math"] if rel in FAST_MATH else []), "-c", str(reference / rel), "-o", str(obj)])
+    linear_copy = patched_linear(reference)
+    obj = OUT / "gpu_linear_patched.o"
+    objects.append(obj)
+    jobs.append([*nvcc, "-c", str(linear_copy), "-o", str(obj)])
     for rel in CPU_SOURCES:   # the GPU entry points dispatch to these for CPU tensors, so the symbols must resolve
         obj = OUT / ("gpu_" + rel.replace("/", "_") + ".o")
         objects.append(obj)
         jobs.append([*cxx, "-c", str(reference / rel), "-o", str(obj)])
-    obj = OUT / "ref_wrap_cuda.o"
-    objects.append(obj)
-    jobs.append([*cxx, "-c", str(wrap), "-o", str(obj)])
+    for wrap in wraps:
+        obj = OUT / (wrap.stem + ".o")
+        objects.append(obj)
+        jobs.append([*cxx, "-c", str(wrap), "-o", str(obj)])
 
     def run(cmd):
         proc = subprocess.run(cmd, capture_output=True, text=True)
@@ -126,9 +155,10 @@ def build_cuda(reference: Path, force: bool = False) -> Path | None:
         list(pool.map(run, jobs))
     run(["/usr/local/cuda/bin/nvcc", "-ccbin", "/usr/bin/g++", "-shared", "-cudart", "shared", "-Xcompiler", "-fopenmp",
          "-gencode", "arch=compute_100a,code=sm_100a", "-Xlinker", "-rpath,/usr/local/cuda/lib64", "-Xlinker", "--no-undefined",
-         "-o", str(LIB_CUDA), *map(str, objects)])
+         "-o", str(LIB_CUDA), *map(str, objects), "-lcublasLt", "-lcublas"])
     for o in objects:
         o.unlink(missing_ok=True)
+    linear_copy.unlink(missing_ok=True)
     return LIB_CUDA
 
 

@@ -25,3 +25,20 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_sessionfinish(session, exitstatus):
+    """After a GPU run: every comparison the parity tests made, with the error each assertion used and, beside it, the
+    plain norm-scaled error max|a-b|/rms(b). Written to $CGPT_PARITY_REPORT when that is set."""
+    import os
+    path = os.environ.get("CGPT_PARITY_REPORT")
+    try:
+        from gpu_util import REPORT
+    except Exception:  # pragma: no cover
+        return
+    if not path or not REPORT:
+        return
+    with open(path, "w") as f:
+        f.write("comparison\tmetric\terror\ttolerance\tplain max|a-b|/rms(b)\n")
+        for what, metric, e, tol, plain in REPORT:
+            f.write(f"{what}\t{metric}\t{e:.3e}\t{tol:.1e}\t{plain:.3e}\n")

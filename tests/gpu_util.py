@@ -41,7 +41,22 @@ def max_err(got, want):
     return float(np.max(np.abs(got - want)) / max(np.max(np.abs(want)), 1e-30))
 
 
+def plain_err(got, want):
+    """The parity bar's error as it is usually written: max |a-b| / rms(b) (rms(b) = ||b||_2 / sqrt(n))."""
+    got = np.asarray(got, np.float64); want = np.asarray(want, np.float64)
+    rms = np.sqrt(np.mean(want ** 2))
+    return float(np.max(np.abs(got - want)) / max(rms, 1e-30))
+
+
+# (what, metric used, value, tolerance, plain max|a-b|/rms(b)) of every comparison of the session; tests/conftest.py writes it
+# out at the end of a GPU run so that the plain norm-scaled number stands beside the one each assertion used.
+REPORT = []
+
+
 def assert_close(got, want, tol, what="", metric="rms"):
-    e = scaled_err(got, want) if metric == "rms" else max_err(got, want)
+    """metric: "rms" = scaled_err, "max" = max_err, "plain" = plain_err."""
+    e = {"rms": scaled_err, "max": max_err, "plain": plain_err}[metric](got, want)
+    plain = plain_err(got, want)
+    REPORT.append((what, metric, e, tol, plain))
     assert np.all(np.isfinite(np.asarray(got))), f"{what}: non-finite output"
-    assert e <= tol, f"{what}: norm-scaled max error {e:.3e} > {tol:.1e}"
+    assert e <= tol, f"{what}: {metric} error {e:.3e} > {tol:.1e} (plain max|a-b|/rms(b) = {plain:.3e})"
