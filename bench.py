@@ -377,9 +377,17 @@ def run_ours(args) -> None:
         except Exception as exc:
             line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "reference", "sample": repr(exc)}
         print(json.dumps(line), flush=True)
+    ts.close()      # the captured graph holds the collectives: release it before the process group goes
     if world > 1:
         dist.barrier()
+        torch.cuda.synchronize()
+        # The line is printed and every rank is past its last collective. Should the process group's shutdown stall (its
+        # watchdog waiting on work it can no longer observe), leave after 30 s instead of holding the launcher for minutes.
+        guard = threading.Timer(30.0, lambda: os._exit(0))
+        guard.daemon = True
+        guard.start()
         dist.destroy_process_group()
+        guard.cancel()
 
 
 def main() -> None:

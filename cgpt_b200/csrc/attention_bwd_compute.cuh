@@ -1,5 +1,9 @@
-// Compute role (warps 0-3) of attention_bwd_tc_kernel: thread t owns stationary row t = TMEM lane t.
-// Included by attention_bwd_tc.cu only.
+// Compute role (warps 0-7) of attention_bwd_tc_kernel. The two warpgroups take the streaming tiles in turn: warpgroup w
+// owns the tiles with (it & 1) == w, i.e. always the same one of the two T1/T2 buffers in TMEM, and thread t of a
+// warpgroup owns stationary row t = TMEM lane t of its tile (all 64 columns, in two chunks of 32). While one warpgroup
+// waits for its tile's products, for a TMEM load or for its stores to land, the other is in its arithmetic, so the
+// per-tile latencies of the chain (T products -> load -> exponentials -> store -> accumulating products) overlap
+// instead of adding up in every tile period. Included by attention_bwd_tc.cu only.
 #pragma once
 
 // One thread's 32 columns of a tile: P = 2^(S*scale2 - lse2) (0 where masked), W = P * (dP*scale - delta*scale), both packed
@@ -40,7 +44,7 @@ __device__ __forceinline__ bool bwd_compute(unsigned char* smem, const BwdBars& 
                                             int accumulate) {
     using L = BwdSmem<D>;
     const int row = threadIdx.x & (kRows - 1);         // 0..127: TMEM lane; two threads (one per warpgroup) share a row
-    const int half = threadIdx.x >> 7;                 // which 32 of the tile's 64 columns this thread handles
+    const int half = threadIdx.x >> 7;                 // warpgroup: owns the tiles with (it & 1) == half; half of the epilogue's columns
     const int warp = (threadIdx.x >> 5) & 3;           // lane quarter of this warp
     const std::uint32_t lane_base = static_cast<std::uint32_t>(warp * 32) << 16;
     const float scale2 = dm.scale * kLog2e;
@@ -62,11 +66,13 @@ __device__ __forceinline__ bool bwd_compute(unsigned char* smem, const BwdBars& 
     bool failed = false;
 
     constexpr int kYStages = L::kStages;
-    int ys = 0;                 // ring stage of the streaming tile = it % kYStages
-    std::uint32_t ypar = 0;     // its phase = (it / kYStages) & 1
-    for (int it = 0; it < g.n_it; ++it) {
-        const int s = it & 1;
-        const std::uint32_t par = (it >> 1) & 1;
+    using TM = BwdTmem<D, MODE>;
+    constexpr int kTBufs = TM::kTBufs;
+    for (int it = half; it < g.n_it; it += 2) {
+        const int s = it % kTBufs;                                 // the tile's T1/T2 buffer in TMEM
+        const std::uint32_t par = (it / kTBufs) & 1;               // and the phase of its barriers
+        const int ys = it % kYStages;                              // ring stage of the streaming tile
+        const std::uint32_t ypar = (it / kYStages) & 1;            // and its phase
         int head, y0;
         bwd_stream_coords<MODE>(g, it, &head, &y0);
         if (!mbar_wait(&bars.t_full[s], par)) failed = true;
@@ -80,10 +86,10 @@ __device__ __forceinline__ bool bwd_compute(unsigned char* smem, const BwdBars& 
         bool need_mask;
         if (MODE == MODE_DQ) need_mask = (y0 + kCols > dm.sk) || (dm.causal && y0 + kCols - 1 > dm.offset + g.x0);
         else need_mask = dm.causal && (g.x0 + kRows - 1 > dm.offset + y0);
-        {
-            const int c0 = half * 32;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kCols; c0 += 32) {
             std::uint32_t t1[32], t2[32];
-            tmem_ld_32x32_x2(tmem + s * kCols + lane_base + c0, t1, tmem + 128 + s * kCols + lane_base + c0, t2);
+            tmem_ld_32x32_x2(tmem + TM::kT1 + s * kCols + lane_base + c0, t1, tmem + TM::kT2 + s * kCols + lane_base + c0, t2);
             std::uint32_t pu[16], pw[16];
             // column j of this thread's 32 is visible iff j <= thr (dQ: key <= limit) or j >= thr (dKV: query >= key - offset)
             const int thr = MODE == MODE_DQ ? limit - y0 - c0 : x_idx - dm.offset - y0 - c0;
@@ -92,14 +98,13 @@ __device__ __forceinline__ bool bwd_compute(unsigned char* smem, const BwdBars& 
             // U (P^T) and W (dS or dS^T) go back into TMEM over this thread's own, already read, columns of T1 and T2:
             // 16 packed words at columns [c0, c0 + 16) of the tile's buffer. The accumulating products read them from
             // there as their A operands, so neither the stores nor the operand reads touch shared memory.
-            if (MODE == MODE_DKV) tmem_st_32x16(tmem + s * kCols + lane_base + c0, pu);
-            tmem_st_32x16(tmem + 128 + s * kCols + lane_base + c0, pw);
+            if (MODE == MODE_DKV) tmem_st_32x16(tmem + TM::kT1 + s * kCols + lane_base + c0, pu);
+            tmem_st_32x16(tmem + TM::kT2 + s * kCols + lane_base + c0, pw);
         }
         tmem_st_wait();
         tc_fence_before_sync();
         mbar_arrive(&bars.w_full[s]);
         if (threadIdx.x == 0) bwd_trace(bars, it, 4);
-        if (++ys == kYStages) { ys = 0; ypar ^= 1u; }
     }
 
     // ---- epilogue: accumulators -> global
@@ -118,7 +123,7 @@ __device__ __forceinline__ bool bwd_compute(unsigned char* smem, const BwdBars& 
     for (int o = 0; o < kOuts; ++o) {
         // dKV: acc1 = dV -> out2 (grad_value), acc2 = dK -> out1 (grad_key); dQ: acc1 -> out1
         T* dst = (MODE == MODE_DKV ? (o == 0 ? out2 : out1) : out1) + dst_off;
-        const std::uint32_t acc = tmem + 256 + o * D;
+        const std::uint32_t acc = tmem + TM::kAcc + o * D;
 #pragma unroll
         for (int cc = 0; cc < D / 2; cc += 32) {
             const int c0 = half * (D / 2) + cc;

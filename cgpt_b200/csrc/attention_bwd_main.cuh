@@ -25,10 +25,11 @@ __device__ __forceinline__ void bwd_cta(const CUtensorMap& map_x1, const CUtenso
     bars.stat_full = bar + 1 + kYStages;        // [kYStages]
     bars.y_free = bar + 1 + 2 * kYStages;       // [kYStages]
     bars.uw_free = bar + 1 + 3 * kYStages;      // [1]
-    bars.t_full = bars.uw_free + 1;             // [2]
-    bars.w_full = bars.uw_free + 3;             // [2]
-    bars.acc_done = bars.uw_free + 5;
-    static_assert((1 + 3 * kYStages + 6) * 8 + 4 <= 256, "barrier area");
+    constexpr int kTBufs = BwdTmem<D, MODE>::kTBufs;
+    bars.t_full = bars.uw_free + 1;             // [3]
+    bars.w_full = bars.uw_free + 4;             // [3]
+    bars.acc_done = bars.uw_free + 7;
+    static_assert((1 + 3 * kYStages + 8) * 8 + 4 <= 256, "barrier area");
     bars.trace = (trace != nullptr && item == items / 4) ? trace : nullptr;
     std::uint32_t* tmem_slot = reinterpret_cast<std::uint32_t*>(bars.acc_done + 1);
 
@@ -74,9 +75,9 @@ __device__ __forceinline__ void bwd_cta(const CUtensorMap& map_x1, const CUtenso
             mbar_init(&bars.y_free[s], 1);
         }
         mbar_init(bars.uw_free, 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < kTBufs; ++s) {
             mbar_init(&bars.t_full[s], 1);
-            mbar_init(&bars.w_full[s], 2 * kRows);
+            mbar_init(&bars.w_full[s], kRows);          // one warpgroup owns each of the two T buffers
         }
         mbar_init(bars.acc_done, 1);
         mbar_init_fence();

@@ -110,7 +110,9 @@ __device__ __forceinline__ bool bwd_mma_issuer(unsigned char* smem, const BwdBar
     constexpr std::uint32_t idesc_t = idesc_f16(fmt, 0, 0, kRows, kCols);   // T = X Y^T: both K-major
     constexpr std::uint32_t idesc_acc = idesc_f16(fmt, 0, 1, kRows, D);     // acc += U/W (K-major) * Y (N-major)
     constexpr std::uint32_t kYStage16 = (2 * L::kYBytes) >> 4;              // ring stage stride in descriptor units
-    const std::uint32_t tmem_acc1 = tmem + 256, tmem_acc2 = tmem + 256 + D;
+    using TM = BwdTmem<D, MODE>;
+    constexpr int kTBufs = TM::kTBufs;
+    const std::uint32_t tmem_acc1 = tmem + TM::kAcc, tmem_acc2 = tmem + TM::kAcc + D;
     const std::uint64_t dx1 = smem_desc_sw128(smem_u32(smem + L::kX1), 16, 1024);
     const std::uint64_t dx2 = smem_desc_sw128(smem_u32(smem + L::kX2), 16, 1024);
     const std::uint32_t y_base = smem_u32(smem + L::kY);
@@ -119,13 +121,13 @@ __device__ __forceinline__ bool bwd_mma_issuer(unsigned char* smem, const BwdBar
     const std::uint64_t dy1n = smem_desc_sw128(y_base, kCols * 128, 1024);              // as N-major B of the accumulations
     const std::uint64_t dy2n = smem_desc_sw128(y_base + L::kYBytes, kCols * 128, 1024);
 
-    // T1/T2 of tile `it` whose streaming pair sits in ring stage ys (phase ypar)
-    auto issue_t = [&](int it, int ys, std::uint32_t ypar) -> bool {
+    // T1/T2 of tile `it` (TMEM buffer tb) whose streaming pair sits in ring stage ys (phase ypar)
+    auto issue_t = [&](int it, int tb, int ys, std::uint32_t ypar) -> bool {
         if (!mbar_wait(&bars.y_full[ys], ypar)) return false;
         bwd_trace(bars, it, 1);
         tc_fence_after_sync();
-        const int s = it & 1;
-        const std::uint32_t t1 = tmem + s * kCols, t2 = tmem + 128 + s * kCols;
+        const int s = tb;
+        const std::uint32_t t1 = tmem + TM::kT1 + s * kCols, t2 = tmem + TM::kT2 + s * kCols;
         const std::uint64_t y1 = dy1k + ys * kYStage16, y2 = dy2k + ys * kYStage16;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
@@ -142,21 +144,31 @@ __device__ __forceinline__ bool bwd_mma_issuer(unsigned char* smem, const BwdBar
     };
 
     if (!mbar_wait(bars.x_full, 0)) return false;
-    if (!issue_t(0, 0, 0u)) return false;
+    // The T products run kTBufs - 1 tiles ahead of the accumulating products. `ahead` = the next tile whose T products
+    // have not been issued, with its TMEM buffer, ring stage and phase kept as counters (no divisions in this thread).
+    int ahead = 0, ahead_tb = 0, ahead_ys = 0;
+    std::uint32_t ahead_par = 0;
+    auto issue_next_t = [&]() -> bool {
+        if (!issue_t(ahead, ahead_tb, ahead_ys, ahead_par)) return false;
+        ++ahead;
+        if (++ahead_tb == kTBufs) ahead_tb = 0;
+        if (++ahead_ys == L::kStages) { ahead_ys = 0; ahead_par ^= 1u; }
+        return true;
+    };
+    for (int p = 0; p < kTBufs - 1 && p < g.n_it; ++p)
+        if (!issue_next_t()) return false;
     int ys = 0;                  // ring stage of tile `it`
-    std::uint32_t ypar = 0;
+    int tb = 0;                  // its TMEM buffer = it % kTBufs
+    std::uint32_t tpar = 0;      // phase of that buffer's barriers = (it / kTBufs) & 1
     for (int it = 0; it < g.n_it; ++it) {
-        const int s = it & 1;
-        int ys_next = ys + 1;
-        std::uint32_t ypar_next = ypar;
-        if (ys_next == L::kStages) { ys_next = 0; ypar_next ^= 1u; }
-        if (it + 1 < g.n_it && !issue_t(it + 1, ys_next, ypar_next)) return false;
-        if (!mbar_wait(&bars.w_full[s], (it >> 1) & 1)) return false;
+        const int s = tb;
+        if (ahead < g.n_it && !issue_next_t()) return false;
+        if (!mbar_wait(&bars.w_full[s], tpar)) return false;
         bwd_trace(bars, it, 2);
         tc_fence_after_sync();
         const std::uint32_t acc = it > 0 ? 1u : 0u;
         const std::uint64_t y1 = dy1n + ys * kYStage16, y2 = dy2n + ys * kYStage16;
-        const std::uint32_t u_tmem = tmem + s * kCols, w_tmem = tmem + 128 + s * kCols;   // over T1 / T2 of this tile
+        const std::uint32_t u_tmem = tmem + TM::kT1 + s * kCols, w_tmem = tmem + TM::kT2 + s * kCols;   // over T1 / T2 of this tile
 #pragma unroll
         for (int k = 0; k < kCols / 16; ++k) {
             // A: TMEM, lanes = stationary rows, 16 streaming rows (one K step) = 8 packed columns; the two compute
@@ -174,8 +186,8 @@ __device__ __forceinline__ bool bwd_mma_issuer(unsigned char* smem, const BwdBar
             }
         }
         tc_commit(&bars.y_free[ys]);     // the streaming tile's ring stage may be refilled ...
-        ys = ys_next;
-        ypar = ypar_next;
+        if (++ys == L::kStages) ys = 0;
+        if (++tb == kTBufs) { tb = 0; tpar ^= 1u; }
     }
     tc_commit(bars.acc_done);
     return true;

@@ -64,6 +64,23 @@ template <int D> struct BwdSmem {
     static_assert(kAlignSlack >= 0, "attention backward shared memory exceeds the 227 KB a CTA may use");
 };
 
+// TMEM columns of one CTA (512 in all): the T1 / T2 buffers of the tiles in flight, then the accumulators. The MMA
+// thread issues the T products of a tile kTBufs - 1 tiles ahead of the accumulating products; it can only do so
+// while a buffer is free, and a buffer is held from the T products of its tile until the accumulating products
+// have consumed the U / W written over it. With two buffers the thread has to wait for the compute warps' result
+// of tile it before it may issue T(it + 2), so the warps' whole latency per tile (wake-up, TMEM load, exponentials,
+// TMEM store, hand-over) sits in the loop: period = (tensor time + compute latency) / 2. Three buffers, wherever
+// 512 columns allow them (every case but dK/dV at head_dim 128, whose two accumulators take 256), take that latency
+// out of the loop.
+template <int D, int MODE> struct BwdTmem {
+    static constexpr int kAccCols = (MODE == 1 ? 2 : 1) * D;
+    static constexpr int kTBufs = (512 - kAccCols) >= 3 * 2 * kCols ? 3 : 2;
+    static constexpr int kT1 = 0;
+    static constexpr int kT2 = kTBufs * kCols;
+    static constexpr int kAcc = 2 * kTBufs * kCols;
+    static_assert(kAcc + kAccCols <= 512, "TMEM columns");
+};
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

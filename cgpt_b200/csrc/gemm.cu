@@ -193,13 +193,25 @@ column_sum_kernel(T* __restrict__ out, const T* __restrict__ in, long long rows,
 }
 
 #include "gemm_persistent.cuh"
+#include "gemm_pair.cuh"
 #include "gemm_swiglu.cuh"
 
 // C[M,N] (+)= sum_i A_i[M,K_i] * B_i, i < segments (1..kMaxKSegments): one launch, one pass over C.
-template <typename T, int BN, bool A_MN, bool B_MN>
+// Whether the CTA-pair kernel (gemm_pair.cuh) is used where its tile shape applies. Diagnosis builds can switch it off
+// (CGPT_B200_GEMM_PAIR=0) to compare the two kernels.
+inline bool pair_kernel_enabled() {
+    static const bool on = [] { const char* e = diagnosis_env("CGPT_B200_GEMM_PAIR"); return !(e != nullptr && e[0] == '0'); }();
+    return on;
+}
+
+// PAIR: 256 x 256 tiles on CTA pairs (BN must be 256) instead of 128 x BN tiles on single CTAs.
+template <typename T, int BN, bool A_MN, bool B_MN, bool PAIR = false>
 int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int segments, int M, int N, int accumulate, int dtype,
               cudaStream_t s) {
     using Cfg = GemmCfg<BN>;
+    static_assert(!PAIR || BN == kPairBN, "the pair kernel has 256-column tiles");
+    constexpr int kTileM = PAIR ? kPairBM : BM;        // rows of a work unit's tile
+    constexpr int kBoxN = PAIR ? BN / 2 : BN;          // B rows (columns of C) one CTA loads per K block
     GemmOperands ops;
     ops.segments = segments;
     ops.groups = 1;
@@ -219,7 +231,7 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
         const std::uint64_t b_dims_k[2] = {static_cast<std::uint64_t>(Ki), static_cast<std::uint64_t>(N)};
         const std::uint64_t b_dims_n[2] = {static_cast<std::uint64_t>(N), static_cast<std::uint64_t>(Ki)};
         const std::uint64_t b_st_k[1] = {static_cast<std::uint64_t>(Ki) * 2}, b_st_n[1] = {static_cast<std::uint64_t>(N) * 2};
-        const std::uint32_t b_box_k[2] = {BK, BN}, b_box_n[2] = {64, BK};
+        const std::uint32_t b_box_k[2] = {BK, kBoxN}, b_box_n[2] = {64, BK};
         CGPT_TRY(make_tensor_map(&ops.b[i], dtype, Bs[g], 2, B_MN ? b_dims_n : b_dims_k, B_MN ? b_st_n : b_st_k, B_MN ? b_box_n : b_box_k));
         if (i < segments) {
             total_kb += (Ki + BK - 1) / BK;
@@ -228,12 +240,13 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
         ops.kb_end[i] = total_kb;
     }
     const CUtensorMap& ta = ops.a[0];
-    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-    // Split K when the output tiles alone leave most SMs idle and K is long enough to amortise it.
+    const int tiles_m = (M + kTileM - 1) / kTileM, tiles_n = (N + BN - 1) / BN;
+    // Split K when the output tiles alone leave most SMs (pairs) idle and K is long enough to amortise it.
+    constexpr int kWorkers = PAIR ? kNumSMs / 2 : kNumSMs;
     int splits = 1;
     const int tiles = tiles_m * tiles_n;
-    if (tiles < kNumSMs) {
-        splits = kNumSMs / tiles;
+    if (tiles < kWorkers) {
+        splits = kWorkers / tiles;
         const int max_by_k = total_kb / 8 > 0 ? total_kb / 8 : 1;   // at least 8 K blocks (512) per split
         if (splits > max_by_k) splits = max_by_k;
         if (splits > 32) splits = 32;
@@ -247,10 +260,17 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
         CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(splits) * M * N * sizeof(float), s));
         partial = static_cast<float*>(scratch);
     }
-    auto pkernel = gemm_tcgen05_persistent_kernel<T, BN, A_MN, B_MN>;
+    void (*pkernel)(GemmOperands, GemmOutputs, T*, float*, int, int, int, int, int, int, int, int) = nullptr;
+    int smem_bytes = Cfg::kSmemBytes;
+    if constexpr (PAIR) {
+        pkernel = gemm_tcgen05_pair_kernel<T, A_MN, B_MN>;
+        smem_bytes = PairCfg::kSmemBytes;
+    } else {
+        pkernel = gemm_tcgen05_persistent_kernel<T, BN, A_MN, B_MN>;
+    }
     static PerDeviceOnce attr_once;
     if (attr_once.needed()) {
-        CGPT_CUDA_TRY(cudaFuncSetAttribute(pkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        CGPT_CUDA_TRY(cudaFuncSetAttribute(pkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         attr_once.done();
     }
     int epi = splits > 1 ? kEpiPartial : (accumulate ? kEpiAccumulate : kEpiStore);
@@ -262,7 +282,11 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
     if (timed) CGPT_CUDA_TRY(cudaEventRecord(g_timing.events[g_timing.used], s));
     {
         const long long units = static_cast<long long>(tiles) * splits;
-        const unsigned grid = static_cast<unsigned>(units < kNumSMs ? units : kNumSMs);
+        unsigned grid = static_cast<unsigned>(units < kNumSMs ? units : kNumSMs);
+        if (PAIR) {
+            grid = static_cast<unsigned>(pair_grid(reinterpret_cast<const void*>(pkernel), static_cast<int>(units < kNumSMs ? units : kNumSMs)));
+            if (grid == 0) return CGPT_ERR_UNSUPPORTED;   // clusters of 2 cannot be scheduled here: the caller takes the single-CTA kernel
+        }
         // Plain stores of 16-bit output go through shared memory and TMA (needs a 16-byte aligned C and N % 8 == 0).
         GemmOutputs outs;
         outs.c[0] = outs.c[1] = outs.c[2] = ta;      // placeholders: only read by the TMA-store epilogue
@@ -276,11 +300,11 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
             // diagnosis builds only: CGPT_B200_GEMM_NOSTORE=2 stages the tile in shared memory but never issues the TMA store
             // and =3 issues every TMA store to the first 16 KB of C (same store mechanics, no memory-system load)
             static const int diag = [] { const char* e = diagnosis_env("CGPT_B200_GEMM_NOSTORE"); return e ? std::atoi(e) : 0; }();
-            if (diag == 2) epi = kEpiStageOnly;
-            if (diag == 3) epi = kEpiStoreTmaFixed;
+            if (!PAIR && diag == 2) epi = kEpiStageOnly;
+            if (!PAIR && diag == 3) epi = kEpiStoreTmaFixed;
         }
         outs.c[1] = outs.c[2] = outs.c[0];
-        pkernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ops, outs, C, partial, M, N, total_kb, tiles_m, tiles_n, splits, kb_per_split, epi);
+        pkernel<<<grid, kGemmThreads, smem_bytes, s>>>(ops, outs, C, partial, M, N, total_kb, tiles_m, tiles_n, splits, kb_per_split, epi);
     }
     count_launch();
     CGPT_LAUNCH_CHECK();
@@ -307,10 +331,19 @@ int launch_tc_layout(T* C, const T* const* A, const T* const* B, const int* K, i
     // 128x256 tiles whenever N allows: a 128x128 tile needs as many shared-memory operand bytes per MMA as the
     // tensor core can consume, 128x256 needs 3/4 of that per FLOP. Few tiles are compensated by split-K.
     const bool wide = N >= 256;
+    // 256 x 256 tiles on CTA pairs when both dimensions allow them (two thirds of the shared-memory traffic per FLOP)
+    // Measured on the training shapes: +1..4 % on the forward and dX products, +11 % on the LM-head logits, but -15 % on
+    // the weight-gradient products (both operands MN-major, K = tokens, split-K), which therefore stay on single CTAs.
+    const bool pair = wide && M >= kPairBM && a_mn == 0 && pair_kernel_enabled();
 #define CGPT_GEMM_CASE(AM, BMN)                                                                  \
-    if (a_mn == AM && b_mn == BMN)                                                               \
+    if (a_mn == AM && b_mn == BMN) {                                                             \
+        if (pair) {                                                                              \
+            const int rc = launch_tc<T, 256, AM != 0, BMN != 0, true>(C, A, B, K, segments, M, N, accumulate, dtype, s); \
+            if (rc != CGPT_ERR_UNSUPPORTED) return rc;                                           \
+        }                                                                                        \
         return wide ? launch_tc<T, 256, AM != 0, BMN != 0>(C, A, B, K, segments, M, N, accumulate, dtype, s) \
-                    : launch_tc<T, 128, AM != 0, BMN != 0>(C, A, B, K, segments, M, N, accumulate, dtype, s);
+                    : launch_tc<T, 128, AM != 0, BMN != 0>(C, A, B, K, segments, M, N, accumulate, dtype, s); \
+    }
     CGPT_GEMM_CASE(0, 0)
     CGPT_GEMM_CASE(0, 1)
     CGPT_GEMM_CASE(1, 1)
@@ -322,11 +355,14 @@ int launch_tc_layout(T* C, const T* const* A, const T* const* B, const int* K, i
 // Y_g[M, N_g] = A[M, K] * B_g[N_g, K]^T for up to three outputs that share A, as ONE launch: the N tiles of all groups
 // form one work list (better wave quantisation than three launches, A read through L2 by neighbouring CTAs).
 // Tensor-core path only (16-bit, aligned, N_g % 8 == 0); returns CGPT_ERR_UNSUPPORTED otherwise.
-template <typename T>
+template <typename T, bool PAIR = false>
 int launch_tc_groups(T* const* Cs, const T* A, const T* const* Bs, const int* Ns, int groups, int M, int K, int dtype, cudaStream_t s) {
     constexpr int BN = 256;
     using Cfg = GemmCfg<BN>;
+    constexpr int kTileM = PAIR ? kPairBM : BM;
+    constexpr int kWorkers = PAIR ? kNumSMs / 2 : kNumSMs;
     if (groups < 1 || groups > kMaxKSegments || !aligned16(A) || K % 8 != 0 || K < 32) return CGPT_ERR_UNSUPPORTED;
+    if (PAIR && M < kPairBM) return CGPT_ERR_UNSUPPORTED;
     GemmOperands ops;
     GemmOutputs outs;
     ops.segments = 1;
@@ -334,7 +370,7 @@ int launch_tc_groups(T* const* Cs, const T* A, const T* const* Bs, const int* Ns
     ops.group_dim = 0;
     const std::uint64_t a_dims[2] = {static_cast<std::uint64_t>(K), static_cast<std::uint64_t>(M)};
     const std::uint64_t k_st[1] = {static_cast<std::uint64_t>(K) * 2};
-    const std::uint32_t a_box[2] = {BK, BM}, b_box[2] = {BK, BN}, c_box[2] = {64, BM};
+    const std::uint32_t a_box[2] = {BK, BM}, b_box[2] = {BK, PAIR ? BN / 2 : BN}, c_box[2] = {64, BM};
     int tiles_n = 0;
     double flops = 0.0;
     for (int i = 0; i < kMaxKSegments; ++i) {
@@ -353,19 +389,31 @@ int launch_tc_groups(T* const* Cs, const T* A, const T* const* Bs, const int* Ns
         ops.tile_end[i] = tiles_n;
         ops.kb_end[i] = (K + BK - 1) / BK;
     }
-    const int tiles_m = (M + BM - 1) / BM;
+    const int tiles_m = (M + kTileM - 1) / kTileM;
     const long long units = static_cast<long long>(tiles_m) * tiles_n;
-    if (units < kNumSMs) return CGPT_ERR_UNSUPPORTED;   // too small to be worth it: no split-K in this form
-    auto pkernel = gemm_tcgen05_persistent_kernel<T, BN, false, false>;
+    if (units < kWorkers) return CGPT_ERR_UNSUPPORTED;   // too small to be worth it: no split-K in this form
+    void (*pkernel)(GemmOperands, GemmOutputs, T*, float*, int, int, int, int, int, int, int, int) = nullptr;
+    int smem_bytes = Cfg::kSmemBytes;
+    unsigned grid = kNumSMs;
+    if constexpr (PAIR) {
+        pkernel = gemm_tcgen05_pair_kernel<T, false, false>;
+        smem_bytes = PairCfg::kSmemBytes;
+    } else {
+        pkernel = gemm_tcgen05_persistent_kernel<T, BN, false, false>;
+    }
     static PerDeviceOnce attr_once;
     if (attr_once.needed()) {
-        CGPT_CUDA_TRY(cudaFuncSetAttribute(pkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        CGPT_CUDA_TRY(cudaFuncSetAttribute(pkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         attr_once.done();
+    }
+    if (PAIR) {
+        grid = static_cast<unsigned>(pair_grid(reinterpret_cast<const void*>(pkernel), kNumSMs));
+        if (grid == 0) return CGPT_ERR_UNSUPPORTED;
     }
     const bool timed = g_timing.enabled && g_timing.used + 2 <= g_timing.events.size();
     if (timed) CGPT_CUDA_TRY(cudaEventRecord(g_timing.events[g_timing.used], s));
-    pkernel<<<kNumSMs, kGemmThreads, Cfg::kSmemBytes, s>>>(ops, outs, Cs[0], nullptr, M, Ns[0], (K + BK - 1) / BK, tiles_m, tiles_n, 1,
-                                                          (K + BK - 1) / BK, kEpiStoreTma);
+    pkernel<<<grid, kGemmThreads, smem_bytes, s>>>(ops, outs, Cs[0], nullptr, M, Ns[0], (K + BK - 1) / BK, tiles_m, tiles_n, 1,
+                                                  (K + BK - 1) / BK, kEpiStoreTma);
     count_launch();
     CGPT_LAUNCH_CHECK();
     if (timed) {
@@ -379,11 +427,13 @@ int launch_tc_groups(T* const* Cs, const T* A, const T* const* Bs, const int* Ns
 // dW_g[M_g, N] (+)= dY_g[K, M_g]^T X[K, N] for up to three weight gradients that share X, as ONE launch: the M tiles of
 // all groups form one work list (both operands MN-major, K = tokens). With few tiles K is split as in the plain
 // launcher: fp32 partials [split][sum of padded M_g][N], then one fixed-order reduce per group.
-template <typename T>
+template <typename T, bool PAIR = false>
 int launch_tc_mgroups(T* const* Cs, const T* const* As, const T* B, const int* Ms, int groups, int N, int K, int accumulate,
                       int dtype, cudaStream_t s) {
     constexpr int BN = 256;
     using Cfg = GemmCfg<BN>;
+    constexpr int kTileM = PAIR ? kPairBM : BM;
+    constexpr int kWorkers = PAIR ? kNumSMs / 2 : kNumSMs;
     if (groups < 1 || groups > kMaxKSegments || !aligned16(B) || N % 8 != 0 || N < BN || K < 32) return CGPT_ERR_UNSUPPORTED;
     GemmOperands ops;
     GemmOutputs outs;
@@ -405,9 +455,10 @@ int launch_tc_mgroups(T* const* Cs, const T* const* As, const T* B, const int* M
         CGPT_TRY(make_tensor_map(&ops.b[i], dtype, B, 2, b_dims, b_st, mn_box));
         const std::uint64_t c_dims[2] = {static_cast<std::uint64_t>(N), static_cast<std::uint64_t>(Ms[g])};
         CGPT_TRY(make_tensor_map(&outs.c[i], dtype, Cs[g], 2, c_dims, b_st, c_box));
+        if (PAIR && Ms[g] < kPairBM) return CGPT_ERR_UNSUPPORTED;
         if (i < groups) {
-            m_first[i] = tiles_m * BM;
-            tiles_m += (Ms[g] + BM - 1) / BM;
+            m_first[i] = tiles_m * kTileM;
+            tiles_m += (Ms[g] + kTileM - 1) / kTileM;
             flops += 2.0 * Ms[g] * N * K;
         }
         ops.tile_end[i] = tiles_m;
@@ -417,8 +468,8 @@ int launch_tc_mgroups(T* const* Cs, const T* const* As, const T* B, const int* M
     const int total_kb = (K + BK - 1) / BK;
     const int tiles = tiles_m * tiles_n;
     int splits = 1;
-    if (tiles < kNumSMs) {
-        splits = kNumSMs / tiles;
+    if (tiles < kWorkers) {
+        splits = kWorkers / tiles;
         const int max_by_k = total_kb / 8 > 0 ? total_kb / 8 : 1;
         if (splits > max_by_k) splits = max_by_k;
         if (splits > 32) splits = 32;
@@ -428,25 +479,36 @@ int launch_tc_mgroups(T* const* Cs, const T* const* As, const T* B, const int* M
     if (accumulate && splits == 1) return CGPT_ERR_UNSUPPORTED;
     const int kb_per_split = (total_kb + splits - 1) / splits;
     splits = (total_kb + kb_per_split - 1) / kb_per_split;
-    const int m_pad = tiles_m * BM;
+    const int m_pad = tiles_m * kTileM;
     float* partial = nullptr;
     if (splits > 1) {
         void* scratch = nullptr;
         CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(splits) * m_pad * N * sizeof(float), s));
         partial = static_cast<float*>(scratch);
     }
-    auto pkernel = gemm_tcgen05_persistent_kernel<T, BN, true, true>;
+    void (*pkernel)(GemmOperands, GemmOutputs, T*, float*, int, int, int, int, int, int, int, int) = nullptr;
+    int smem_bytes = Cfg::kSmemBytes;
+    if constexpr (PAIR) {
+        pkernel = gemm_tcgen05_pair_kernel<T, true, true>;
+        smem_bytes = PairCfg::kSmemBytes;
+    } else {
+        pkernel = gemm_tcgen05_persistent_kernel<T, BN, true, true>;
+    }
     static PerDeviceOnce attr_once;
     if (attr_once.needed()) {
-        CGPT_CUDA_TRY(cudaFuncSetAttribute(pkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        CGPT_CUDA_TRY(cudaFuncSetAttribute(pkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         attr_once.done();
     }
     const long long units = static_cast<long long>(tiles) * splits;
-    const unsigned grid = static_cast<unsigned>(units < kNumSMs ? units : kNumSMs);
+    unsigned grid = static_cast<unsigned>(units < kNumSMs ? units : kNumSMs);
+    if (PAIR) {
+        grid = static_cast<unsigned>(pair_grid(reinterpret_cast<const void*>(pkernel), static_cast<int>(units < kNumSMs ? units : kNumSMs)));
+        if (grid == 0) return CGPT_ERR_UNSUPPORTED;
+    }
     const bool timed = g_timing.enabled && g_timing.used + 2 <= g_timing.events.size();
     if (timed) CGPT_CUDA_TRY(cudaEventRecord(g_timing.events[g_timing.used], s));
-    pkernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ops, outs, Cs[0], partial, m_pad, N, total_kb, tiles_m, tiles_n, splits,
-                                                       kb_per_split, splits > 1 ? kEpiPartial : kEpiStoreTma);
+    pkernel<<<grid, kGemmThreads, smem_bytes, s>>>(ops, outs, Cs[0], partial, m_pad, N, total_kb, tiles_m, tiles_n, splits,
+                                                  kb_per_split, splits > 1 ? kEpiPartial : kEpiStoreTma);
     count_launch();
     CGPT_LAUNCH_CHECK();
     if (timed) {
@@ -621,6 +683,17 @@ extern "C" int cgpt_linear_forward_fused(void* const* y, const void* x, const vo
     }
     if (rows == 0 || in_features == 0 || rows > 0x7fffffffull || in_features > 0x7fffffffull) return CGPT_ERR_SHAPE;
     int rc = CGPT_ERR_UNSUPPORTED;
+    if (pair_kernel_enabled()) {   // 256 x 256 tiles on CTA pairs where the shapes allow them
+        if (dtype == CGPT_DTYPE_F16)
+            rc = launch_tc_groups<__half, true>(reinterpret_cast<__half* const*>(y), static_cast<const __half*>(x),
+                                                reinterpret_cast<const __half* const*>(w), ns, static_cast<int>(count), static_cast<int>(rows),
+                                                static_cast<int>(in_features), dtype, s);
+        else if (dtype == CGPT_DTYPE_BF16)
+            rc = launch_tc_groups<__nv_bfloat16, true>(reinterpret_cast<__nv_bfloat16* const*>(y), static_cast<const __nv_bfloat16*>(x),
+                                                       reinterpret_cast<const __nv_bfloat16* const*>(w), ns, static_cast<int>(count),
+                                                       static_cast<int>(rows), static_cast<int>(in_features), dtype, s);
+        if (rc != CGPT_ERR_UNSUPPORTED) return rc;
+    }
     if (dtype == CGPT_DTYPE_F16)
         rc = launch_tc_groups<__half>(reinterpret_cast<__half* const*>(y), static_cast<const __half*>(x),
                                       reinterpret_cast<const __half* const*>(w), ns, static_cast<int>(count), static_cast<int>(rows),

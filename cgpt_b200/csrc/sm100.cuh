@@ -134,6 +134,62 @@ __device__ __forceinline__ void mma_f16_ts(std::uint32_t d_tmem, std::uint32_t a
         : "memory");
 }
 
+// ------------------------------------------------------------------------ CTA pairs (cta_group::2)
+// Two CTAs of a cluster of 2 (ranks 0 and 1, on the two SMs of one TPC) run ONE tcgen05.mma per K step: M = 256 rows
+// (128 per CTA, each CTA's own A tile and TMEM accumulator), N up to 256 with each CTA holding HALF of the B tile in
+// its own shared memory. The leader (rank 0) issues the MMA for both; barriers are addressed across the pair through
+// shared::cluster addresses (mapa). Per FLOP each SM then reads and fills two thirds of the shared-memory bytes a
+// single-CTA 128 x 256 tile needs. No load is multicast: every CTA issues the TMA loads of the bytes it keeps.
+__device__ __forceinline__ std::uint32_t cluster_ctarank() {
+    std::uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared-memory offset in the CTA of rank `rank`
+__device__ __forceinline__ std::uint32_t mapa_shared(std::uint32_t local_addr, std::uint32_t rank) {
+    std::uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+// Every thread of both CTAs. Not the .aligned form: the lanes of a warp reach it at different times (lane 0 of the
+// producer and MMA warps runs a loop the other lanes skip).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(std::uint32_t cluster_addr) {   // arrive on a barrier of either CTA
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load into THIS CTA's shared memory whose completion bytes are counted on a barrier of either CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* tmap, std::uint32_t bar_cluster_addr, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<std::uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(std::uint32_t* smem_result, std::uint32_t columns) {  // one warp of EACH CTA
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(std::uint32_t taddr, std::uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
+}
+// D[tmem of both CTAs] (+)= A * B over the pair; issued by one thread of the leader CTA.
+__device__ __forceinline__ void mma_f16_ss_pair(std::uint32_t d_tmem, std::uint64_t a_desc, std::uint64_t b_desc,
+                                                std::uint32_t idesc, std::uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The barrier (of either CTA, shared::cluster address) gets one arrival once every pair MMA issued so far has completed.
+__device__ __forceinline__ void tc_commit_pair(std::uint32_t bar_cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
 // Shared-memory operand descriptor, 128-byte swizzle. The tile must start on a 1024-byte boundary
 // (descriptors for later K steps may add to the start address inside the tile).
 //   K-major  tile [rows][64 x 16-bit]: rows 128 B apart, 8-row groups `sbo` = 1024 B apart; lbo unused.

@@ -191,6 +191,16 @@ class TrainStep:
             done.record(self.stream)
         return PendingLoss(host, done)
 
+    def close(self) -> None:
+        """Drains the step's stream and releases the captured graph. With more than one rank the graph holds NCCL kernels
+        and the events of the collectives captured into it: call this before the process group is destroyed, or the
+        group's shutdown waits on work that only exists inside the graph."""
+        self.stream.synchronize()
+        if self.graph is not None:
+            self.graph.reset()
+            self.graph = None
+        self._keep = None
+
     def check(self) -> bool:
         """Synchronises the step's stream, refreshes the host-side step counters of the optimizer states and returns
         False if a step since the last check was skipped for non-finite gradients. Raises if a tensor-core kernel's

@@ -45,7 +45,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--model", default="small", help="preset: 104m, small, tiny, 1.3b")
     p.add_argument("--validation-fraction", type=float, default=0.1)
     p.add_argument("--save-avg-loss", action="store_true")
-    p.add_argument("--checkpoint-interval", type=int, default=0, help="also write a checkpoint every N steps (0 = only at the end)")
+    p.add_argument("--checkpoint-interval", type=int, default=0, help="also write a checkpoint to <output-dir>/step-N every N steps (0 = only at the end)")
     p.add_argument("--overlap-allreduce", action=argparse.BooleanOptionalAction, default=True,
                    help="ranks > 1: start each gradient bucket's all-reduce during the backward, inside the captured graph "
                         "(--no-overlap-allreduce: all buckets after the backward)")
@@ -186,15 +186,16 @@ def main(argv=None) -> int:
             mean /= world
         return float(mean.item())
 
-    def save(step: int) -> None:
+    def save(step: int, directory: str | None = None) -> None:
         # The step just enqueued (graph replay, all-reduce, AdamW) runs on ts.stream while the copies below run on torch's
         # current stream: drain the step first, on every rank, and let check() refresh the optimizer's host-side step
         # counters, which the checkpoint stores (they are otherwise only refreshed at the logging points).
         ts.stream.synchronize()
         ts.check()
         if rank == 0:
-            checkpoint.save_model(args.output_dir, ts.storage)
-            checkpoint.save_optimizer(args.output_dir, ts.storage, ts.states, {"step": step})
+            directory = directory or args.output_dir
+            checkpoint.save_model(directory, ts.storage)
+            checkpoint.save_optimizer(directory, ts.storage, ts.states, {"step": step})
 
     loss_log = None
     if args.save_avg_loss and rank == 0:
@@ -232,10 +233,11 @@ def main(argv=None) -> int:
             if step % args.validation_interval == 0 or step == total_steps:
                 log(f"step {step}: validation loss {validate():.4f}")
             if args.checkpoint_interval and step % args.checkpoint_interval == 0 and step < total_steps:
-                save(step)
+                save(step, os.path.join(args.output_dir, f"step-{step}"))   # train/train.cpp:493-526 exports to <output>/step-N
     save(step)
     if loss_log is not None:
         loss_log.close()
+    ts.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -201,34 +201,53 @@ def test_tiny_model_one_adamw_step_against_reference_cuda(M, gradients, max_grad
 
 
 def test_loss_after_50_identical_steps_against_reference_loop(M):
-    """50 optimizer steps on one fixed batch of the tiny model: the library's step (CUDA graph replay + AdamW) against the
-    reference's loop (its CudaGraph replay of forward + cross-entropy + backward, then adamw_step_many_async with the
-    trainer's options: betas 0.9/0.95, wd 0.1, global-norm clip 1.0, loss scale 1024, constant lr 3e-4)."""
+    """50 optimizer steps on one fixed batch of the tiny model: the library's step (one CUDA graph: forward, loss, backward,
+    AdamW) against the reference's loop (its CudaGraph replay of forward + cross-entropy + backward, then
+    adamw_step_many_async with the trainer's options: betas 0.9/0.95, wd 0.1, global-norm clip 1.0, loss scale 1024,
+    constant lr 3e-4). Bar: 1e-3 absolute on the loss.
+
+    The reference's loop is not reproducible: it accumulates embedding rows, dK/dV (head_dim 64) and the gradient norm with
+    atomics in arrival order, and on a repeated batch the loss falls from 10.4 to about 2 in these 50 steps, so rounding-level
+    differences grow. Two instances of the reference therefore run side by side from the same weights: the library (whose
+    own trajectory is bit-reproducible) has to stay within the bar of one of them, or within 1.5 times the distance the two
+    reference runs have drifted apart from each other; over the first 20 steps, before that drift matters, the bar holds
+    against both."""
     from cgpt_b200 import optim
     o = M.preset("tiny")
     batch, seq, steps, lr = 2, 128, 50, 3e-4
     adam = optim.AdamWOptions(lr, 0.9, 0.95, 1e-8, 0.1, LOSS_SCALE, 1.0)
-    ts, ref = make_pair(M, o, batch, seq, adam, use_graph=True)
+    ts, ref_a = make_pair(M, o, batch, seq, adam, use_graph=True)
+    b = o.block_options
+    ref_b = R.RefModel(o.vocabulary_size, o.num_layers, b.hidden_size, b.intermediate_size, b.num_query_heads, b.num_kv_heads,
+                       b.head_dim, b.rotary_dim or b.head_dim, b.rms_epsilon, batch, seq, ts.cos, ts.sin)
+    ref_b.init(0)
     set_batch(ts, o, batch, seq, seed=7)
-    lib_losses, ref_losses = [], []
+    lib, ra, rb = [], [], []
     stream = torch.cuda.Stream()
     for _ in range(steps):
         ts.step(lr)
-        lib_losses.append(ts.read_loss())
+        lib.append(ts.read_loss())
         with torch.cuda.stream(stream):
-            ref.step(ts.token_ids, ts.targets, LOSS_SCALE, graph=True)
-            ref.adamw(lr, 0.9, 0.95, 1e-8, 0.1, LOSS_SCALE, 1.0)
-            ref_losses.append(ref.loss())
+            for ref, out in ((ref_a, ra), (ref_b, rb)):
+                ref.step(ts.token_ids, ts.targets, LOSS_SCALE, graph=True)
+                ref.adamw(lr, 0.9, 0.95, 1e-8, 0.1, LOSS_SCALE, 1.0)
+                out.append(ref.loss())
     assert ts.check()
     with torch.cuda.stream(stream):
-        ok, step = ref.check()
-    assert ok and step == steps
-    print("loss trajectory (library / reference):", [(round(a, 4), round(b, 4)) for a, b in list(zip(lib_losses, ref_losses))[::7]])
-    assert lib_losses[-1] < lib_losses[0] - 0.5, "the loss must fall on a repeated batch"
-    worst = max(abs(a - b) for a, b in zip(lib_losses, ref_losses))
-    print(f"largest loss difference over {steps} steps: {worst:.2e}; after the last step: {abs(lib_losses[-1] - ref_losses[-1]):.2e}")
-    assert abs(lib_losses[-1] - ref_losses[-1]) <= 1e-3, (lib_losses[-1], ref_losses[-1])
-    ref.close()
+        for ref in (ref_a, ref_b):
+            ok, step = ref.check()
+            assert ok and step == steps
+    print("loss trajectory (library / reference run 1 / reference run 2):",
+          [(round(x, 4), round(y, 4), round(z, 4)) for x, y, z in list(zip(lib, ra, rb))[::7]])
+    assert lib[-1] < lib[0] - 0.5, "the loss must fall on a repeated batch"
+    early = max(max(abs(x - y), abs(x - z)) for x, y, z in list(zip(lib, ra, rb))[:20])
+    drift = abs(ra[-1] - rb[-1])
+    dist = min(abs(lib[-1] - ra[-1]), abs(lib[-1] - rb[-1]))
+    print(f"first 20 steps: largest |library - reference| {early:.2e}; after step {steps}: |library - nearest reference run| {dist:.2e}, "
+          f"|reference run 1 - reference run 2| {drift:.2e}")
+    assert early <= 1e-3, early
+    assert dist <= max(1e-3, 1.5 * drift), (lib[-1], ra[-1], rb[-1])
+    ref_a.close(); ref_b.close()
 
 
 def test_full_size_104m_layer_against_reference_cuda_block(M):

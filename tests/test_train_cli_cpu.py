@@ -105,3 +105,22 @@ def test_presets_have_the_documented_sizes():
     assert profiling.model_flops_per_token(o) + profiling.attention_flops_per_token(o, 1024) == 683_147_264
     with pytest.raises(ValueError):
         M.preset("no-such-model")
+
+
+def test_learning_rate_schedule_matches_reference_header():
+    """LearningRateScheduler.learning_rate() against values produced by the reference's own header-only scheduler
+    (include/optim/lr_scheduler.h:37-51; fixture generated by tests/golden/make_lr_golden.py): warm-up, cosine part, the
+    last step (exactly the minimum) and steps past the end."""
+    import json
+    from pathlib import Path
+    from cgpt_b200.optim import LearningRateScheduler, LearningRateSchedulerOptions
+    cases = json.loads((Path(__file__).parent / "golden" / "lr_schedule.json").read_text())
+    assert len(cases) >= 5
+    for c in cases:
+        s = LearningRateScheduler(LearningRateSchedulerOptions(c["initial"], c["minimum"], c["warmup"], c["total"]))
+        for step, want in zip(c["steps"], c["values"]):
+            got = s.learning_rate(step)
+            assert abs(got - want) <= 2e-7 * max(abs(want), c["initial"]), (c, step, got, want)
+        # the last step returns the minimum itself, not a value of the cosine (the fixture holds it as fp32)
+        assert s.learning_rate(c["total"] - 1) == c["minimum"]
+        assert np.float32(c["minimum"]) == np.float32(c["values"][c["steps"].index(c["total"] - 1)])

@@ -83,3 +83,32 @@ def test_asynchronous_loss_read_equals_synchronous_read():
         return out
 
     assert run(True) == run(False)
+
+
+def test_mid_run_checkpoint_resumes_to_the_same_weights(tmp_path, capsys):
+    """--checkpoint-interval writes <output>/step-N while later steps are already enqueued on the step's stream. A run that
+    resumes from a checkpoint taken at a step that is no logging point (13) must end with exactly the weights and
+    optimizer state of the uninterrupted run: the checkpoint holds a consistent state (step drained before the copies,
+    step counter refreshed) and the resumed run continues the epoch where the saved one stopped."""
+    from cgpt_b200 import train_cli
+    from safetensors import safe_open
+    tokens = np.random.default_rng(5).integers(0, 200, 40000).astype(np.int32)
+    path = str(tmp_path / "tokens.npy")
+    np.save(path, tokens)
+    out_a, out_b = str(tmp_path / "a"), str(tmp_path / "b")
+    common = ["--input", path, "--model", "tiny", "--vocab-size", "256", "--batch-size", "4", "--sequence-length", "64",
+              "--validation-interval", "100", "--validation-batches", "1", "--learning-rate", "1e-3", "--min-learning-rate", "1e-4",
+              "--max-steps", "30", "--epochs", "3"]
+    assert train_cli.main(common + ["--checkpoint-interval", "13", "--output-dir", out_a]) == 0
+    capsys.readouterr()
+    mid = os.path.join(out_a, "step-13")
+    assert os.path.exists(os.path.join(mid, "optimizer.safetensors"))
+    with safe_open(os.path.join(mid, "optimizer.safetensors"), framework="pt") as f:
+        assert '"step": 13' in f.metadata()["extra"]
+    assert train_cli.main(common + ["--load-dir", mid, "--output-dir", out_b]) == 0
+    assert "resuming at step 13" in capsys.readouterr().out
+    for name in ("model.safetensors", "optimizer.safetensors"):
+        with safe_open(os.path.join(out_a, name), framework="pt") as fa, safe_open(os.path.join(out_b, name), framework="pt") as fb:
+            assert sorted(fa.keys()) == sorted(fb.keys())
+            for k in fa.keys():
+                assert torch.equal(fa.get_tensor(k), fb.get_tensor(k)), f"{name}:{k} differs between the resumed and the uninterrupted run"
