@@ -37,6 +37,10 @@ def time_gemms(train_step, steps: int = 2) -> dict:
     reducer, ts._reducer = getattr(ts, "_reducer", None), None    # this pass runs on one rank only: no collectives
     try:
         with torch.cuda.stream(ts.stream):
+            # Head start for the host: the event pairs bracket GPU time, and a launch the host has not submitted yet when
+            # the GPU reaches its first event would put the GPU's wait for the host inside the bracket. 40 ms of spinning
+            # on the stream lets the host enqueue the whole pass before the GPU starts it.
+            torch.cuda._sleep(int(0.040 * 1.9e9))
             for _ in range(steps):
                 ts.enqueue_model_step()
         ts.stream.synchronize()
