@@ -117,3 +117,34 @@ def test_many_tensors_against_oracle(optim, dt, max_norm):
             np.testing.assert_allclose(host(s.first_moment), m, rtol=1e-5, atol=1e-9)
             np.testing.assert_allclose(host(s.second_moment), v, rtol=1e-5, atol=1e-12)
             assert np.max(np.abs(host(p) - O.rnd(got, dt))) == 0.0, "param must be the rounded master"
+
+
+def test_learning_rate_from_device_scalar_equals_host_value(optim):
+    """cgpt_adamw_step_device_lr: the update reads the learning rate from a device scalar when it runs (the form that sits
+    inside a captured graph while a schedule changes the rate). Three steps with three rates written to the scalar must
+    give bit-identical parameters, master weights and moments to three steps that pass the same rates by value."""
+    torch.manual_seed(3)
+    sizes = [1000, 4096 * 3 + 5, 257]
+    rates = [3e-4, 2.5e-4, 1e-5]
+    results = []
+    for device_lr in (False, True):
+        ps = [(torch.randn(n, device="cuda") * 0.02).half() for n in sizes]
+        gs = [torch.randn(n, device="cuda").half() for n in sizes]
+        torch.manual_seed(3)      # same tensors in both passes
+        sts = [optim.AdamWState.for_parameter(p) for p in ps]
+        ws = optim.AdamWWorkspace()
+        ent = [optim.AdamWBatchEntry(p, g, s) for p, g, s in zip(ps, gs, sts)]
+        scalar = torch.zeros(1, device="cuda")
+        for lr in rates:
+            o = optim.AdamWOptions(lr if not device_lr else 123.0, 0.9, 0.95, 1e-8, 0.1, 8.0, 1.0)
+            if device_lr:
+                scalar.fill_(lr)
+                optim.adamw_step_many_async(ent, o, ws, learning_rate_device=scalar)
+            else:
+                optim.adamw_step_many_async(ent, o, ws)
+        assert optim.adamw_check(ws) and sts[0].step == 3
+        results.append([t.clone() for p, s in zip(ps, sts) for t in (p, s.master_parameter, s.first_moment, s.second_moment)])
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+    with pytest.raises(Exception):
+        optim.adamw_step_many_async(ent, o, ws, learning_rate_device=torch.zeros(2, device="cuda"))
