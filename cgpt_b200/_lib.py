@@ -90,6 +90,7 @@ _pBP, _pBS, _pMC, _pMT, _pMS = (C.POINTER(BlockParams), C.POINTER(BlockSaved), C
 
 SIGNATURES = {
     "cgpt_cut_cross_entropy": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _f, _i, _sz, _i, _vp]),
+    "cgpt_cut_cross_entropy_form": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _f, _i, _sz, _i, _vp]),
     "cgpt_block_workspace_bytes": (_sz, [_pMC, _sz, _sz]),
     "cgpt_block_forward": (_i, [_vp, _vp, _pBP, _pBS, _vp, _vp, _vp, _pMC, _sz, _sz, _sz, _vp]),
     "cgpt_block_backward": (_i, [_vp, _vp, _vp, _pBP, _pBP, _pBS, _vp, _vp, _vp, _pMC, _sz, _sz, _sz, _vp]),

@@ -245,6 +245,13 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// exp as the reference's fast-math build computes __expf: ex2.approx.ftz(x * log2 e).
+__device__ __forceinline__ float fast_exp(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
+    return y;
+}
+
 // Dispatch a lambda-like macro body over the storage dtype.
 #define CGPT_DISPATCH_DTYPE(dtype, T, ...)                       \
     switch (dtype) {                                             \

@@ -158,7 +158,40 @@ int ce_launch(float* row_loss, void* grad, const void* logits, const std::uint32
 }
 
 #include "cross_entropy_ring.cuh"
+#include "cross_entropy_tiles.cuh"
 }  // namespace
+
+int softmax_grad_rows(float* row_loss, void* logits_to_grad, const float2* partial, const float* target_logit,
+                      const std::uint32_t* targets, long long rows, long long vocab, int tiles, float inv_total_rows,
+                      float gradient_scale, int dtype, cudaStream_t s) {
+    if (dtype != CGPT_DTYPE_F16 && dtype != CGPT_DTYPE_BF16) return CGPT_ERR_UNSUPPORTED;
+    if (vocab % 8 != 0 || !aligned16(logits_to_grad) || vocab > 0x7fffffffll || tiles < 1) return CGPT_ERR_UNSUPPORTED;
+    const unsigned grid = static_cast<unsigned>(rows < kNumSMs * 8ll ? rows : kNumSMs * 8ll);
+    if (dtype == CGPT_DTYPE_F16)
+        softmax_grad_rows_kernel<__half><<<grid, kTileGradThreads, 0, s>>>(row_loss, static_cast<__half*>(logits_to_grad), partial,
+                                                                          target_logit, targets, rows, static_cast<int>(vocab), tiles,
+                                                                          inv_total_rows, gradient_scale);
+    else
+        softmax_grad_rows_kernel<__nv_bfloat16><<<grid, kTileGradThreads, 0, s>>>(row_loss, static_cast<__nv_bfloat16*>(logits_to_grad),
+                                                                                 partial, target_logit, targets, rows,
+                                                                                 static_cast<int>(vocab), tiles, inv_total_rows,
+                                                                                 gradient_scale);
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+    return CGPT_OK;
+}
+
+int softmax_stats_reduce(float2* row_stats, float* row_loss, const float2* partial, const float* target_logit,
+                         const std::uint32_t* targets, long long rows, long long vocab, int tiles, float inv_total_rows,
+                         cudaStream_t s) {
+    if (vocab > 0x7fffffffll || tiles < 1) return CGPT_ERR_UNSUPPORTED;
+    const long long blocks = (rows + 7) / 8;
+    softmax_stats_reduce_kernel<<<static_cast<unsigned>(blocks < kNumSMs * 8ll ? blocks : kNumSMs * 8ll), 256, 0, s>>>(
+        row_stats, row_loss, partial, target_logit, targets, rows, static_cast<int>(vocab), tiles, inv_total_rows);
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+    return CGPT_OK;
+}
 
 int cross_entropy_rows(float* row_loss, void* grad, const void* logits, const std::uint32_t* targets, long long rows,
                        long long vocab, float inv_total_rows, float gradient_scale, int dtype, cudaStream_t s) {

@@ -14,13 +14,6 @@ constexpr int kRingThreads = 1024;         // one CTA per SM: 64 registers per t
 constexpr int kRingWarps = kRingThreads / 32;
 constexpr int kRingCpt = 4;                // 16-byte chunks per thread held in registers (32 fp32 values)
 
-// exp as the reference's fast-math build computes __expf: ex2.approx.ftz(x * log2 e).
-__device__ __forceinline__ float fast_exp(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
-    return y;
-}
-
 // Packed pair arithmetic on the storage dtype.
 template <typename T> struct Packed2;
 template <> struct Packed2<__half> {

@@ -532,7 +532,85 @@ int launch_tc_mgroups(T* const* Cs, const T* const* As, const T* B, const int* M
     return CGPT_OK;
 }
 
+// LM-head logits X [M,K] * Cw [N,K]^T on CTA pairs with a softmax epilogue (gemm_pair.cuh). out: the logits
+// (kSoftmaxStatsStore) or the gradient (kSoftmaxGrad), [M,N]; not used by kSoftmaxStats. No split-K.
+template <typename T, int SOFTMAX>
+int launch_pair_softmax(T* out, const T* X, const T* Cw, int M, int N, int K, const SoftmaxEpilogue& sx, int dtype, cudaStream_t s) {
+    constexpr int BN = kPairBN;
+    GemmOperands ops;
+    GemmOutputs outs;
+    ops.segments = 1;
+    ops.groups = 1;
+    ops.group_dim = 0;
+    const int total_kb = (K + BK - 1) / BK;
+    const std::uint64_t a_dims[2] = {static_cast<std::uint64_t>(K), static_cast<std::uint64_t>(M)};
+    const std::uint64_t b_dims[2] = {static_cast<std::uint64_t>(K), static_cast<std::uint64_t>(N)};
+    const std::uint64_t k_st[1] = {static_cast<std::uint64_t>(K) * 2};
+    const std::uint32_t a_box[2] = {BK, BM}, b_box[2] = {BK, BN / 2}, c_box[2] = {64, BM};
+    for (int i = 0; i < kMaxKSegments; ++i) {
+        CGPT_TRY(make_tensor_map(&ops.a[i], dtype, X, 2, a_dims, k_st, a_box));
+        CGPT_TRY(make_tensor_map(&ops.b[i], dtype, Cw, 2, b_dims, k_st, b_box));
+        ops.kb_end[i] = total_kb;
+        ops.tile_end[i] = 0;
+        outs.c[i] = ops.a[0];      // placeholder unless the epilogue stores
+    }
+    if (SOFTMAX != kSoftmaxStats) {
+        const std::uint64_t c_dims[2] = {static_cast<std::uint64_t>(N), static_cast<std::uint64_t>(M)};
+        const std::uint64_t c_st[1] = {static_cast<std::uint64_t>(N) * 2};
+        CGPT_TRY(make_tensor_map(&outs.c[0], dtype, out, 2, c_dims, c_st, c_box));
+        outs.c[1] = outs.c[2] = outs.c[0];
+    }
+    const int tiles_m = (M + kPairBM - 1) / kPairBM, tiles_n = (N + BN - 1) / BN;
+    const long long units = static_cast<long long>(tiles_m) * tiles_n;
+    auto* pkernel = gemm_pair_softmax_kernel<T, SOFTMAX>;
+    static PerDeviceOnce attr_once;
+    if (attr_once.needed()) {
+        CGPT_CUDA_TRY(cudaFuncSetAttribute(pkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::kSmemBytes));
+        attr_once.done();
+    }
+    const unsigned grid = static_cast<unsigned>(pair_grid(reinterpret_cast<const void*>(pkernel), static_cast<int>(units < kNumSMs ? units : kNumSMs)));
+    if (grid == 0) return CGPT_ERR_UNSUPPORTED;
+    const bool timed = g_timing.enabled && g_timing.used + 2 <= g_timing.events.size();
+    if (timed) CGPT_CUDA_TRY(cudaEventRecord(g_timing.events[g_timing.used], s));
+    pkernel<<<grid, kGemmThreads, PairCfg::kSmemBytes, s>>>(ops, outs, M, N, total_kb, tiles_m, tiles_n, sx);
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+    if (timed) {
+        CGPT_CUDA_TRY(cudaEventRecord(g_timing.events[g_timing.used + 1], s));
+        g_timing.used += 2;
+        g_timing.flops.push_back(2.0 * M * N * K);
+    }
+    return CGPT_OK;
+}
+
 }  // namespace
+
+int gemm_logits_softmax(int mode, void* out, const void* x, const void* c, long long M, long long N, long long K,
+                        float2* partial, float* target_logit, const std::uint32_t* targets, const float2* row_stats,
+                        float out_scale, int dtype, cudaStream_t s) {
+    if (!x || !c || !targets) return CGPT_ERR_NULL;
+    if (mode != kSoftmaxStats && !out) return CGPT_ERR_NULL;
+    if (mode == kSoftmaxGrad ? !row_stats : (!partial || !target_logit)) return CGPT_ERR_NULL;
+    if (dtype != CGPT_DTYPE_F16 && dtype != CGPT_DTYPE_BF16) return CGPT_ERR_UNSUPPORTED;
+    if (M < kPairBM || N < kPairBN || K < 32 || M > 0x7fffffffll || N > 0x7fffffffll || K > 0x7fffffffll || K % 8 != 0 || N % 8 != 0 ||
+        !aligned16(x) || !aligned16(c) || (out != nullptr && !aligned16(out)) || !pair_kernel_enabled())
+        return CGPT_ERR_UNSUPPORTED;
+    const SoftmaxEpilogue sx{partial, target_logit, targets, row_stats, out_scale};
+    const int m = static_cast<int>(M), n = static_cast<int>(N), k = static_cast<int>(K);
+#define CGPT_SOFTMAX_CASE(MODE)                                                                                              \
+    if (mode == MODE) {                                                                                                      \
+        if (dtype == CGPT_DTYPE_F16)                                                                                         \
+            return launch_pair_softmax<__half, MODE>(static_cast<__half*>(out), static_cast<const __half*>(x),              \
+                                                     static_cast<const __half*>(c), m, n, k, sx, dtype, s);                  \
+        return launch_pair_softmax<__nv_bfloat16, MODE>(static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(x), \
+                                                        static_cast<const __nv_bfloat16*>(c), m, n, k, sx, dtype, s);         \
+    }
+    CGPT_SOFTMAX_CASE(kSoftmaxStatsStore)
+    CGPT_SOFTMAX_CASE(kSoftmaxStats)
+    CGPT_SOFTMAX_CASE(kSoftmaxGrad)
+#undef CGPT_SOFTMAX_CASE
+    return CGPT_ERR_OPTION;
+}
 
 // C[M,N] (+)= sum_i A_i * B_i over `segments` operand pairs chained along K (1 for a plain GEMM).
 // a_mn = 0: A_i stored [M,K_i] (K contiguous); 1: A_i stored [K_i,M]. b_mn = 0: B_i stored [N,K_i]; 1: B_i stored

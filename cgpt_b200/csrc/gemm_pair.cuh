@@ -34,11 +34,27 @@ struct PairCfg {
     static_assert(kSmemBytes <= 232448, "pair GEMM shared memory exceeds the 227 KB a CTA may use");
 };
 
-template <typename T, bool A_MN, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
-gemm_tcgen05_pair_kernel(const __grid_constant__ GemmOperands ops, const __grid_constant__ GemmOutputs outs,
+// Softmax work the epilogue can do on a 256 x 256 tile of LM-head logits while it is still in TMEM (the logits product of
+// the cut cross-entropy). A thread of the epilogue owns one row of the tile, so row statistics need no exchange.
+//   kSoftmaxStatsStore  store the 16-bit logits AND write, per row and tile, (max, sum exp(l - max)) over the tile's
+//                       columns of the ROUNDED logits, plus the target's logit where the tile holds the target column
+//   kSoftmaxStats       the same without storing the logits (pass 1 of the recomputing form)
+//   kSoftmaxGrad        store G = (exp(l - row max) / row sum - onehot) * out_scale instead of the logits (pass 2)
+// Per element the arithmetic is the row kernel's (cross_entropy_ring.cuh): logits rounded to the storage dtype,
+// ex2.approx.ftz((l - max) * log2 e), non-target gradient e * (1/sum * out_scale), target (e * 1/sum - 1) * out_scale.
+enum : int { kSoftmaxNone = 0, kSoftmaxStatsStore = 1, kSoftmaxStats = 2, kSoftmaxGrad = 3 };
+struct SoftmaxEpilogue {
+    float2* partial;                 // [M][tiles_n]
+    float* target_logit;             // [M]; written for rows whose target column exists
+    const std::uint32_t* targets;    // [M]
+    const float2* row_stats;         // [M] (row max, 1 / row sum): kSoftmaxGrad only
+    float out_scale;
+};
+
+template <typename T, bool A_MN, bool B_MN, int SOFTMAX>
+__device__ __forceinline__ void gemm_pair_body(const GemmOperands& ops, const GemmOutputs& outs,
                          T* __restrict__ C, float* __restrict__ partial, int M, int N, int total_kb, int tiles_m,
-                         int tiles_n, int splits, int kb_per_split, int epilogue) {
+                         int tiles_n, int splits, int kb_per_split, int epilogue, const SoftmaxEpilogue& sx) {
     using Cfg = PairCfg;
     constexpr int BN = kPairBN;
     extern __shared__ unsigned char gemm_smem_raw[];
@@ -175,7 +191,103 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmOperands ops, const __grid_
             tc_fence_after_sync();
             const int row = tile_m * kPairBM + static_cast<int>(rank) * BM + quarter * 32 + lane;
             const std::uint32_t tmem_acc = tmem_base + buf * BN + (static_cast<std::uint32_t>(quarter * 32) << 16);
-            if (epilogue == kEpiStoreTma) {
+            if constexpr (SOFTMAX != kSoftmaxNone) {
+                constexpr bool kStores = SOFTMAX != kSoftmaxStats;
+                const int et = threadIdx.x - 64;
+                const int trow = quarter * 32 + lane;
+                const bool row_ok = row < M;
+                const std::uint32_t tgt = row_ok ? sx.targets[row] : 0xffffffffu;
+                const long long rel = static_cast<long long>(tgt) - static_cast<long long>(tile_n) * BN;
+                // the target's column inside this tile, or -1 (other tile, or no valid target)
+                const int tgt_rel = (tgt < static_cast<std::uint32_t>(N) && rel >= 0 && rel < BN) ? static_cast<int>(rel) : -1;
+                float run_m = -3.0e38f, run_s = 0.f, target_value = 0.f;
+                float row_max = 0.f, inv_sum = 0.f;
+                if (SOFTMAX == kSoftmaxGrad && row_ok) {
+                    const float2 st = sx.row_stats[row];
+                    row_max = st.x;
+                    inv_sum = st.y;
+                }
+                const float k = inv_sum * sx.out_scale;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 64) {
+                    unsigned char* buf_s = staging + stage_buf * (BM * 128);
+                    if (kStores) {
+                        if (et == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                    }
+                    std::uint32_t r0[32], r1[32];
+                    tmem_ld_32x32_x2(tmem_acc + c0, r0, tmem_acc + c0 + 32, r1);
+                    float v[64];
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) { v[e] = __uint_as_float(r0[e]); v[32 + e] = __uint_as_float(r1[e]); }
+                    // the values a materialised logits tensor would hold
+#pragma unroll
+                    for (int e = 0; e < 64; e += 2) round_pair_to_storage<T>(v[e], v[e + 1]);
+                    const int ncols = N - (tile_n * BN + c0);     // columns of this chunk that exist
+                    const bool hit = tgt_rel >= c0 && tgt_rel < c0 + 64;
+                    if (hit) {
+#pragma unroll
+                        for (int e = 0; e < 64; ++e)
+                            if (c0 + e == tgt_rel) target_value = v[e];
+                    }
+                    if (SOFTMAX != kSoftmaxGrad) {
+                        if (ncols > 0) {
+                            if (ncols < 64) {
+#pragma unroll
+                                for (int e = 0; e < 64; ++e)
+                                    if (e >= ncols) v[e] = -3.0e38f;
+                            }
+                            float m4[4] = {v[0], v[1], v[2], v[3]};
+#pragma unroll
+                            for (int e = 4; e < 64; ++e) m4[e & 3] = fmaxf(m4[e & 3], v[e]);
+                            const float new_m = fmaxf(fmaxf(run_m, fmaxf(m4[0], m4[1])), fmaxf(m4[2], m4[3]));
+                            float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                            for (int e = 0; e < 64; ++e) s4[e & 3] += fast_exp(v[e] - new_m);
+                            run_s = run_s * fast_exp(run_m - new_m) + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
+                            run_m = new_m;
+                            if (ncols < 64) {   // the store below must not see the mask (TMA clips the columns anyway)
+#pragma unroll
+                                for (int e = 0; e < 64; ++e)
+                                    if (e >= ncols) v[e] = 0.f;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 64; ++e) v[e] = fast_exp(v[e] - row_max) * k;
+                        if (hit) {
+                            const float g = (fast_exp(target_value - row_max) * inv_sum - 1.0f) * sx.out_scale;
+#pragma unroll
+                            for (int e = 0; e < 64; ++e)
+                                if (c0 + e == tgt_rel) v[e] = g;
+                        }
+                    }
+                    if (kStores) {
+#pragma unroll
+                        for (int jj = 0; jj < 8; ++jj) {
+                            float w[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) w[e] = v[8 * jj + e];
+                            store_vec<T, 8>(reinterpret_cast<T*>(buf_s + trow * 128 + ((jj ^ (trow & 7)) << 4)), w);
+                        }
+                        fence_proxy_async_smem();
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (et == 0) {
+                            const int cx = tile_n * BN + c0;
+                            const int cy = tile_m * kPairBM + static_cast<int>(rank) * BM;
+                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                                         ::"l"(reinterpret_cast<std::uint64_t>(&outs.c[0])), "r"(smem_u32(buf_s)), "r"(cx), "r"(cy)
+                                         : "memory");
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        }
+                        stage_buf ^= 1;
+                    }
+                }
+                if (SOFTMAX != kSoftmaxGrad && row_ok) {
+                    sx.partial[static_cast<long long>(row) * tiles_n + tile_n] = make_float2(run_m, run_s);
+                    if (tgt_rel >= 0) sx.target_logit[row] = target_value;
+                }
+            } else if (epilogue == kEpiStoreTma) {
                 const int et = threadIdx.x - 64;
                 const int trow = quarter * 32 + lane;
 #pragma unroll 1
@@ -237,6 +349,25 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmOperands ops, const __grid_
         tc_fence_after_sync();
         tmem_dealloc_pair(tmem_base, 2 * BN);
     }
+}
+
+template <typename T, bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ GemmOperands ops, const __grid_constant__ GemmOutputs outs,
+                         T* __restrict__ C, float* __restrict__ partial, int M, int N, int total_kb, int tiles_m,
+                         int tiles_n, int splits, int kb_per_split, int epilogue) {
+    const SoftmaxEpilogue none{nullptr, nullptr, nullptr, nullptr, 0.f};
+    gemm_pair_body<T, A_MN, B_MN, kSoftmaxNone>(ops, outs, C, partial, M, N, total_kb, tiles_m, tiles_n, splits, kb_per_split,
+                                                epilogue, none);
+}
+
+// The LM-head product X C^T (both operands K-major, no split-K) with one of the softmax epilogues.
+template <typename T, int SOFTMAX>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_pair_softmax_kernel(const __grid_constant__ GemmOperands ops, const __grid_constant__ GemmOutputs outs, int M, int N,
+                         int total_kb, int tiles_m, int tiles_n, const SoftmaxEpilogue sx) {
+    gemm_pair_body<T, false, false, SOFTMAX>(ops, outs, nullptr, nullptr, M, N, total_kb, tiles_m, tiles_n, 1, total_kb,
+                                             kEpiStoreTma, sx);
 }
 
 // Grid of the pair kernel: two CTAs per cluster, one cluster per TPC that can host it.

@@ -169,8 +169,10 @@ def transformer_block_backward(grad_input, grad_output, input, weights: dict, gr
 
 def cut_cross_entropy_forward_backward(loss, input_gradient, classifier_gradient, input, classifier, device_targets,
                                        target_count, stream=None, gradient_scale: float = 1.0,
-                                       accumulate_classifier_gradient: bool = False, chunk_rows: int = 0):
-    """cut_cross_entropy_forward_backward (include/ops/cut_cross_entropy.h:25-33); F32, F16 or BF16."""
+                                       accumulate_classifier_gradient: bool = False, chunk_rows: int = 0, form: int = 0):
+    """cut_cross_entropy_forward_backward (include/ops/cut_cross_entropy.h:25-33); F32, F16 or BF16.
+    form: 0 = the library's default, 1 = row kernel over stored logits, 2 = tile statistics from the logits product's
+    epilogue + one streaming gradient pass, 3 = logits never stored (recomputed; gradient written by the epilogue)."""
     ts = (input_gradient, classifier_gradient, input, classifier)
     if any((not t.is_cuda) or t.dtype != input.dtype or not t.is_contiguous() for t in ts) or input.dim() != 2 \
             or classifier.dim() != 2 or classifier.shape[1] != input.shape[1]:
@@ -179,10 +181,11 @@ def cut_cross_entropy_forward_backward(loss, input_gradient, classifier_gradient
         raise _lib.CgptInvalidArgument("cut_cross_entropy: incompatible gradient or target count")
     if not (loss.is_cuda and loss.dtype == torch.float32 and tuple(loss.shape) == (1,)):
         raise _lib.CgptInvalidArgument("cut_cross_entropy: loss must be a CUDA F32 tensor with shape [1]")
-    check(lib.cgpt_cut_cross_entropy(ptr(loss), ptr(input_gradient), ptr(classifier_gradient), ptr(input),
-                                     ptr(classifier), ptr(device_targets), input.shape[0], classifier.shape[0],
-                                     input.shape[1], float(gradient_scale), int(accumulate_classifier_gradient),
-                                     chunk_rows, dtype_code(input), stream_ptr(stream)), "cut_cross_entropy_forward_backward")
+    check(lib.cgpt_cut_cross_entropy_form(int(form), ptr(loss), ptr(input_gradient), ptr(classifier_gradient), ptr(input),
+                                          ptr(classifier), ptr(device_targets), input.shape[0], classifier.shape[0],
+                                          input.shape[1], float(gradient_scale), int(accumulate_classifier_gradient),
+                                          chunk_rows, dtype_code(input), stream_ptr(stream)),
+          "cut_cross_entropy_forward_backward")
 
 
 class ModelStorage:

@@ -1,7 +1,8 @@
 """`python -m cgpt_b200.profile_ops <op> [--iters N]`: launches one operator a few times on inputs larger
 than L2 but a few hundred MB at most, so that `ncu -k regex:<kernel>` captures of it end by themselves.
 Ops: gemm_fwd, gemm_dx, gemm_dw, attention_fwd, attention_bwd, rmsnorm_bwd, swiglu_bwd, rope_bwd, embedding_bwd, adamw,
-cross_entropy, qknorm_fwd, qknorm_bwd.
+cross_entropy, cce (one 8192-row chunk of the cut cross-entropy at hidden 1024, vocabulary 32000; --cce-form 1|2|3),
+qknorm_fwd, qknorm_bwd.
 Prints the CUDA-event time per launch (taken without a profiler attached it is the number to quote)."""
 from __future__ import annotations
 
@@ -31,6 +32,8 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--attention-shape", choices=["104m", "d64"], default="104m",
                     help="attention ops: 8/2 heads of 128 (the 104m layer) or 12/4 heads of 64")
+    ap.add_argument("--cce-form", type=int, default=0, help="cce: 0 default, 1 row kernel, 2 tile statistics, 3 recompute")
+    ap.add_argument("--rows", type=int, default=8192, help="cce: rows (8192 is one chunk)")
     a = ap.parse_args()
     h = lambda *s: torch.randn(*s, device="cuda").half()
     T, d, I = 32768, 1024, 2048
@@ -87,6 +90,15 @@ def main() -> None:
         loss = torch.zeros(1, device="cuda")
         ms = _run(lambda: ops.cross_entropy_forward_backward(loss, z, z, t, rows, None, 1024.0), a.iters)
         print(f"cross_entropy {rows}x{V} in place: {ms * 1e3:.1f} us, {2.0 * rows * V * 2 / ms / 1e6:.0f} GB/s algorithmic")
+    elif a.op == "cce":
+        from . import model as M
+        rows, V = a.rows, 32000
+        x, c = h(rows, d), h(V, d) * 0.02
+        t = torch.randint(0, V, (rows,), device="cuda", dtype=torch.int32)
+        loss, dx, dc = torch.zeros(1, device="cuda"), torch.empty_like(x), torch.empty_like(c)
+        ms = _run(lambda: M.cut_cross_entropy_forward_backward(loss, dx, dc, x, c, t, rows, None, 1024.0, form=a.cce_form), a.iters)
+        print(f"cce form {a.cce_form} {rows}x{d}x{V}: {ms * 1e3:.1f} us, {3 * 2.0 * rows * d * V / ms / 1e9:.1f} TFLOP/s on 3 products, "
+              f"loss {float(loss.item()):.6f}")
     elif a.op == "adamw":
         sizes = [32000 * 1024] + [1024 * 1024, 2048 * 1024, 2048 * 1024, 1024 * 2048] * 8
         ps = [h(n) * 0.02 for n in sizes]

@@ -56,7 +56,7 @@ def time_gemms(train_step, steps: int = 2) -> dict:
             "launches": int(n.value) // steps, "gemm_flops": fl.value / steps, "model_flops": model}
 
 
-def time_cut_cross_entropy(rows: int, hidden: int, vocab: int, iters: int = 5) -> dict:
+def time_cut_cross_entropy(rows: int, hidden: int, vocab: int, iters: int = 5, form: int = 0) -> dict:
     """The loss layer alone: cut cross-entropy forward + backward (loss, dX, dC) on fp16 N(0,1) activations, an N(0,0.02)
     classifier and uniform targets, gradient scale 1024. Credited work: three products of 2*rows*vocab*hidden FLOPs (logits,
     dX, dC); algorithmic bytes: X, C, dX, dC and the targets. Time: CUDA events around `iters` calls after 2 warm-up calls."""
@@ -67,7 +67,7 @@ def time_cut_cross_entropy(rows: int, hidden: int, vocab: int, iters: int = 5) -
     t = torch.randint(0, vocab, (rows,), generator=g, device="cuda", dtype=torch.int32)
     loss = torch.zeros(1, device="cuda")
     dx, dc = torch.empty_like(x), torch.empty_like(c)
-    fn = lambda: M.cut_cross_entropy_forward_backward(loss, dx, dc, x, c, t, rows, None, 1024.0)
+    fn = lambda: M.cut_cross_entropy_forward_backward(loss, dx, dc, x, c, t, rows, None, 1024.0, form=form)
     for _ in range(2):
         fn()
     torch.cuda.synchronize()
@@ -79,7 +79,7 @@ def time_cut_cross_entropy(rows: int, hidden: int, vocab: int, iters: int = 5) -
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / iters
     flops = 3.0 * 2.0 * rows * vocab * hidden
-    return {"shape": f"{rows} x {hidden} x {vocab}", "us": ms * 1e3, "tflops": flops / ms / 1e9, "credited_flops": flops,
+    return {"shape": f"{rows} x {hidden} x {vocab}", "form": form, "us": ms * 1e3, "tflops": flops / ms / 1e9, "credited_flops": flops,
             "algorithmic_bytes": 2.0 * 2 * (rows * hidden + vocab * hidden) + 4 * rows, "loss": float(loss.item())}
 
 

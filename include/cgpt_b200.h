@@ -350,6 +350,19 @@ int cgpt_cut_cross_entropy(float* loss, void* dx, void* dc, const void* x, const
                            const uint32_t* targets, size_t rows, size_t vocab, size_t hidden,
                            float gradient_scale, int accumulate_dc, size_t chunk_rows, int dtype,
                            cgpt_stream_t stream);
+/* The same operator with the form of a chunk chosen by the caller (cgpt_cut_cross_entropy uses the fastest measured):
+ *   CGPT_CCE_ROWS       logits product into the scratch, one row kernel turns them into G in place;
+ *   CGPT_CCE_TILES      the logits product's epilogue also leaves (max, sum exp) of every 256-column tile of every row,
+ *                       so G is one streaming pass over the scratch without row reductions;
+ *   CGPT_CCE_RECOMPUTE  the logits are never stored: a first product leaves only the tile statistics, a second one
+ *                       recomputes the logits and its epilogue writes G from tensor memory (four products, not three).
+ * The last two need 16-bit tensors, chunks of at least 256 rows, vocab >= 256 and % 8 == 0, hidden % 8 == 0 and return
+ * CGPT_ERR_UNSUPPORTED otherwise. All forms give the same loss and gradients up to the rounding of the row sums. */
+enum { CGPT_CCE_DEFAULT = 0, CGPT_CCE_ROWS = 1, CGPT_CCE_TILES = 2, CGPT_CCE_RECOMPUTE = 3 };
+int cgpt_cut_cross_entropy_form(int form, float* loss, void* dx, void* dc, const void* x, const void* c,
+                                const uint32_t* targets, size_t rows, size_t vocab, size_t hidden,
+                                float gradient_scale, int accumulate_dc, size_t chunk_rows, int dtype,
+                                cgpt_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Transformer block / model forward and backward (host orchestration in C++ inside the library).

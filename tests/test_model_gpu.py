@@ -66,6 +66,35 @@ def test_cce_against_oracle(M, rows, vocab, hidden, chunk, dt):
     assert_close(host(dc2), 2 * host(dc), tol / 2, "dc accumulate", metric="max")
 
 
+@pytest.mark.parametrize("rows,vocab,hidden,chunk,dt", [(512, 32000, 256, 0, "f16"), (1000, 4096, 768, 384, "f16"),
+                                                        (600, 1000, 64, 300, "bf16"), (256, 264, 32, 0, "f16")])
+@pytest.mark.parametrize("form", [2, 3])
+def test_cce_forms_agree(M, rows, vocab, hidden, chunk, dt, form):
+    """The tile-statistics form and the recomputing form of the loss layer against the row-kernel form and the oracle:
+    vocabularies that are not a multiple of the 256-column tile (1000, 264), several chunks, a ragged last chunk that the
+    pair kernel cannot take (1000 = 2 x 384 + 232 rows: the explicit form refuses), targets at both ends of the vocabulary
+    and one outside it."""
+    r = np.random.default_rng(rows + vocab)
+    x, cl = dev(r.standard_normal((rows, hidden)), dt), dev(0.05 * r.standard_normal((vocab, hidden)), dt)
+    t = r.integers(0, vocab, rows); t[5] = vocab + 3; t[7] = vocab - 1; t[9] = 0
+    out = {}
+    for f in (1, form):
+        loss = torch.zeros(1, device="cuda"); dx, dc = torch.full_like(x, float("nan")), torch.full_like(cl, float("nan"))
+        if f != 1 and rows == 1000:
+            with pytest.raises(Exception):
+                M.cut_cross_entropy_forward_backward(loss, dx, dc, x, cl, ids_dev(t), rows, None, 1024.0, chunk_rows=chunk, form=f)
+            return
+        M.cut_cross_entropy_forward_backward(loss, dx, dc, x, cl, ids_dev(t), rows, None, 1024.0, chunk_rows=chunk, form=f)
+        out[f] = (float(loss.item()), host(dx), host(dc))
+    el, edx, edc = O.cut_cross_entropy(host(x), host(cl), t, 1024.0)
+    tol = {"f16": 1e-2, "bf16": 5e-2}[dt]
+    assert abs(out[form][0] - float(el)) <= 1e-3
+    assert abs(out[form][0] - out[1][0]) <= 2e-6 * max(1.0, abs(out[1][0]))
+    assert_close(out[form][1], edx, tol, "dx"); assert_close(out[form][2], edc, tol / 2, "dc", metric="max")
+    # against the row-kernel form: same rounded logits, same exponentials; only the order of the row sums differs
+    assert_close(out[form][1], out[1][1], tol / 10, "dx vs rows form"); assert_close(out[form][2], out[1][2], tol / 10, "dc vs rows form", metric="max")
+
+
 # --------------------------------------------------------------------------------------------- block
 @pytest.mark.parametrize("batch,seq,opts", [(2, 128, (256, 688, 4, 2, 64, 64)), (1, 96, (64, 64, 2, 1, 32, 32)), (2, 64, (256, 512, 2, 1, 128, 128))])
 def test_block_forward_backward(M, batch, seq, opts):
