@@ -111,12 +111,15 @@ SIGNATURES = {
     "cgpt_linear_backward_weight_fused": (_i, [C.POINTER(_vp), C.POINTER(_vp), _vp, C.POINTER(_sz), _sz, _sz, _sz, _i, _i, _vp]),
     "cgpt_linear_swiglu_forward": (_i, [_vp] * 6 + [_sz] * 3 + [_i, _vp]),
     "cgpt_linear_backward_input_fused": (_i, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_sz), _sz, _sz, _sz, _i, _i, _vp]),
+    "cgpt_linear_forward_sum": (_i, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_sz), _sz, _sz, _sz, _vp, _i, _vp]),
     "cgpt_attention_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _f, _i, _sz, _i, _i, _vp]),
     "cgpt_attention_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _f, _i,
                                      _sz, _i, _i, _i, _vp]),
     "cgpt_rmsnorm_forward": (_i, [_vp, _vp, _vp, _sz, _sz, _f, _i, _vp]),
     "cgpt_rmsnorm_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _f, _i, _vp]),
     "cgpt_rmsnorm_backward_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _f, _i, _vp]),
+    "cgpt_rmsnorm_forward_dual": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _f, _i, _vp]),
+    "cgpt_rmsnorm_backward_dual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _f, _i, _vp]),
     "cgpt_qknorm_rope_forward": (_i, [_vp] * 8 + [_sz] * 8 + [_f, _i, _vp]),
     "cgpt_qknorm_rope_backward": (_i, [_vp] * 12 + [_sz] * 8 + [_f, _i, _vp]),
     "cgpt_rope_forward": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _i, _vp]),

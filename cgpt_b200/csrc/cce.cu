@@ -19,6 +19,8 @@
 // Reference semantics: src/ops/cut_cross_entropy.cu:97-160 (F32 tensors; same loss and gradients, no
 // gradient_scale there) and, for what CGPT's trainer computes on fp16 logits, src/ops/cross_entropy.cu:
 // 134-245 between linear_forward and linear_backward (train/train.cpp:536-544).
+#include <cstdlib>
+
 #include "internal.h"
 #include "launch_counter.h"
 
@@ -41,7 +43,11 @@ int cut_cross_entropy_form(int form, float* loss, void* dx, void* dc, const void
         return CGPT_ERR_SHAPE;
     if (form < kCceAuto || form > kCceRecompute) return CGPT_ERR_OPTION;
     const bool explicit_form = form != kCceAuto;
-    if (form == kCceAuto) form = kCceDefault;
+    if (form == kCceAuto) {
+        // diagnosis builds: CGPT_B200_CCE_FORM=1|2|3 replaces the default form (same-box comparisons inside a training step)
+        static const int forced = [] { const char* e = diagnosis_env("CGPT_B200_CCE_FORM"); return e ? std::atoi(e) : 0; }();
+        form = forced >= kCceRows && forced <= kCceRecompute ? forced : kCceDefault;
+    }
     if (chunk_rows == 0) chunk_rows = 8192;
     if (chunk_rows > rows) chunk_rows = rows;
     const std::size_t esz = dtype_size(dtype);

@@ -83,7 +83,7 @@ template <int BN> struct GemmCfg {
 // Device status word shared by the contraction kernels: non-zero means a bounded wait ran out.
 __device__ unsigned int g_gemm_status = 0;
 
-enum : int { kEpiStore = 0, kEpiAccumulate = 1, kEpiPartial = 2, kEpiNone = 3, kEpiStoreTma = 4, kEpiStageOnly = 5, kEpiStoreTmaFixed = 6 };
+enum : int { kEpiStore = 0, kEpiAccumulate = 1, kEpiPartial = 2, kEpiNone = 3, kEpiStoreTma = 4, kEpiStageOnly = 5, kEpiStoreTmaFixed = 6, kEpiStoreTmaResidual = 7 };
 
 // Optional timing of the tensor-core GEMM launches (eager mode only, never during stream capture):
 // a CUDA event pair around every tensor-core GEMM launch plus its algorithmic FLOPs.
@@ -207,11 +207,13 @@ inline bool pair_kernel_enabled() {
 // PAIR: 256 x 256 tiles on CTA pairs (BN must be 256) instead of 128 x BN tiles on single CTAs.
 template <typename T, int BN, bool A_MN, bool B_MN, bool PAIR = false>
 int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int segments, int M, int N, int accumulate, int dtype,
-              cudaStream_t s) {
+              cudaStream_t s, const T* residual = nullptr) {
     using Cfg = GemmCfg<BN>;
     static_assert(!PAIR || BN == kPairBN, "the pair kernel has 256-column tiles");
     constexpr int kTileM = PAIR ? kPairBM : BM;        // rows of a work unit's tile
     constexpr int kBoxN = PAIR ? BN / 2 : BN;          // B rows (columns of C) one CTA loads per K block
+    // a residual operand is added only by the pair kernel's TMA-store epilogue
+    if (residual != nullptr && (!PAIR || accumulate || N % 64 != 0 || !aligned16(C) || !aligned16(residual))) return CGPT_ERR_UNSUPPORTED;
     GemmOperands ops;
     ops.segments = segments;
     ops.groups = 1;
@@ -255,6 +257,7 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
     int kb_per_split = (total_kb + splits - 1) / splits;
     splits = (total_kb + kb_per_split - 1) / kb_per_split;   // no empty split
     float* partial = nullptr;
+    if (splits > 1 && residual != nullptr) return CGPT_ERR_UNSUPPORTED;
     if (splits > 1) {
         void* scratch = nullptr;
         CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(splits) * M * N * sizeof(float), s));
@@ -297,6 +300,7 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
             const std::uint32_t box_c[2] = {64, BM};
             CGPT_TRY(make_tensor_map(&tc, dtype, C, 2, dims_c, st_c, box_c));
             epi = kEpiStoreTma;
+            if (PAIR && residual != nullptr) epi = kEpiStoreTmaResidual;
             // diagnosis builds only: CGPT_B200_GEMM_NOSTORE=2 stages the tile in shared memory but never issues the TMA store
             // and =3 issues every TMA store to the first 16 KB of C (same store mechanics, no memory-system load)
             static const int diag = [] { const char* e = diagnosis_env("CGPT_B200_GEMM_NOSTORE"); return e ? std::atoi(e) : 0; }();
@@ -304,7 +308,8 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
             if (!PAIR && diag == 3) epi = kEpiStoreTmaFixed;
         }
         outs.c[1] = outs.c[2] = outs.c[0];
-        pkernel<<<grid, kGemmThreads, smem_bytes, s>>>(ops, outs, C, partial, M, N, total_kb, tiles_m, tiles_n, splits, kb_per_split, epi);
+        T* c_arg = epi == kEpiStoreTmaResidual ? const_cast<T*>(residual) : C;    // that epilogue reads it, the store goes through the map
+        pkernel<<<grid, kGemmThreads, smem_bytes, s>>>(ops, outs, c_arg, partial, M, N, total_kb, tiles_m, tiles_n, splits, kb_per_split, epi);
     }
     count_launch();
     CGPT_LAUNCH_CHECK();
@@ -327,7 +332,7 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
 
 template <typename T>
 int launch_tc_layout(T* C, const T* const* A, const T* const* B, const int* K, int segments, int M, int N, int a_mn, int b_mn,
-                     int accumulate, int dtype, cudaStream_t s) {
+                     int accumulate, int dtype, cudaStream_t s, const T* residual = nullptr) {
     // 128x256 tiles whenever N allows: a 128x128 tile needs as many shared-memory operand bytes per MMA as the
     // tensor core can consume, 128x256 needs 3/4 of that per FLOP. Few tiles are compensated by split-K.
     const bool wide = N >= 256;
@@ -338,9 +343,10 @@ int launch_tc_layout(T* C, const T* const* A, const T* const* B, const int* K, i
 #define CGPT_GEMM_CASE(AM, BMN)                                                                  \
     if (a_mn == AM && b_mn == BMN) {                                                             \
         if (pair) {                                                                              \
-            const int rc = launch_tc<T, 256, AM != 0, BMN != 0, true>(C, A, B, K, segments, M, N, accumulate, dtype, s); \
+            const int rc = launch_tc<T, 256, AM != 0, BMN != 0, true>(C, A, B, K, segments, M, N, accumulate, dtype, s, residual); \
             if (rc != CGPT_ERR_UNSUPPORTED) return rc;                                           \
         }                                                                                        \
+        if (residual != nullptr) return CGPT_ERR_UNSUPPORTED;                                    \
         return wide ? launch_tc<T, 256, AM != 0, BMN != 0>(C, A, B, K, segments, M, N, accumulate, dtype, s) \
                     : launch_tc<T, 128, AM != 0, BMN != 0>(C, A, B, K, segments, M, N, accumulate, dtype, s); \
     }
@@ -617,7 +623,8 @@ int gemm_logits_softmax(int mode, void* out, const void* x, const void* c, long 
 // [K_i,N]. Chooses the tensor-core kernel for 16-bit dtypes when TMA can address the operands (16-byte aligned
 // bases, leading dimensions a multiple of 8 elements), else one SIMT launch per segment.
 int gemm_dispatch_segments(void* C, const void* const* A, const void* const* B, const long long* K, int segments, long long M,
-                           long long N, int a_mn, int b_mn, int accumulate, int dtype, bool force_simt, cudaStream_t s) {
+                           long long N, int a_mn, int b_mn, int accumulate, int dtype, bool force_simt, cudaStream_t s,
+                           const void* residual = nullptr) {
     if (!C || !A || !B || !K) return CGPT_ERR_NULL;
     if (segments < 1 || segments > kMaxKSegments) return CGPT_ERR_SHAPE;
     if (!valid_float_dtype(dtype)) return CGPT_ERR_DTYPE;
@@ -639,11 +646,13 @@ int gemm_dispatch_segments(void* C, const void* const* A, const void* const* B, 
         if (dtype == CGPT_DTYPE_F16)
             return launch_tc_layout<__half>(static_cast<__half*>(C), reinterpret_cast<const __half* const*>(A),
                                             reinterpret_cast<const __half* const*>(B), k32, segments, static_cast<int>(M),
-                                            static_cast<int>(N), a_mn, b_mn, accumulate, dtype, s);
+                                            static_cast<int>(N), a_mn, b_mn, accumulate, dtype, s, static_cast<const __half*>(residual));
         return launch_tc_layout<__nv_bfloat16>(static_cast<__nv_bfloat16*>(C), reinterpret_cast<const __nv_bfloat16* const*>(A),
                                                reinterpret_cast<const __nv_bfloat16* const*>(B), k32, segments, static_cast<int>(M),
-                                               static_cast<int>(N), a_mn, b_mn, accumulate, dtype, s);
+                                               static_cast<int>(N), a_mn, b_mn, accumulate, dtype, s,
+                                               static_cast<const __nv_bfloat16*>(residual));
     }
+    if (residual != nullptr) return CGPT_ERR_UNSUPPORTED;   // the caller adds it with a separate pass
     for (int i = 0; i < segments; ++i) {
         const long long Ki = K[i];
         const long long a_sm = a_mn ? 1 : Ki, a_sk = a_mn ? M : 1, b_sn = b_mn ? 1 : Ki, b_sk = b_mn ? N : 1;
@@ -840,6 +849,30 @@ extern "C" int cgpt_linear_backward_input_fused(void* dx, const void* const* dy,
     return gemm_dispatch_segments(dx, dy, w, ks, static_cast<int>(count), static_cast<long long>(rows),
                                   static_cast<long long>(in_features), 0, 1, accumulate_input, dtype, false,
                                   static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cgpt_linear_forward_sum(void* y, const void* const* x, const void* const* w, const size_t* in_features,
+                                       size_t count, size_t rows, size_t out_features, const void* residual, int dtype,
+                                       cgpt_stream_t stream) {
+    if (!y || !x || !w || !in_features) return CGPT_ERR_NULL;
+    if (count < 1 || count > static_cast<size_t>(kMaxKSegments)) return CGPT_ERR_SHAPE;
+    long long ks[kMaxKSegments] = {0, 0, 0};
+    for (size_t i = 0; i < count; ++i) {
+        if (!x[i] || !w[i]) return CGPT_ERR_NULL;
+        if (in_features[i] == 0 || in_features[i] > 0x7fffffffull) return CGPT_ERR_SHAPE;
+        ks[i] = static_cast<long long>(in_features[i]);
+    }
+    if (rows == 0 || out_features == 0 || rows > 0x7fffffffull || out_features > 0x7fffffffull) return CGPT_ERR_SHAPE;
+    auto s = static_cast<cudaStream_t>(stream);
+    const long long T = static_cast<long long>(rows), O = static_cast<long long>(out_features);
+    // Y = R + sum_i X_i W_i^T: A_i = X_i [rows, in_i], B_i = W_i [out, in_i], both K-major, chained along K
+    int rc = gemm_dispatch_segments(y, x, w, ks, static_cast<int>(count), T, O, 0, 0, 0, dtype, false, s, residual);
+    if (rc != CGPT_ERR_UNSUPPORTED || residual == nullptr) return rc;
+    // no epilogue that adds the residual for this shape or dtype: the product alone, then one elementwise pass
+    // (y may not alias the residual on this path: the product is written first)
+    if (y == residual) return CGPT_ERR_OPTION;
+    CGPT_TRY(gemm_dispatch_segments(y, x, w, ks, static_cast<int>(count), T, O, 0, 0, 0, dtype, false, s));
+    return cgpt_add(y, y, residual, nullptr, rows * out_features, dtype, stream);
 }
 
 extern "C" int cgpt_b200_device_status(unsigned int* status_out, int clear) {

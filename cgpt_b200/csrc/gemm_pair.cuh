@@ -287,12 +287,22 @@ __device__ __forceinline__ void gemm_pair_body(const GemmOperands& ops, const Ge
                     sx.partial[static_cast<long long>(row) * tiles_n + tile_n] = make_float2(run_m, run_s);
                     if (tgt_rel >= 0) sx.target_logit[row] = target_value;
                 }
-            } else if (epilogue == kEpiStoreTma) {
+            } else if (epilogue == kEpiStoreTma || epilogue == kEpiStoreTmaResidual) {
                 const int et = threadIdx.x - 64;
                 const int trow = quarter * 32 + lane;
+                // kEpiStoreTmaResidual: C points at a [M, N] tensor that is added to the product in fp32 before the one
+                // rounding (N % 64 == 0, checked by the host: a chunk of 64 columns is inside the row or outside it)
+                const bool with_residual = epilogue == kEpiStoreTmaResidual;
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 64) {
                     unsigned char* buf_s = staging + stage_buf * (BM * 128);
+                    uint4 res[8];
+                    const bool res_ok = with_residual && row < M && tile_n * BN + c0 < N;
+                    if (res_ok) {     // issued before the waits below: the loads fly under them
+                        const uint4* rp = reinterpret_cast<const uint4*>(C + static_cast<long long>(row) * N + tile_n * BN + c0);
+#pragma unroll
+                        for (int jj = 0; jj < 8; ++jj) res[jj] = __ldg(rp + jj);
+                    }
                     if (et == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                     std::uint32_t r0[32], r1[32];
@@ -303,6 +313,12 @@ __device__ __forceinline__ void gemm_pair_body(const GemmOperands& ops, const Ge
                         float v[8];
 #pragma unroll
                         for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(src[e]);
+                        if (res_ok) {
+                            Pack<T, 8> pk;
+                            *reinterpret_cast<uint4*>(&pk) = res[jj];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) v[e] += to_f32<T>(pk.v[e]);
+                        }
                         store_vec<T, 8>(reinterpret_cast<T*>(buf_s + trow * 128 + ((jj ^ (trow & 7)) << 4)), v);
                     }
                     fence_proxy_async_smem();

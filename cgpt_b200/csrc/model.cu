@@ -127,9 +127,15 @@ struct Branches {
     int lane() const { return two ? 1 : 0; }
 };
 
+// Diagnosis builds: CGPT_B200_DUAL_NORM=0 runs the two norms of the block input as separate passes (comparison runs).
+bool dual_norm_enabled() {
+    static const bool on = [] { const char* e = diagnosis_env("CGPT_B200_DUAL_NORM"); return !(e && e[0] == '0'); }();
+    return on;
+}
+
 int mlp_forward(const void* in, const cgpt_block_params* w, const cgpt_block_saved* sv, const BlockScratch& ws, const Dims& m,
-                int dt, float eps, cudaStream_t stream) {
-    CGPT_TRY(cgpt_rmsnorm_forward(sv->norm, in, w->ffn_norm, m.rows, m.d, eps, dt, stream));
+                int dt, float eps, bool with_norm, bool with_down, cudaStream_t stream) {
+    if (with_norm) CGPT_TRY(cgpt_rmsnorm_forward(sv->norm, in, w->ffn_norm, m.rows, m.d, eps, dt, stream));
     // gate, up and the activation (two GEMMs and an activation pass in the reference, :566-579). The one-launch form
     // (cgpt_linear_swiglu_forward, same results bit for bit) measured 300 us against 292 us for the three launches at
     // the 104m shape, so the block uses it only in diagnosis builds with CGPT_B200_FUSED_SWIGLU=1.
@@ -142,12 +148,14 @@ int mlp_forward(const void* in, const cgpt_block_params* w, const cgpt_block_sav
         CGPT_TRY(cgpt_linear_forward(sv->up, sv->norm, w->up_proj, m.rows, m.d, m.inter, dt, stream));
         CGPT_TRY(cgpt_swiglu_forward(sv->activated, sv->gate, sv->up, m.rows * m.inter, dt, stream));
     }
+    if (!with_down) return CGPT_OK;     // the caller folds the down projection into the block's final product
     return cgpt_linear_forward(ws.ffn_out, sv->activated, w->down_proj, m.rows, m.inter, m.d, dt, stream);
 }
 
 // MLP branch of the backward (transformer_block.cu:663-681): ends with grad_in = grad_out + d(ffn_norm).
 int mlp_backward(void* grad_in, const void* grad_out, const void* in, const cgpt_block_params* w, const cgpt_block_params* g,
-                 const cgpt_block_saved* sv, const BlockScratch& ws, const Dims& m, int dt, float eps, cudaStream_t stream) {
+                 const cgpt_block_saved* sv, const BlockScratch& ws, const Dims& m, int dt, float eps, bool with_norm,
+                 cudaStream_t stream) {
     CGPT_TRY(cgpt_linear_backward(ws.d_act, g->down_proj, nullptr, grad_out, sv->activated, w->down_proj, m.rows, m.inter,
                                   m.d, 0, 0, 0, dt, stream));
     CGPT_TRY(cgpt_swiglu_backward(ws.d_gate, ws.d_up, ws.d_act, sv->gate, sv->up, m.rows * m.inter, 0, 0, dt, stream));
@@ -163,6 +171,7 @@ int mlp_backward(void* grad_in, const void* grad_out, const void* in, const cgpt
         const size_t outs[2] = {m.inter, m.inter};
         CGPT_TRY(cgpt_linear_backward_weight_fused(dws, dys, sv->norm, outs, 2, m.rows, m.d, 0, dt, stream));
     }
+    if (!with_norm) return CGPT_OK;     // the caller runs the backward of both norms of the block input in one pass
     // grad_in = grad_out + d(ffn_norm)  (the reference's D2D copy + add_inplace, :678-681)
     return cgpt_rmsnorm_backward(grad_in, g->ffn_norm, ws.d_ffn_norm_in, in, w->ffn_norm, grad_out, nullptr, m.rows, m.d, eps,
                                  dt, stream);
@@ -189,14 +198,22 @@ extern "C" int cgpt_block_forward(void* out, const void* in, const cgpt_block_pa
     Branches br;
     CGPT_TRY(br.begin(static_cast<cudaStream_t>(stream)));
     CGPT_TRY(br.fork());
+    // one stream: the output and down projections run as one product with the residual (diagnosis builds can switch
+    // that off with CGPT_B200_MERGE_OUT=0 to compare)
+    static const bool merge_out = [] { const char* e = diagnosis_env("CGPT_B200_MERGE_OUT"); return !(e && e[0] == '0'); }();
+    const bool merged = !br.two && merge_out;
+    void* norm_attn = sv->attention_norm_output != nullptr ? sv->attention_norm_output : ws.norm_f;
+    // The attention norm's output is kept only if the caller gave a buffer for it (sv->norm holds the FFN norm's output,
+    // as in the reference). One stream: both norms of the block input in one pass over it, before either branch.
+    const bool dual = !br.two && dual_norm_enabled();
+    if (dual)
+        CGPT_TRY(cgpt_rmsnorm_forward_dual(norm_attn, sv->norm, in, w->attention_norm, w->ffn_norm, m.rows, m.d, eps, dt, stream));
     {   // MLP branch on the same block input (parallel residual), on the side stream
         ScratchLane lane(br.lane());
-        CGPT_TRY(mlp_forward(in, w, sv, ws, m, dt, eps, br.side));
+        CGPT_TRY(mlp_forward(in, w, sv, ws, m, dt, eps, !dual, !merged, br.side));
     }
-    // attention branch on the caller's stream; its norm output is kept only if the caller gave a buffer for it
-    // (sv->norm holds the FFN norm's output, as in the reference)
-    void* norm_attn = sv->attention_norm_output != nullptr ? sv->attention_norm_output : ws.norm_f;
-    CGPT_TRY(cgpt_rmsnorm_forward(norm_attn, in, w->attention_norm, m.rows, m.d, eps, dt, stream));
+    // attention branch on the caller's stream
+    if (!dual) CGPT_TRY(cgpt_rmsnorm_forward(norm_attn, in, w->attention_norm, m.rows, m.d, eps, dt, stream));
     {   // query, key and value projections of the same input as one launch (three in the reference, :496-510)
         void* ys[3] = {sv->query_pre_norm, sv->key_pre_norm, sv->value};
         const void* wts[3] = {w->q_projection, w->k_projection, w->v_projection};
@@ -217,6 +234,17 @@ extern "C" int cgpt_block_forward(void* out, const void* in, const cgpt_block_pa
     }
     CGPT_TRY(cgpt_attention_forward(sv->attention_output, sv->attention_logsumexp, sv->query, sv->key, sv->value, batch,
                                     seq, seq, m.hq, m.hkv, m.hd, 0.0f, 1, position_offset, dt, 0, stream));
+    if (merged) {
+        // out = in + attention_output Wo^T + activated Wdown^T as ONE product chained along K, the block input added in
+        // its epilogue (the reference: two projections and two in-place adds, :541-546 and :580-595)
+        const void* xs[2] = {sv->attention_output, sv->activated};
+        const void* wts[2] = {w->o_projection, w->down_proj};
+        const size_t ins[2] = {m.qdim, m.inter};
+        const int rc = cgpt_linear_forward_sum(out, xs, wts, ins, 2, m.rows, m.d, in, dt, stream);
+        if (rc != CGPT_ERR_OPTION) return rc;
+        // out aliases in and this shape has no adding epilogue: the separate form
+        CGPT_TRY(cgpt_linear_forward(ws.ffn_out, sv->activated, w->down_proj, m.rows, m.inter, m.d, dt, stream));
+    }
     CGPT_TRY(cgpt_linear_forward(ws.attn_proj, sv->attention_output, w->o_projection, m.rows, m.qdim, m.d, dt, stream));
     CGPT_TRY(br.join());
     return cgpt_add(out, in, ws.attn_proj, ws.ffn_out, m.rows * m.d, dt, stream);
@@ -235,9 +263,10 @@ extern "C" int cgpt_block_backward(void* grad_in, const void* grad_out, const vo
     Branches br;
     CGPT_TRY(br.begin(static_cast<cudaStream_t>(stream)));
     CGPT_TRY(br.fork());
+    const bool dual = !br.two && dual_norm_enabled();
     {   // ---- MLP branch on the side stream; it writes grad_in = grad_out + d(ffn_norm)
         ScratchLane lane(br.lane());
-        CGPT_TRY(mlp_backward(grad_in, grad_out, in, w, g, sv, ws, m, dt, eps, br.side));
+        CGPT_TRY(mlp_backward(grad_in, grad_out, in, w, g, sv, ws, m, dt, eps, !dual, br.side));
     }
     // ---- attention branch (:682-747)
     CGPT_TRY(cgpt_linear_backward(ws.d_attn_out, g->o_projection, nullptr, grad_out, sv->attention_output, w->o_projection,
@@ -279,6 +308,9 @@ extern "C" int cgpt_block_backward(void* grad_in, const void* grad_out, const vo
         const size_t outs[3] = {m.qdim, m.kvdim, m.kvdim};
         CGPT_TRY(cgpt_linear_backward_weight_fused(dws, dys, norm_a, outs, 3, m.rows, m.d, 0, dt, stream));
     }
+    if (dual)   // one stream: grad_in = grad_out + d(ffn_norm) + d(attention_norm) in one pass (:678-681, :745-747)
+        return cgpt_rmsnorm_backward_dual(grad_in, g->attention_norm, g->ffn_norm, ws.d_attn_norm_in, ws.d_ffn_norm_in, in,
+                                          w->attention_norm, w->ffn_norm, grad_out, m.rows, m.d, eps, dt, stream);
     // grad_in += d(attention_norm): needs the MLP branch's grad_in
     CGPT_TRY(br.join());
     return cgpt_rmsnorm_backward(grad_in, g->attention_norm, ws.d_attn_norm_in, in, w->attention_norm, grad_in, nullptr,

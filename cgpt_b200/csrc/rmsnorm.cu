@@ -14,6 +14,7 @@
 // (deterministic, no atomics). Algorithmic HBM bytes per row: 3 * hidden * sizeof(T)
 // (+ hidden * sizeof(T) per residual operand).
 #include <cstdlib>
+#include <initializer_list>
 #include <mutex>
 
 #include "common.cuh"
@@ -228,6 +229,7 @@ rmsnorm_dw_reduce_kernel(T* __restrict__ dw, const float* __restrict__ partial, 
 }
 
 #include "rmsnorm_warp.cuh"
+#include "rmsnorm_dual.cuh"
 
 struct Plan {
     int vec, cpt, wpr;
@@ -420,6 +422,120 @@ extern "C" int cgpt_rmsnorm_backward(void* dx, void* dw, const void* dy, const v
         return launch_backward<T, 1>(dx, dw, dy, x, w, residual_a, residual_b, rows, hidden, epsilon, p, s);
     });
     return CGPT_OK;
+}
+
+// Two norms of the same input in one pass (rmsnorm_dual.cuh). Fast path: 16-bit rows of 256..1024 elements, 16-byte
+// aligned; every other shape runs the two single-norm operators one after the other (same results up to the one
+// rounding the fused backward saves).
+namespace cgpt {
+namespace {
+template <typename T>
+int launch_forward_dual(void* y_a, void* y_b, const void* x, const void* w_a, const void* w_b, std::size_t rows, std::size_t hidden,
+                        float eps, cudaStream_t s) {
+    const int cpt = static_cast<int>((hidden / 8 + 31) / 32);
+    const std::size_t need = (rows + 2 * warp_rows::kWarps - 1) / (2 * warp_rows::kWarps);
+    const std::size_t cap = static_cast<std::size_t>(kNumSMs) * 4;
+    const int grid = static_cast<int>(need < cap ? need : cap);
+#define CGPT_RMS_FWD_DUAL(CPT)                                                                                            \
+    warp_rows::rmsnorm_forward_dual_warp_kernel<T, CPT><<<grid, warp_rows::kThreads, 0, s>>>(                             \
+        static_cast<T*>(y_a), static_cast<T*>(y_b), static_cast<const T*>(x), static_cast<const T*>(w_a),                \
+        static_cast<const T*>(w_b), static_cast<long long>(rows), static_cast<int>(hidden), eps)
+    switch (cpt) {
+        case 1: CGPT_RMS_FWD_DUAL(1); break;
+        case 2: CGPT_RMS_FWD_DUAL(2); break;
+        case 3: CGPT_RMS_FWD_DUAL(3); break;
+        default: CGPT_RMS_FWD_DUAL(4); break;
+    }
+#undef CGPT_RMS_FWD_DUAL
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+    return CGPT_OK;
+}
+
+template <typename T, int CPT>
+int launch_backward_dual_cpt(void* dx, float* partial, const void* dy_a, const void* dy_b, const void* x, const void* w_a,
+                             const void* w_b, const void* res, std::size_t rows, std::size_t hidden, float eps, int grid,
+                             cudaStream_t s) {
+    constexpr std::size_t smem = static_cast<std::size_t>(2 * CPT * 2 * warp_rows::kThreads) * sizeof(float4) + 2 * CPT * 32 * sizeof(uint4);
+    static PerDeviceOnce attr_once;
+    if (attr_once.needed()) {
+        CGPT_CUDA_TRY(cudaFuncSetAttribute(warp_rows::rmsnorm_backward_dual_warp_kernel<T, CPT>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        attr_once.done();
+    }
+    warp_rows::rmsnorm_backward_dual_warp_kernel<T, CPT><<<grid, warp_rows::kThreads, smem, s>>>(
+        static_cast<T*>(dx), partial, static_cast<const T*>(dy_a), static_cast<const T*>(dy_b), static_cast<const T*>(x),
+        static_cast<const T*>(w_a), static_cast<const T*>(w_b), static_cast<const T*>(res), static_cast<long long>(rows),
+        static_cast<int>(hidden), eps);
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+    return CGPT_OK;
+}
+
+template <typename T>
+int launch_backward_dual(void* dx, void* dw_a, void* dw_b, const void* dy_a, const void* dy_b, const void* x, const void* w_a,
+                         const void* w_b, const void* res, std::size_t rows, std::size_t hidden, float eps, cudaStream_t s) {
+    const int cpt = static_cast<int>((hidden / 8 + 31) / 32);
+    const std::size_t need = (rows + warp_rows::kWarps - 1) / warp_rows::kWarps;
+    const std::size_t cap = static_cast<std::size_t>(kNumSMs) * 2;
+    const int grid = static_cast<int>(need < cap ? need : cap);
+    void* scratch = nullptr;
+    CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(grid) * 2 * hidden * sizeof(float), s));
+    float* partial = static_cast<float*>(scratch);
+    switch (cpt) {
+        case 1: CGPT_TRY((launch_backward_dual_cpt<T, 1>(dx, partial, dy_a, dy_b, x, w_a, w_b, res, rows, hidden, eps, grid, s))); break;
+        case 2: CGPT_TRY((launch_backward_dual_cpt<T, 2>(dx, partial, dy_a, dy_b, x, w_a, w_b, res, rows, hidden, eps, grid, s))); break;
+        case 3: CGPT_TRY((launch_backward_dual_cpt<T, 3>(dx, partial, dy_a, dy_b, x, w_a, w_b, res, rows, hidden, eps, grid, s))); break;
+        default: CGPT_TRY((launch_backward_dual_cpt<T, 4>(dx, partial, dy_a, dy_b, x, w_a, w_b, res, rows, hidden, eps, grid, s))); break;
+    }
+    warp_rows::dw_reduce_dual_kernel<T><<<static_cast<unsigned>((2 * hidden + 31) / 32), 1024, 0, s>>>(
+        static_cast<T*>(dw_a), static_cast<T*>(dw_b), partial, grid, static_cast<int>(hidden));
+    count_launch();
+    CGPT_LAUNCH_CHECK();
+    return CGPT_OK;
+}
+
+bool dual_fast_path(std::size_t hidden, int dtype, std::initializer_list<const void*> ptrs) {
+    if (dtype != CGPT_DTYPE_F16 && dtype != CGPT_DTYPE_BF16) return false;
+    if (hidden % 8 != 0 || !warp_rows::applicable(hidden, 8, 2)) return false;
+    for (const void* p : ptrs)
+        if (!aligned16(p)) return false;
+    return true;
+}
+}  // namespace
+}  // namespace cgpt
+
+extern "C" int cgpt_rmsnorm_forward_dual(void* y_a, void* y_b, const void* x, const void* w_a, const void* w_b, size_t rows,
+                                         size_t hidden, float epsilon, int dtype, cgpt_stream_t stream) {
+    if (!y_a || !y_b || !x || !w_a || !w_b) return CGPT_ERR_NULL;
+    if (!valid_float_dtype(dtype)) return CGPT_ERR_DTYPE;
+    if (rows == 0 || hidden == 0 || hidden > 0x7fffffffull || rows > (1ull << 40)) return CGPT_ERR_SHAPE;
+    if (!(epsilon > 0.f)) return CGPT_ERR_OPTION;
+    auto s = static_cast<cudaStream_t>(stream);
+    if (dual_fast_path(hidden, dtype, {y_a, y_b, x, w_a, w_b})) {
+        if (dtype == CGPT_DTYPE_F16) return launch_forward_dual<__half>(y_a, y_b, x, w_a, w_b, rows, hidden, epsilon, s);
+        return launch_forward_dual<__nv_bfloat16>(y_a, y_b, x, w_a, w_b, rows, hidden, epsilon, s);
+    }
+    CGPT_TRY(cgpt_rmsnorm_forward(y_a, x, w_a, rows, hidden, epsilon, dtype, stream));
+    return cgpt_rmsnorm_forward(y_b, x, w_b, rows, hidden, epsilon, dtype, stream);
+}
+
+extern "C" int cgpt_rmsnorm_backward_dual(void* dx, void* dw_a, void* dw_b, const void* dy_a, const void* dy_b, const void* x,
+                                          const void* w_a, const void* w_b, const void* residual, size_t rows, size_t hidden,
+                                          float epsilon, int dtype, cgpt_stream_t stream) {
+    if (!dx || !dw_a || !dw_b || !dy_a || !dy_b || !x || !w_a || !w_b) return CGPT_ERR_NULL;
+    if (!valid_float_dtype(dtype)) return CGPT_ERR_DTYPE;
+    if (rows == 0 || hidden == 0 || hidden > 0x7fffffffull || rows > (1ull << 40)) return CGPT_ERR_SHAPE;
+    if (!(epsilon > 0.f)) return CGPT_ERR_OPTION;
+    auto s = static_cast<cudaStream_t>(stream);
+    if (dual_fast_path(hidden, dtype, {dx, dy_a, dy_b, x, w_a, w_b, residual})) {
+        if (dtype == CGPT_DTYPE_F16)
+            return launch_backward_dual<__half>(dx, dw_a, dw_b, dy_a, dy_b, x, w_a, w_b, residual, rows, hidden, epsilon, s);
+        return launch_backward_dual<__nv_bfloat16>(dx, dw_a, dw_b, dy_a, dy_b, x, w_a, w_b, residual, rows, hidden, epsilon, s);
+    }
+    // dx = residual + backward a, then dx += backward b (dx is its own residual in the second call)
+    CGPT_TRY(cgpt_rmsnorm_backward(dx, dw_a, dy_a, x, w_a, residual, nullptr, rows, hidden, epsilon, dtype, stream));
+    return cgpt_rmsnorm_backward(dx, dw_b, dy_b, x, w_b, dx, nullptr, rows, hidden, epsilon, dtype, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -173,6 +173,26 @@ def linear_backward_input_fused(grad_input, grad_outputs, weights, stream=None, 
                                                dtype_code(grad_input), stream_ptr(stream)), "linear_backward_input_fused")
 
 
+def linear_forward_sum(output, inputs, weights, residual=None, stream=None):
+    """output = residual + sum_i inputs[i] @ weights[i].T for up to three projections into the same output, in one pass
+    (cgpt_linear_forward_sum; the end of the reference's parallel-residual block is two projections and two adds)."""
+    import ctypes as C
+    n = len(inputs)
+    _require(1 <= n <= 3 and len(weights) == n, "linear_forward_sum: 1..3 projections")
+    _same_cuda_dtype("linear_forward_sum", output, *inputs, *weights, *([residual] if residual is not None else []))
+    out_f = output.shape[-1]
+    rows = output.numel() // out_f
+    for x, w in zip(inputs, weights):
+        _require(w.dim() == 2 and w.shape[0] == out_f and x.shape[-1] == w.shape[1] and x.numel() == rows * w.shape[1],
+                 "linear_forward_sum: incompatible shapes")
+    _require(residual is None or residual.shape == output.shape, "linear_forward_sum: residual must have the output's shape")
+    xs = (C.c_void_p * n)(*[ptr(t) for t in inputs])
+    ws = (C.c_void_p * n)(*[ptr(t) for t in weights])
+    ins = (C.c_size_t * n)(*[w.shape[1] for w in weights])
+    check(lib.cgpt_linear_forward_sum(ptr(output), xs, ws, ins, n, rows, out_f, ptr(residual) if residual is not None else None,
+                                      dtype_code(output), stream_ptr(stream)), "linear_forward_sum")
+
+
 def gemm(c, a, b, m, n, k, a_layout=0, b_layout=0, accumulate=False, force_simt=False, stream=None):
     """Raw contraction C[m,n] (+)= A B of the library (see cgpt_gemm in include/cgpt_b200.h)."""
     _same_cuda_dtype("gemm", c, a, b)
@@ -277,6 +297,32 @@ def rmsnorm_backward(grad_input, grad_weight, grad_output, input, weight, epsilo
     check(lib.cgpt_rmsnorm_backward(ptr(grad_input), ptr(grad_weight), ptr(grad_output), ptr(input), ptr(weight),
                                     ptr(residual_a), ptr(residual_b), input.shape[0], input.shape[1],
                                     float(epsilon), dtype_code(input), stream_ptr(stream)), "rmsnorm_backward")
+
+
+def rmsnorm_forward_dual(output_a, output_b, input, weight_a, weight_b, epsilon, stream=None):
+    """Both RMSNorms of a parallel-residual block's input in one pass over it (cgpt_rmsnorm_forward_dual)."""
+    _same_cuda_dtype("rmsnorm_forward_dual", output_a, output_b, input, weight_a, weight_b)
+    _require(input.dim() == 2 and output_a.shape == input.shape and output_b.shape == input.shape and weight_a.dim() == 1
+             and weight_a.shape[0] == input.shape[1] and weight_b.shape == weight_a.shape, "rmsnorm_forward_dual: incompatible shapes")
+    check(lib.cgpt_rmsnorm_forward_dual(ptr(output_a), ptr(output_b), ptr(input), ptr(weight_a), ptr(weight_b), input.shape[0],
+                                        input.shape[1], float(epsilon), dtype_code(input), stream_ptr(stream)), "rmsnorm_forward_dual")
+
+
+def rmsnorm_backward_dual(grad_input, grad_weight_a, grad_weight_b, grad_output_a, grad_output_b, input, weight_a, weight_b,
+                          epsilon, residual=None, stream=None):
+    """grad_input = residual + the input gradients of both norms of the same input, and both weight gradients, in one
+    pass (cgpt_rmsnorm_backward_dual)."""
+    extra = [residual] if residual is not None else []
+    _same_cuda_dtype("rmsnorm_backward_dual", grad_input, grad_weight_a, grad_weight_b, grad_output_a, grad_output_b, input,
+                     weight_a, weight_b, *extra)
+    _require(input.dim() == 2 and all(t.shape == input.shape for t in (grad_input, grad_output_a, grad_output_b, *extra))
+             and weight_a.dim() == 1 and weight_a.shape[0] == input.shape[1]
+             and all(t.shape == weight_a.shape for t in (weight_b, grad_weight_a, grad_weight_b)),
+             "rmsnorm_backward_dual: incompatible shapes")
+    check(lib.cgpt_rmsnorm_backward_dual(ptr(grad_input), ptr(grad_weight_a), ptr(grad_weight_b), ptr(grad_output_a),
+                                         ptr(grad_output_b), ptr(input), ptr(weight_a), ptr(weight_b), ptr(residual),
+                                         input.shape[0], input.shape[1], float(epsilon), dtype_code(input), stream_ptr(stream)),
+          "rmsnorm_backward_dual")
 
 
 # ------------------------------------------------------------------------------------------------ RoPE

@@ -136,6 +136,17 @@ int cgpt_linear_swiglu_forward(void* gate, void* up, void* activated, const void
 int cgpt_linear_backward_input_fused(void* dx, const void* const* dy, const void* const* w,
                                      const size_t* out_features, size_t count, size_t rows, size_t in_features,
                                      int accumulate_input, int dtype, cgpt_stream_t stream);
+/* Sum of `count` (1..3) projections into the same output, plus an optional residual, in one pass:
+ *      Y[rows,out] = R[rows,out] + sum_i X_i[rows,in_i] W_i[out,in_i]^T.
+ * No single counterpart in the reference: it is the end of the parallel-residual block, where the reference runs the
+ * output projection, the down projection and two in-place adds (src/core/transformer_block.cu:541-546, 580-595). The
+ * products share the fp32 accumulator and the residual is added to it before the one rounding to the storage dtype.
+ * x, w: arrays of `count` device pointers (host arrays); in_features: `count` sizes; residual may be NULL. Y may alias
+ * R only where the tensor-core epilogue adds it (16-bit, out % 64 == 0, rows >= 256): otherwise the product is written
+ * first and R added by an elementwise pass, and aliasing returns CGPT_ERR_OPTION. */
+int cgpt_linear_forward_sum(void* y, const void* const* x, const void* const* w, const size_t* in_features,
+                            size_t count, size_t rows, size_t out_features, const void* residual, int dtype,
+                            cgpt_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Grouped-query softmax attention, forward with saved log-sum-exp and backward.
@@ -193,6 +204,18 @@ int cgpt_rmsnorm_backward(void* dx, void* dw, const void* dy, const void* x, con
 int cgpt_rmsnorm_backward_noalloc(void* dx, void* dw, const void* dy, const void* x, const void* w,
                                   const void* residual_a, const void* residual_b, size_t rows,
                                   size_t hidden, float epsilon, int dtype, cgpt_stream_t stream);
+/* Both RMSNorms of a parallel-residual block's input in one pass (the attention branch's and the MLP branch's norm read
+ * the same x and share rsqrt(mean(x^2) + eps); reference src/core/transformer_block.cu:483-487, :556-560 forward and
+ * :678-681, :745-747 backward, where they are separate calls plus a copy and two in-place adds):
+ *   forward   y_a = rmsnorm(x; w_a), y_b = rmsnorm(x; w_b)
+ *   backward  dx = residual + rmsnorm_backward(dy_a; x, w_a) + rmsnorm_backward(dy_b; x, w_b), dw_a, dw_b
+ * with the three terms of dx summed in fp32 and rounded once. residual may be NULL; dx may alias it. 16-bit rows of
+ * 256..1024 elements take the one-pass kernels, every other shape runs the single-norm operators one after the other. */
+int cgpt_rmsnorm_forward_dual(void* y_a, void* y_b, const void* x, const void* w_a, const void* w_b, size_t rows,
+                              size_t hidden, float epsilon, int dtype, cgpt_stream_t stream);
+int cgpt_rmsnorm_backward_dual(void* dx, void* dw_a, void* dw_b, const void* dy_a, const void* dy_b, const void* x,
+                               const void* w_a, const void* w_b, const void* residual, size_t rows, size_t hidden,
+                               float epsilon, int dtype, cgpt_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
  * RoPE on adjacent pairs (x[2p], x[2p+1]) of the first rotary_dim dims of each head, angle index

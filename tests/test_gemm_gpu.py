@@ -128,6 +128,35 @@ def test_linear_backward_input_fused(ops, dtype, rows, in_f, outs):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,out_f,ins", [(512, 256, (256, 512)), (4096, 1024, (1024, 2048)), (1000, 136, (200, 72)),
+                                            (300, 320, (64,)), (256, 64, (128, 128, 32)), (2048, 1000, (256, 64))])
+def test_linear_forward_sum(ops, dtype, rows, out_f, ins):
+    """Y = R + sum_i X_i W_i^T in one launch against the fp32 sum of matmuls: shapes the CTA-pair epilogue takes (also with
+    a ragged last row tile, 300 rows), shapes that fall back to product + elementwise add (out % 64 != 0, fp32), no
+    residual, and Y aliasing R."""
+    g = torch.Generator(device="cuda").manual_seed(rows + out_f + len(ins))
+    xs = [torch.randn(rows, i, generator=g, device="cuda").to(dtype) for i in ins]
+    ws = [(torch.randn(out_f, i, generator=g, device="cuda") * 0.05).to(dtype) for i in ins]
+    r = torch.randn(rows, out_f, generator=g, device="cuda").to(dtype)
+    prod = sum(x.float() @ w.float().T for x, w in zip(xs, ws))
+    y = torch.full((rows, out_f), float("nan"), device="cuda", dtype=dtype)
+    ops.linear_forward_sum(y, xs, ws, r)
+    torch.cuda.synchronize()
+    assert_close(host(y), host(prod + r.float()), TOL[dtype], f"sum of projections + residual {dtype} {rows}x{out_f} {ins}")
+    y2 = torch.full_like(y, float("nan"))
+    ops.linear_forward_sum(y2, xs, ws)
+    assert_close(host(y2), host(prod), TOL[dtype], "sum of projections")
+    pair_epilogue = dtype != torch.float32 and out_f % 64 == 0 and out_f >= 256 and rows >= 256
+    y3 = r.clone()
+    if pair_epilogue:      # in place over the residual: every element is read by the thread that later stores its tile row
+        ops.linear_forward_sum(y3, xs, ws, y3)
+        assert torch.equal(y3, y)
+    else:
+        with pytest.raises(Exception):
+            ops.linear_forward_sum(y3, xs, ws, y3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("rows,in_f,inter", [(256, 128, 128), (4096, 1024, 2048), (1000, 136, 200), (384, 256, 688)])
 def test_linear_swiglu_forward(ops, dtype, rows, in_f, inter):
     """Fused gate/up/activation against the three separate operators (same rounding points) and the fp32 matmul."""

@@ -253,8 +253,10 @@ def test_loss_after_50_identical_steps(M):
 
 
 def test_two_stream_branches_match_one_stream():
-    """The block's MLP branch on the library's side stream (fork/join by events, also inside a captured graph) gives
-    bit-identical gradients and weights to the single-stream order."""
+    """The block's MLP branch on the library's side stream (fork/join by events): eager and captured runs are bit-identical
+    to each other. Against the single-stream order only the end of the block differs: one stream sums the output and down
+    projections and the residual in one fp32 accumulator (one rounding), two streams round each projection before the
+    add, so those runs agree to the rounding of a 16-bit activation."""
     from cgpt_b200 import _lib
     from cgpt_b200 import model as M, optim as OPT
     from cgpt_b200.train import TrainStep
@@ -274,9 +276,13 @@ def test_two_stream_branches_match_one_stream():
             results.append((loss, ts.storage.flat_gradients.clone(), ts.storage.token_embedding.clone()))
         finally:
             _lib.check(_lib.lib.cgpt_b200_set_branch_streams(0), "set_branch_streams")
-    for loss, grads, emb in results[1:]:
-        assert loss == results[0][0]
-        assert torch.equal(grads, results[0][1]) and torch.equal(emb, results[0][2])
+    assert results[2][0] == results[1][0]
+    assert torch.equal(results[2][1], results[1][1]) and torch.equal(results[2][2], results[1][2])
+    assert abs(results[1][0] - results[0][0]) <= 1e-4
+    assert_close(host(results[1][1]), host(results[0][1]), 1e-2, "gradients, two streams vs one", metric="max")
+    # AdamW's first updates are lr * g / (|g| + eps): an element whose gradient is near zero may move by lr in either
+    # direction, so after 3 steps two runs whose gradients differ by a rounding differ by at most 2 * lr * 3 per weight
+    assert float((results[1][2].float() - results[0][2].float()).abs().max()) <= 2 * 3e-4 * 3 * 1.05
 
 
 def test_large_config_shapes_step_is_finite_and_reproducible():

@@ -50,6 +50,37 @@ def test_rmsnorm_forward_backward(ops, rows, hidden, dt):
     assert torch.equal(dx, dx2) and torch.equal(dw, dw2)
 
 
+@pytest.mark.parametrize("rows,hidden,dt", [(300, 1024, "f16"), (77, 768, "f16"), (1000, 256, "bf16"), (257, 520, "f16"),
+                                            (33, 2048, "bf16"), (5, 1024, "f32"), (64, 100, "f16")])
+@pytest.mark.parametrize("with_residual", [True, False])
+def test_rmsnorm_dual(ops, rows, hidden, dt, with_residual):
+    """Both norms of one input in one pass against the oracle and against the single-norm operators: the forward is
+    bit-identical to two single calls; the backward sums residual + both input gradients in fp32 with one rounding, so
+    it agrees with the oracle's fp32 sum (and with the chained single calls to a rounding of the storage dtype).
+    Shapes of the one-pass kernels (16-bit, 256..1024 columns) and shapes that fall back to the single operators."""
+    r = rng(rows + hidden)
+    x, da, db, res = (dev(r.standard_normal((rows, hidden)), dt) for _ in range(4))
+    wa, wb = dev(1 + 0.05 * r.standard_normal(hidden), dt), dev(1 + 0.05 * r.standard_normal(hidden), dt)
+    ya, yb, ya1, yb1 = (torch.full_like(x, float("nan")) for _ in range(4))
+    ops.rmsnorm_forward_dual(ya, yb, x, wa, wb, 1e-5)
+    ops.rmsnorm_forward(ya1, x, wa, 1e-5); ops.rmsnorm_forward(yb1, x, wb, 1e-5)
+    assert torch.equal(ya, ya1) and torch.equal(yb, yb1)
+    dx, dwa, dwb = torch.full_like(x, float("nan")), torch.full_like(wa, float("nan")), torch.full_like(wb, float("nan"))
+    ops.rmsnorm_backward_dual(dx, dwa, dwb, da, db, x, wa, wb, 1e-5, residual=res if with_residual else None)
+    ea, ewa = O.rmsnorm_backward(rounded(da), rounded(x), rounded(wa), 1e-5)
+    eb, ewb = O.rmsnorm_backward(rounded(db), rounded(x), rounded(wb), 1e-5)
+    want = ea + eb + (rounded(res) if with_residual else 0.0)
+    assert_close(host(dx), want, TOL[dt], "dual dx")
+    assert_close(host(dwa), ewa, TOL[dt] * 2, "dual dw a"); assert_close(host(dwb), ewb, TOL[dt] * 2, "dual dw b")
+    dw1 = torch.empty_like(wa)
+    ops.rmsnorm_backward(torch.empty_like(x), dw1, da, x, wa, 1e-5)
+    assert torch.equal(dw1, dwa)       # same partial sums, same order
+    if with_residual:                  # in place over the residual
+        dx2 = res.clone()
+        ops.rmsnorm_backward_dual(dx2, dwa, dwb, da, db, x, wa, wb, 1e-5, residual=dx2)
+        assert torch.equal(dx2, dx)
+
+
 def test_rmsnorm_backward_residuals(ops):
     r = rng(3)
     x, dy, a, b = (dev(r.standard_normal((257, 1024)), "f16") for _ in range(4))
