@@ -58,6 +58,11 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<std::uintptr_t>(
 // stream capture: a growth request while the stream is capturing returns an error instead).
 // Every kernel that needs global scratch and was not handed a caller workspace takes it from here.
 int scratch_get(void** out, std::size_t bytes, cudaStream_t stream);
+// CTAs of `kernel` (with this block size and dynamic shared memory) that one SM holds at a time, from the occupancy
+// calculator, cached per (kernel, device). Grid-stride kernels size their grid as kNumSMs * this, so that every CTA is
+// resident from the start: a grid of, say, 4 CTAs per SM on a kernel that fits 3 runs a last third of the work at a third
+// of the occupancy.
+int resident_ctas_per_sm(const void* kernel, int threads, std::size_t dynamic_smem);
 
 // Holds `bytes` of the arena for the lifetime of the object, so that ops called meanwhile (which use
 // scratch_get themselves) are placed behind it. `inner_headroom` is the most scratch those inner ops may

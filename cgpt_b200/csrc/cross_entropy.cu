@@ -166,7 +166,10 @@ int softmax_grad_rows(float* row_loss, void* logits_to_grad, const float2* parti
                       float gradient_scale, int dtype, cudaStream_t s) {
     if (dtype != CGPT_DTYPE_F16 && dtype != CGPT_DTYPE_BF16) return CGPT_ERR_UNSUPPORTED;
     if (vocab % 8 != 0 || !aligned16(logits_to_grad) || vocab > 0x7fffffffll || tiles < 1) return CGPT_ERR_UNSUPPORTED;
-    const unsigned grid = static_cast<unsigned>(rows < kNumSMs * 8ll ? rows : kNumSMs * 8ll);
+    const void* kernel = dtype == CGPT_DTYPE_F16 ? reinterpret_cast<const void*>(softmax_grad_rows_kernel<__half>)
+                                                 : reinterpret_cast<const void*>(softmax_grad_rows_kernel<__nv_bfloat16>);
+    const long long resident = static_cast<long long>(kNumSMs) * resident_ctas_per_sm(kernel, kTileGradThreads, 0);
+    const unsigned grid = static_cast<unsigned>(rows < resident ? rows : resident);
     if (dtype == CGPT_DTYPE_F16)
         softmax_grad_rows_kernel<__half><<<grid, kTileGradThreads, 0, s>>>(row_loss, static_cast<__half*>(logits_to_grad), partial,
                                                                           target_logit, targets, rows, static_cast<int>(vocab), tiles,

@@ -108,9 +108,11 @@ add_kernel(T* out, const T* a, const T* b, const T* c, long long count) {
     }
 }
 
-inline unsigned stream_grid(long long count, int vec) {
+// Grid of a grid-stride kernel of 256 threads: enough CTAs for the elements, at most what the SMs hold at a time.
+template <typename Kernel>
+inline unsigned stream_grid(Kernel kernel, long long count, int vec) {
     long long blocks = (count + 256ll * vec - 1) / (256ll * vec);
-    const long long cap = static_cast<long long>(kNumSMs) * 16;
+    const long long cap = static_cast<long long>(kNumSMs) * resident_ctas_per_sm(reinterpret_cast<const void*>(kernel), 256, 0);
     if (blocks > cap) blocks = cap;
     return static_cast<unsigned>(blocks < 1 ? 1 : blocks);
 }
@@ -129,10 +131,10 @@ extern "C" int cgpt_swiglu_forward(void* y, const void* gate, const void* up, si
     CGPT_DISPATCH_DTYPE(dtype, T, {
         constexpr int V = 16 / sizeof(T);
         if (al)
-            swiglu_forward_kernel<T, V><<<stream_grid(count, V), 256, 0, s>>>(
+            swiglu_forward_kernel<T, V><<<stream_grid(swiglu_forward_kernel<T, V>, count, V), 256, 0, s>>>(
                 static_cast<T*>(y), static_cast<const T*>(gate), static_cast<const T*>(up), static_cast<long long>(count));
         else
-            swiglu_forward_kernel<T, 1><<<stream_grid(count, 1), 256, 0, s>>>(
+            swiglu_forward_kernel<T, 1><<<stream_grid(swiglu_forward_kernel<T, 1>, count, 1), 256, 0, s>>>(
                 static_cast<T*>(y), static_cast<const T*>(gate), static_cast<const T*>(up), static_cast<long long>(count));
         count_launch();
         CGPT_LAUNCH_CHECK();
@@ -150,11 +152,11 @@ extern "C" int cgpt_swiglu_backward(void* dgate, void* dup, const void* dy, cons
     CGPT_DISPATCH_DTYPE(dtype, T, {
         constexpr int V = 16 / sizeof(T);
         if (al)
-            swiglu_backward_kernel<T, V><<<stream_grid(count, V), 256, 0, s>>>(
+            swiglu_backward_kernel<T, V><<<stream_grid(swiglu_backward_kernel<T, V>, count, V), 256, 0, s>>>(
                 static_cast<T*>(dgate), static_cast<T*>(dup), static_cast<const T*>(dy), static_cast<const T*>(gate),
                 static_cast<const T*>(up), static_cast<long long>(count), accumulate_gate, accumulate_up);
         else
-            swiglu_backward_kernel<T, 1><<<stream_grid(count, 1), 256, 0, s>>>(
+            swiglu_backward_kernel<T, 1><<<stream_grid(swiglu_backward_kernel<T, 1>, count, 1), 256, 0, s>>>(
                 static_cast<T*>(dgate), static_cast<T*>(dup), static_cast<const T*>(dy), static_cast<const T*>(gate),
                 static_cast<const T*>(up), static_cast<long long>(count), accumulate_gate, accumulate_up);
         count_launch();
@@ -172,11 +174,11 @@ extern "C" int cgpt_add(void* out, const void* a, const void* b, const void* c, 
     CGPT_DISPATCH_DTYPE(dtype, T, {
         constexpr int V = 16 / sizeof(T);
         if (al)
-            add_kernel<T, V><<<stream_grid(count, V), 256, 0, s>>>(
+            add_kernel<T, V><<<stream_grid(add_kernel<T, V>, count, V), 256, 0, s>>>(
                 static_cast<T*>(out), static_cast<const T*>(a), static_cast<const T*>(b), static_cast<const T*>(c),
                 static_cast<long long>(count));
         else
-            add_kernel<T, 1><<<stream_grid(count, 1), 256, 0, s>>>(
+            add_kernel<T, 1><<<stream_grid(add_kernel<T, 1>, count, 1), 256, 0, s>>>(
                 static_cast<T*>(out), static_cast<const T*>(a), static_cast<const T*>(b), static_cast<const T*>(c),
                 static_cast<long long>(count));
         count_launch();

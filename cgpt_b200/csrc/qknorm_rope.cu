@@ -239,7 +239,9 @@ extern "C" int cgpt_qknorm_rope_forward(void* q, void* k, const void* q_pre, con
                     static_cast<int>(kv_heads), static_cast<int>(head_dim), static_cast<int>(rotary_dim),
                     static_cast<int>(position_offset), epsilon};
     const FastDiv div_qh(static_cast<unsigned>(q_heads)), div_kh(static_cast<unsigned>(kv_heads)), div_seq(static_cast<unsigned>(seq));
-    const unsigned grid = kNumSMs * 4;
+    const void* kernel = dtype == CGPT_DTYPE_F16 ? reinterpret_cast<const void*>(qknorm_rope_kernel<__half, false, kFwdUnroll>)
+                                                 : reinterpret_cast<const void*>(qknorm_rope_kernel<__nv_bfloat16, false, kFwdUnroll>);
+    const unsigned grid = kNumSMs * resident_ctas_per_sm(kernel, kQkThreads, 0);    // every CTA resident: no partial last wave
     if (dtype == CGPT_DTYPE_F16)
         qknorm_rope_kernel<__half, false, kFwdUnroll><<<grid, kQkThreads, 0, s>>>(
             static_cast<__half*>(q), static_cast<__half*>(k), static_cast<const __half*>(q_pre), static_cast<const __half*>(k_pre),
@@ -278,7 +280,9 @@ extern "C" int cgpt_qknorm_rope_backward(void* dq_pre, void* dk_pre, void* dq_no
                     static_cast<int>(kv_heads), static_cast<int>(head_dim), static_cast<int>(rotary_dim),
                     static_cast<int>(position_offset), epsilon};
     const FastDiv div_qh(static_cast<unsigned>(q_heads)), div_kh(static_cast<unsigned>(kv_heads)), div_seq(static_cast<unsigned>(seq));
-    const unsigned grid = kNumSMs * 4;
+    const void* kernel = dtype == CGPT_DTYPE_F16 ? reinterpret_cast<const void*>(qknorm_rope_kernel<__half, true, kBwdUnroll>)
+                                                 : reinterpret_cast<const void*>(qknorm_rope_kernel<__nv_bfloat16, true, kBwdUnroll>);
+    const unsigned grid = kNumSMs * resident_ctas_per_sm(kernel, kQkThreads, 0);
     void* scratch = nullptr;
     CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(grid) * 2 * head_dim * sizeof(float), s));
     float* partial = static_cast<float*>(scratch);

@@ -434,7 +434,7 @@ int launch_forward_dual(void* y_a, void* y_b, const void* x, const void* w_a, co
                         float eps, cudaStream_t s) {
     const int cpt = static_cast<int>((hidden / 8 + 31) / 32);
     const std::size_t need = (rows + 2 * warp_rows::kWarps - 1) / (2 * warp_rows::kWarps);
-    const std::size_t cap = static_cast<std::size_t>(kNumSMs) * 4;
+    const std::size_t cap = static_cast<std::size_t>(kNumSMs) * 2;      // __launch_bounds__(kThreads, 2): two resident CTAs per SM
     const int grid = static_cast<int>(need < cap ? need : cap);
 #define CGPT_RMS_FWD_DUAL(CPT)                                                                                            \
     warp_rows::rmsnorm_forward_dual_warp_kernel<T, CPT><<<grid, warp_rows::kThreads, 0, s>>>(                             \

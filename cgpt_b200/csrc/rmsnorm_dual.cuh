@@ -16,7 +16,7 @@ namespace warp_rows {
 
 // y_a = x * inv * w_a, y_b = x * inv * w_b; two rows per warp per trip.
 template <typename T, int CPT>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)
 rmsnorm_forward_dual_warp_kernel(T* __restrict__ y_a, T* __restrict__ y_b, const T* __restrict__ x, const T* __restrict__ w_a,
                                  const T* __restrict__ w_b, long long rows, int hidden, float epsilon) {
     constexpr int R = 2;

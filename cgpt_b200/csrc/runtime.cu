@@ -2,6 +2,7 @@
 #include <atomic>
 #include <cstdlib>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 #include "launch_counter.h"
@@ -73,6 +74,24 @@ ScratchFrame::~ScratchFrame() { t_frame_offset -= held_; }
 
 ScratchLane::ScratchLane(int lane) : previous_(t_lane) { t_lane = lane; }
 ScratchLane::~ScratchLane() { t_lane = previous_; }
+
+int resident_ctas_per_sm(const void* kernel, int threads, std::size_t dynamic_smem) {
+    struct Entry { const void* kernel; int device, threads; std::size_t smem; int ctas; };
+    static std::mutex mutex;
+    static std::vector<Entry> cache;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return 1;
+    std::lock_guard<std::mutex> lock(mutex);
+    for (const Entry& e : cache)
+        if (e.kernel == kernel && e.device == device && e.threads == threads && e.smem == dynamic_smem) return e.ctas;
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, dynamic_smem) != cudaSuccess || n < 1) {
+        cudaGetLastError();
+        n = 1;
+    }
+    cache.push_back(Entry{kernel, device, threads, dynamic_smem, n});
+    return n;
+}
 
 bool branch_streams_enabled() {
     int v = g_branch_streams.load(std::memory_order_relaxed);
