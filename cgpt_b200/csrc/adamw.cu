@@ -277,7 +277,11 @@ extern "C" int cgpt_adamw_create(cgpt_adamw_workspace** out, const cgpt_adamw_te
     auto* ws = new cgpt_adamw_workspace();
     ws->n_tensors = count;
     ws->n_chunks = static_cast<unsigned int>(host_chunks.size());
-    const unsigned int cap = kNumSMs * 8;
+    // every CTA of the chunk loops resident from the start (the smaller of what the two kernels fit per SM)
+    int per_sm = resident_ctas_per_sm(reinterpret_cast<const void*>(adamw_update_kernel), kAdamThreads, 0);
+    const int per_sm_stats = resident_ctas_per_sm(reinterpret_cast<const void*>(adamw_stats_kernel), kAdamThreads, 0);
+    if (per_sm_stats < per_sm) per_sm = per_sm_stats;
+    const unsigned int cap = static_cast<unsigned int>(kNumSMs * per_sm);
     ws->grid = static_cast<int>(ws->n_chunks < cap ? ws->n_chunks : cap);
     auto s = static_cast<cudaStream_t>(stream);
     auto fail = [&](cudaError_t e) { cgpt_adamw_destroy(ws); return -static_cast<int>(e); };

@@ -1,6 +1,7 @@
 """`python -m cgpt_b200.profile_ops <op> [--iters N]`: launches one operator a few times on inputs larger
 than L2 but a few hundred MB at most, so that `ncu -k regex:<kernel>` captures of it end by themselves.
-Ops: gemm_fwd, gemm_dx, gemm_dw, attention_fwd, attention_bwd, rmsnorm_bwd, swiglu_bwd, rope_bwd, embedding_bwd, adamw,
+Ops: gemm_fwd, gemm_dx, gemm_dw, linear_sum (output + down projection + residual as one product), attention_fwd,
+attention_bwd, rmsnorm_bwd, rmsnorm_dual_fwd, rmsnorm_dual_bwd (both norms of one input in one pass), swiglu_bwd, rope_bwd, embedding_bwd, adamw,
 cross_entropy, cce (one 8192-row chunk of the cut cross-entropy at hidden 1024, vocabulary 32000; --cce-form 1|2|3),
 qknorm_fwd, qknorm_bwd.
 Prints the CUDA-event time per launch (taken without a profiler attached it is the number to quote)."""
@@ -64,6 +65,24 @@ def main() -> None:
         dx, dw = torch.empty_like(x), torch.empty_like(w)
         ms = _run(lambda: ops.rmsnorm_backward(dx, dw, dy, x, w, 1e-5), a.iters)
         print(f"rmsnorm_bwd {T}x{d}: {ms * 1e3:.1f} us, {3.0 * T * d * 2 / ms / 1e6:.0f} GB/s algorithmic")
+    elif a.op == "rmsnorm_dual_bwd":
+        x, da, db, res = h(T, d), h(T, d), h(T, d), h(T, d)
+        wa, wb = torch.ones(d, device="cuda", dtype=torch.float16), torch.ones(d, device="cuda", dtype=torch.float16)
+        dx, dwa, dwb = torch.empty_like(x), torch.empty_like(wa), torch.empty_like(wb)
+        ms = _run(lambda: ops.rmsnorm_backward_dual(dx, dwa, dwb, da, db, x, wa, wb, 1e-5, residual=res), a.iters)
+        print(f"rmsnorm_dual_bwd {T}x{d} (+ residual): {ms * 1e3:.1f} us, {5.0 * T * d * 2 / ms / 1e6:.0f} GB/s algorithmic")
+    elif a.op == "rmsnorm_dual_fwd":
+        x = h(T, d)
+        wa, wb = torch.ones(d, device="cuda", dtype=torch.float16), torch.ones(d, device="cuda", dtype=torch.float16)
+        ya, yb = torch.empty_like(x), torch.empty_like(x)
+        ms = _run(lambda: ops.rmsnorm_forward_dual(ya, yb, x, wa, wb, 1e-5), a.iters)
+        print(f"rmsnorm_dual_fwd {T}x{d}: {ms * 1e3:.1f} us, {3.0 * T * d * 2 / ms / 1e6:.0f} GB/s algorithmic")
+    elif a.op == "linear_sum":
+        xa, xb, res = h(T, d), h(T, I), h(T, d)
+        wo, wd = h(d, d) * 0.02, h(d, I) * 0.02
+        y = torch.empty_like(res)
+        ms = _run(lambda: ops.linear_forward_sum(y, [xa, xb], [wo, wd], res), a.iters)
+        print(f"linear_sum {T}x{d}x({d}+{I}) + residual: {ms * 1e3:.1f} us, {2.0 * T * d * (d + I) / ms / 1e9:.1f} TFLOP/s")
     elif a.op == "swiglu_bwd":
         g, u, dy = h(T, I), h(T, I), h(T, I)
         dg, du = torch.empty_like(g), torch.empty_like(g)
