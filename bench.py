@@ -368,9 +368,7 @@ def run_ours(args) -> None:
             line["cce"]["frac_of_measured_burst_peak"] = line["cce"]["tflops"] / burst if burst else None
             # the three forms of a chunk side by side: row kernel over stored logits, tile statistics from the logits
             # product's epilogue, logits never stored (recomputed; four products for the three credited)
-            names = {1: "rows", 2: "tiles", 3: "recompute"}
-            line["cce"]["forms"] = {names[f]: {k: v for k, v in profiling.time_cut_cross_entropy(32768, 768, 32000, form=f).items()
-                                               if k in ("us", "tflops")} for f in (1, 2, 3)}
+            line["cce"]["forms"] = profiling.time_cut_cross_entropy_forms(32768, 768, 32000)
         except Exception as exc:
             line["cce"] = {"error": repr(exc)}
         if world == 1:

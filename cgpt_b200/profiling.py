@@ -83,6 +83,39 @@ def time_cut_cross_entropy(rows: int, hidden: int, vocab: int, iters: int = 5, f
             "algorithmic_bytes": 2.0 * 2 * (rows * hidden + vocab * hidden) + 4 * rows, "loss": float(loss.item())}
 
 
+def time_cut_cross_entropy_forms(rows: int, hidden: int, vocab: int, rounds: int = 3, iters: int = 3) -> dict:
+    """The three forms of the loss layer side by side on the same inputs (see time_cut_cross_entropy). The forms are timed
+    in turn, `rounds` times over, and the median per form is reported, so that a drifting power-capped clock does not
+    favour whichever form runs first."""
+    from . import model as M
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(rows, hidden, generator=g, device="cuda").half()
+    c = (torch.randn(vocab, hidden, generator=g, device="cuda") * 0.02).half()
+    t = torch.randint(0, vocab, (rows,), generator=g, device="cuda", dtype=torch.int32)
+    loss = torch.zeros(1, device="cuda")
+    dx, dc = torch.empty_like(x), torch.empty_like(c)
+    names = {1: "rows", 2: "tiles", 3: "recompute"}
+    times = {f: [] for f in names}
+    for f in names:     # warm-up: scratch arena, kernel attributes
+        M.cut_cross_entropy_forward_backward(loss, dx, dc, x, c, t, rows, None, 1024.0, form=f)
+    torch.cuda.synchronize()
+    for _ in range(rounds):
+        for f in names:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                M.cut_cross_entropy_forward_backward(loss, dx, dc, x, c, t, rows, None, 1024.0, form=f)
+            e1.record()
+            torch.cuda.synchronize()
+            times[f].append(e0.elapsed_time(e1) / iters)
+    flops = 3.0 * 2.0 * rows * vocab * hidden
+    out = {}
+    for f, name in names.items():
+        ms = sorted(times[f])[len(times[f]) // 2]
+        out[name] = {"us": ms * 1e3, "tflops": flops / ms / 1e9}
+    return out
+
+
 def time_attention_backward(batch: int, seq: int, q_heads: int, kv_heads: int, head_dim: int, iters: int = 10) -> dict:
     """Standalone causal GQA attention backward (flash_gqa_attention_backward_with_lse) on seeded N(0,1) fp16 inputs, O and
     the logsumexp taken from the forward on the same inputs. Time: CUDA events around `iters` back-to-back calls after 3
