@@ -127,6 +127,44 @@ splitk_reduce_kernel(T* __restrict__ out, const float* __restrict__ partial, lon
     }
 }
 
+// The same for up to three outputs whose partial tiles sit one after the other in the partial buffer (the weight gradients
+// of projections that share their input, computed by one launch): one reduce launch instead of one per output.
+// Every count is a multiple of 4 (host check).
+struct ReduceGroups {
+    void* out[3];
+    long long first[3];    // offset of the group's first element inside one split's partial block
+    long long end[3];      // running end of the groups in the concatenated index space
+    int groups;
+};
+template <typename T>
+__global__ void __launch_bounds__(256)
+splitk_reduce_groups_kernel(ReduceGroups g, const float* __restrict__ partial, long long split_stride, int splits, int accumulate) {
+    const long long total = g.end[g.groups - 1];
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 4;
+    for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < total; i += stride) {
+        int grp = 0;
+        long long begin = 0;
+        if (g.groups > 1 && i >= g.end[0]) { grp = 1; begin = g.end[0]; }
+        if (g.groups > 2 && i >= g.end[1]) { grp = 2; begin = g.end[1]; }
+        const long long local = i - begin;
+        const float* src = partial + g.first[grp] + local;
+        float4 acc = *reinterpret_cast<const float4*>(src);
+        for (int s = 1; s < splits; ++s) {
+            const float4 p = *reinterpret_cast<const float4*>(src + s * split_stride);
+            acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+        }
+        float v[4] = {acc.x, acc.y, acc.z, acc.w};
+        T* out = static_cast<T*>(g.out[grp]) + local;
+        if (accumulate) {
+            float old[4];
+            load_vec<T, 4>(old, out);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] += old[e];
+        }
+        store_vec<T, 4>(out, v);
+    }
+}
+
 // ------------------------------------------------------------------------------------- SIMT fallback
 // C[m,n] (+)= sum_k A(m,k) * B(n,k) with arbitrary element strides; 64x64 tile, 4x4 per thread, fp32.
 template <typename T>
@@ -433,13 +471,13 @@ int launch_tc_groups(T* const* Cs, const T* A, const T* const* Bs, const int* Ns
 // dW_g[M_g, N] (+)= dY_g[K, M_g]^T X[K, N] for up to three weight gradients that share X, as ONE launch: the M tiles of
 // all groups form one work list (both operands MN-major, K = tokens). With few tiles K is split as in the plain
 // launcher: fp32 partials [split][sum of padded M_g][N], then one fixed-order reduce per group.
-template <typename T, bool PAIR = false>
+template <typename T>
 int launch_tc_mgroups(T* const* Cs, const T* const* As, const T* B, const int* Ms, int groups, int N, int K, int accumulate,
                       int dtype, cudaStream_t s) {
     constexpr int BN = 256;
     using Cfg = GemmCfg<BN>;
-    constexpr int kTileM = PAIR ? kPairBM : BM;
-    constexpr int kWorkers = PAIR ? kNumSMs / 2 : kNumSMs;
+    constexpr int kTileM = BM;
+    constexpr int kWorkers = kNumSMs;
     if (groups < 1 || groups > kMaxKSegments || !aligned16(B) || N % 8 != 0 || N < BN || K < 32) return CGPT_ERR_UNSUPPORTED;
     GemmOperands ops;
     GemmOutputs outs;
@@ -461,7 +499,6 @@ int launch_tc_mgroups(T* const* Cs, const T* const* As, const T* B, const int* M
         CGPT_TRY(make_tensor_map(&ops.b[i], dtype, B, 2, b_dims, b_st, mn_box));
         const std::uint64_t c_dims[2] = {static_cast<std::uint64_t>(N), static_cast<std::uint64_t>(Ms[g])};
         CGPT_TRY(make_tensor_map(&outs.c[i], dtype, Cs[g], 2, c_dims, b_st, c_box));
-        if (PAIR && Ms[g] < kPairBM) return CGPT_ERR_UNSUPPORTED;
         if (i < groups) {
             m_first[i] = tiles_m * kTileM;
             tiles_m += (Ms[g] + kTileM - 1) / kTileM;
@@ -492,25 +529,16 @@ int launch_tc_mgroups(T* const* Cs, const T* const* As, const T* B, const int* M
         CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(splits) * m_pad * N * sizeof(float), s));
         partial = static_cast<float*>(scratch);
     }
-    void (*pkernel)(GemmOperands, GemmOutputs, T*, float*, int, int, int, int, int, int, int, int) = nullptr;
-    int smem_bytes = Cfg::kSmemBytes;
-    if constexpr (PAIR) {
-        pkernel = gemm_tcgen05_pair_kernel<T, true, true>;
-        smem_bytes = PairCfg::kSmemBytes;
-    } else {
-        pkernel = gemm_tcgen05_persistent_kernel<T, BN, true, true>;
-    }
+    // single-CTA tiles: the CTA-pair kernel measured 15 % slower on these products (both operands MN-major, split-K)
+    auto* pkernel = gemm_tcgen05_persistent_kernel<T, BN, true, true>;
+    const int smem_bytes = Cfg::kSmemBytes;
     static PerDeviceOnce attr_once;
     if (attr_once.needed()) {
         CGPT_CUDA_TRY(cudaFuncSetAttribute(pkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         attr_once.done();
     }
     const long long units = static_cast<long long>(tiles) * splits;
-    unsigned grid = static_cast<unsigned>(units < kNumSMs ? units : kNumSMs);
-    if (PAIR) {
-        grid = static_cast<unsigned>(pair_grid(reinterpret_cast<const void*>(pkernel), static_cast<int>(units < kNumSMs ? units : kNumSMs)));
-        if (grid == 0) return CGPT_ERR_UNSUPPORTED;
-    }
+    const unsigned grid = static_cast<unsigned>(units < kNumSMs ? units : kNumSMs);
     const bool timed = g_timing.enabled && g_timing.used + 2 <= g_timing.events.size();
     if (timed) CGPT_CUDA_TRY(cudaEventRecord(g_timing.events[g_timing.used], s));
     pkernel<<<grid, kGemmThreads, smem_bytes, s>>>(ops, outs, Cs[0], partial, m_pad, N, total_kb, tiles_m, tiles_n, splits,
@@ -522,18 +550,26 @@ int launch_tc_mgroups(T* const* Cs, const T* const* As, const T* B, const int* M
         g_timing.used += 2;
         g_timing.flops.push_back(flops);
     }
-    if (splits > 1) {
+    if (splits > 1) {   // one reduce launch for all groups (every M_g * N is a multiple of 4: M_g % 8 == 0)
         const long long split_stride = static_cast<long long>(m_pad) * N;
-        for (int g = 0; g < groups; ++g) {
-            const long long mn = static_cast<long long>(Ms[g]) * N;
-            long long blocks = (mn / 4 + 255) / 256;
-            if (blocks > kNumSMs * 8) blocks = kNumSMs * 8;
-            if (blocks < 1) blocks = 1;
-            splitk_reduce_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, s>>>(Cs[g], partial + static_cast<long long>(m_first[g]) * N,
-                                                                                 mn, split_stride, splits, accumulate);
-            count_launch();
-            CGPT_LAUNCH_CHECK();
+        ReduceGroups rg;
+        rg.groups = groups;
+        long long total = 0;
+        for (int g = 0; g < 3; ++g) {
+            const int gg = g < groups ? g : 0;
+            rg.out[g] = Cs[gg];
+            rg.first[g] = static_cast<long long>(m_first[gg]) * N;
+            if (g < groups) total += static_cast<long long>(Ms[g]) * N;
+            rg.end[g] = total;
         }
+        long long blocks = (total / 4 + 255) / 256;
+        const long long cap = static_cast<long long>(kNumSMs) *
+                              resident_ctas_per_sm(reinterpret_cast<const void*>(splitk_reduce_groups_kernel<T>), 256, 0);
+        if (blocks > cap) blocks = cap;
+        if (blocks < 1) blocks = 1;
+        splitk_reduce_groups_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, s>>>(rg, partial, split_stride, splits, accumulate);
+        count_launch();
+        CGPT_LAUNCH_CHECK();
     }
     return CGPT_OK;
 }
