@@ -129,9 +129,12 @@ attention_bwd_prep_kernel(float* __restrict__ delta_t, float* __restrict__ lse2_
             Pack<T, 8> pa, po;
             *reinterpret_cast<uint4*>(&pa) = a[u];
             *reinterpret_cast<uint4*>(&po) = o[u];
+            float fa[8], fo[8];
+            unpack_pack(fa, pa);
+            unpack_pack(fo, po);
             float s = 0.f;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) s = fmaf(to_f32<T>(pa.v[e]), to_f32<T>(po.v[e]), s);
+            for (int e = 0; e < 8; ++e) s = fmaf(fa[e], fo[e], s);
             for (int off = lpr >> 1; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
             if (l == 0 && row < rows) {
                 const int h = static_cast<int>(row % hq);

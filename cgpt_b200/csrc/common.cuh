@@ -135,13 +135,48 @@ struct alignas(sizeof(T) * N) Pack {
     T v[N];
 };
 
+// Pack -> fp32. 16-bit types convert two values per packed register (the pair intrinsics select the half inside the
+// conversion instead of extracting it first): same values as the scalar conversions, fewer instructions.
+template <typename T, int N>
+__device__ __forceinline__ void unpack_pack(float (&out)[N], const Pack<T, N>& pk) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) out[i] = to_f32<T>(pk.v[i]);
+}
+template <int N>
+__device__ __forceinline__ void unpack_pack(float (&out)[N], const Pack<__half, N>& pk) {
+    if constexpr (N % 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < N; i += 2) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pk.v[i]));
+            out[i] = f.x;
+            out[i + 1] = f.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) out[i] = __half2float(pk.v[i]);
+    }
+}
+template <int N>
+__device__ __forceinline__ void unpack_pack(float (&out)[N], const Pack<__nv_bfloat16, N>& pk) {
+    if constexpr (N % 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < N; i += 2) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk.v[i]));
+            out[i] = f.x;
+            out[i + 1] = f.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) out[i] = __bfloat162float(pk.v[i]);
+    }
+}
+
 template <typename T, int N>
 __device__ __forceinline__ void load_vec(float (&out)[N], const T* __restrict__ p) {
     using Raw = typename RawVec<sizeof(T) * N>::type;
     Pack<T, N> pk;
     *reinterpret_cast<Raw*>(&pk) = *reinterpret_cast<const Raw*>(p);
-#pragma unroll
-    for (int i = 0; i < N; ++i) out[i] = to_f32<T>(pk.v[i]);
+    unpack_pack(out, pk);
 }
 
 // Streaming (read-once) variant: bypasses L1 allocation.
@@ -150,8 +185,7 @@ __device__ __forceinline__ void load_vec_stream(float (&out)[N], const T* __rest
     using Raw = typename RawVec<sizeof(T) * N>::type;
     Pack<T, N> pk;
     *reinterpret_cast<Raw*>(&pk) = __ldcs(reinterpret_cast<const Raw*>(p));
-#pragma unroll
-    for (int i = 0; i < N; ++i) out[i] = to_f32<T>(pk.v[i]);
+    unpack_pack(out, pk);
 }
 
 // Round-to-nearest conversion of N floats into a Pack. 16-bit types convert two values per instruction

@@ -116,9 +116,10 @@ cross_entropy_ring_kernel(float* __restrict__ row_loss, T* grad, const T* logits
         for (int c = 0; c < kRingCpt; ++c) {
             Pack<T, 8> pk;
             *reinterpret_cast<uint4*>(&pk) = raw[c];
+            unpack_pack(v[c], pk);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                v[c][e] = fast_exp(to_f32<T>(pk.v[e]) - maximum);
+                v[c][e] = fast_exp(v[c][e] - maximum);
                 local_sum += v[c][e];
             }
         }

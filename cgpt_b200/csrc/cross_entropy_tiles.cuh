@@ -62,8 +62,9 @@ softmax_grad_rows_kernel(float* __restrict__ row_loss, T* grad, const float2* __
                     Pack<T, 8> pk;
                     *reinterpret_cast<uint4*>(&pk) = raw[u];
                     float p[8];
+                    unpack_pack(p, pk);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) p[e] = fast_exp(to_f32<T>(pk.v[e]) - st.x) * k;
+                    for (int e = 0; e < 8; ++e) p[e] = fast_exp(p[e] - st.x) * k;
                     store_vec<T, 8>(dst + c * 8, p);
                 }
             }

@@ -316,8 +316,10 @@ __device__ __forceinline__ void gemm_pair_body(const GemmOperands& ops, const Ge
                         if (res_ok) {
                             Pack<T, 8> pk;
                             *reinterpret_cast<uint4*>(&pk) = res[jj];
+                            float rv[8];
+                            unpack_pack(rv, pk);
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) v[e] += to_f32<T>(pk.v[e]);
+                            for (int e = 0; e < 8; ++e) v[e] += rv[e];
                         }
                         store_vec<T, 8>(reinterpret_cast<T*>(buf_s + trow * 128 + ((jj ^ (trow & 7)) << 4)), v);
                     }

@@ -35,22 +35,23 @@ template <typename T>
 __device__ __forceinline__ void unpack8(float (&out)[8], const uint4& raw) {
     Pack<T, 8> pk;
     *reinterpret_cast<uint4*>(&pk) = raw;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) out[i] = to_f32<T>(pk.v[i]);
+    unpack_pack(out, pk);
 }
 template <typename T>
 __device__ __forceinline__ void unpack4(float (&out)[4], const uint2& raw) {
     Pack<T, 4> pk;
     *reinterpret_cast<uint2*>(&pk) = raw;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) out[i] = to_f32<T>(pk.v[i]);
+    unpack_pack(out, pk);
 }
 
 // Two phases per thread, query rows then key rows, so that a phase has one source tensor, one weight vector and one dw
 // accumulator (no per-element selects). Row r of a phase: token = r / heads_of_phase, head = r % heads_of_phase; both
 // tensors are [tokens, heads, head_dim] contiguous, so the row's offset is simply r * head_dim.
-// A warp works on U groups of 32/(head_dim/8) rows per trip; every 16-byte row load of the trip (x, and dy in the
-// backward pass) is issued before the first value is used: U (2U) independent loads in flight per thread.
+// A warp works on 32/(head_dim/8) runs of U CONSECUTIVE rows per trip (a lane group owns one run); every 16-byte row load
+// of the trip (x, and dy in the backward pass) is issued before the first value is used: U (2U) independent loads in
+// flight per thread. Consecutive rows are the heads of one token, so a lane converts its slice of the rotary tables once
+// per token instead of once per row (8 query heads: one table fetch and conversion per 8 rows), and the token / head of
+// a row follow from the run's first row by counting: one division per run, none per row.
 // Row indices fit 31 bits (checked by the host); divisions by heads and seq use precomputed multipliers.
 template <typename T, bool BACKWARD, int U>
 __global__ void __launch_bounds__(kQkThreads)
@@ -67,7 +68,6 @@ qknorm_rope_kernel(T* __restrict__ out_q, T* __restrict__ out_k, const T* __rest
     const int half_rot = dm.rotary_dim / 2;
     const bool rotate = d0 < dm.rotary_dim;
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-    const uint2 zero2 = make_uint2(0u, 0u);
     const unsigned group = static_cast<unsigned>(rows_per_warp) * U;
     const unsigned warps_total = gridDim.x * (kQkThreads / 32);
     const unsigned warp_id = blockIdx.x * (kQkThreads / 32) + warp;
@@ -86,33 +86,32 @@ qknorm_rope_kernel(T* __restrict__ out_q, T* __restrict__ out_k, const T* __rest
 
         const unsigned trips = (rows + group * warps_total - 1) / (group * warps_total);
         for (unsigned trip = 0; trip < trips; ++trip) {
-            const unsigned base = (trip * warps_total + warp_id) * group;
+            const unsigned r0 = (trip * warps_total + warp_id) * group + sub * U;   // first row of this lane group's run
+            const long long off0 = static_cast<long long>(r0) * dm.head_dim + d0;
             uint4 raw_in[U], raw_x[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const unsigned r = base + u * rows_per_warp + sub;
-                const bool active = r < rows;
-                const long long off = static_cast<long long>(r) * dm.head_dim + d0;
-                raw_in[u] = active ? __ldcs(reinterpret_cast<const uint4*>(in + off)) : zero4;
-                if (BACKWARD) raw_x[u] = active ? __ldcs(reinterpret_cast<const uint4*>(xs + off)) : zero4;
+                const bool active = r0 + u < rows;
+                raw_in[u] = active ? __ldcs(reinterpret_cast<const uint4*>(in + off0 + u * dm.head_dim)) : zero4;
+                if (BACKWARD) raw_x[u] = active ? __ldcs(reinterpret_cast<const uint4*>(xs + off0 + u * dm.head_dim)) : zero4;
             }
+            unsigned token = div_heads.div(r0);
+            unsigned head = r0 - token * div_heads.d;
+            bool fetch_tables = true;           // the run's first row, then every row that starts a new token
+            float c[4] = {0.f, 0.f, 0.f, 0.f}, s[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const unsigned r = base + u * rows_per_warp + sub;
-                const bool active = r < rows;
-                const long long off = static_cast<long long>(r) * dm.head_dim + d0;
+                const bool active = r0 + u < rows;
+                const long long off = off0 + u * dm.head_dim;
                 // the rotary tables are small and stay in L1/L2: fetched here, not ahead, to keep registers for the row data
-                uint2 raw_c = zero2, raw_s = zero2;
-                if (active && rotate) {
-                    const unsigned token = div_heads.div(r);
+                if (fetch_tables && active && rotate) {
                     const unsigned pos = token - div_seq.div(token) * div_seq.d + dm.offset;
                     const long long t = static_cast<long long>(pos) * half_rot + d0 / 2;
-                    raw_c = __ldg(reinterpret_cast<const uint2*>(cos_t + t));
-                    raw_s = __ldg(reinterpret_cast<const uint2*>(sin_t + t));
+                    unpack4<T>(c, __ldg(reinterpret_cast<const uint2*>(cos_t + t)));
+                    unpack4<T>(s, __ldg(reinterpret_cast<const uint2*>(sin_t + t)));
                 }
-                float c[4], s[4];
-                unpack4<T>(c, raw_c);
-                unpack4<T>(s, raw_s);
+                fetch_tables = false;
+                if (++head == div_heads.d) { head = 0; ++token; fetch_tables = true; }
                 if (!BACKWARD) {
                     float x[8];
                     unpack8<T>(x, raw_in[u]);

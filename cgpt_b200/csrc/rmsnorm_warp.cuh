@@ -16,8 +16,7 @@ template <typename T>
 __device__ __forceinline__ void unpack8(float (&out)[8], const uint4& raw) {
     Pack<T, 8> pk;
     *reinterpret_cast<uint4*>(&pk) = raw;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) out[i] = to_f32<T>(pk.v[i]);
+    unpack_pack(out, pk);
 }
 
 // Makes the packed registers opaque to the optimiser, so that it unpacks them again where they are used next
