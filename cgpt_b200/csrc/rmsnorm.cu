@@ -436,15 +436,16 @@ int launch_forward_dual(void* y_a, void* y_b, const void* x, const void* w_a, co
     const std::size_t need = (rows + 2 * warp_rows::kWarps - 1) / (2 * warp_rows::kWarps);
     const std::size_t cap = static_cast<std::size_t>(kNumSMs) * 2;      // __launch_bounds__(kThreads, 2): two resident CTAs per SM
     const int grid = static_cast<int>(need < cap ? need : cap);
-#define CGPT_RMS_FWD_DUAL(CPT)                                                                                            \
-    warp_rows::rmsnorm_forward_dual_warp_kernel<T, CPT><<<grid, warp_rows::kThreads, 0, s>>>(                             \
+    const bool exact = hidden == static_cast<std::size_t>(cpt) * 256;      // no column checks in the kernel
+#define CGPT_RMS_FWD_DUAL(CPT, EXACT)                                                                                     \
+    warp_rows::rmsnorm_forward_dual_warp_kernel<T, CPT, EXACT><<<grid, warp_rows::kThreads, 0, s>>>(                      \
         static_cast<T*>(y_a), static_cast<T*>(y_b), static_cast<const T*>(x), static_cast<const T*>(w_a),                \
         static_cast<const T*>(w_b), static_cast<long long>(rows), static_cast<int>(hidden), eps)
     switch (cpt) {
-        case 1: CGPT_RMS_FWD_DUAL(1); break;
-        case 2: CGPT_RMS_FWD_DUAL(2); break;
-        case 3: CGPT_RMS_FWD_DUAL(3); break;
-        default: CGPT_RMS_FWD_DUAL(4); break;
+        case 1: if (exact) CGPT_RMS_FWD_DUAL(1, true); else CGPT_RMS_FWD_DUAL(1, false); break;
+        case 2: if (exact) CGPT_RMS_FWD_DUAL(2, true); else CGPT_RMS_FWD_DUAL(2, false); break;
+        case 3: if (exact) CGPT_RMS_FWD_DUAL(3, true); else CGPT_RMS_FWD_DUAL(3, false); break;
+        default: if (exact) CGPT_RMS_FWD_DUAL(4, true); else CGPT_RMS_FWD_DUAL(4, false); break;
     }
 #undef CGPT_RMS_FWD_DUAL
     count_launch();
@@ -452,18 +453,18 @@ int launch_forward_dual(void* y_a, void* y_b, const void* x, const void* w_a, co
     return CGPT_OK;
 }
 
-template <typename T, int CPT>
+template <typename T, int CPT, bool EXACT>
 int launch_backward_dual_cpt(void* dx, float* partial, const void* dy_a, const void* dy_b, const void* x, const void* w_a,
                              const void* w_b, const void* res, std::size_t rows, std::size_t hidden, float eps, int grid,
                              cudaStream_t s) {
     constexpr std::size_t smem = static_cast<std::size_t>(2 * CPT * 2 * warp_rows::kThreads) * sizeof(float4) + 2 * CPT * 32 * sizeof(uint4);
     static PerDeviceOnce attr_once;
     if (attr_once.needed()) {
-        CGPT_CUDA_TRY(cudaFuncSetAttribute(warp_rows::rmsnorm_backward_dual_warp_kernel<T, CPT>,
+        CGPT_CUDA_TRY(cudaFuncSetAttribute(warp_rows::rmsnorm_backward_dual_warp_kernel<T, CPT, EXACT>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         attr_once.done();
     }
-    warp_rows::rmsnorm_backward_dual_warp_kernel<T, CPT><<<grid, warp_rows::kThreads, smem, s>>>(
+    warp_rows::rmsnorm_backward_dual_warp_kernel<T, CPT, EXACT><<<grid, warp_rows::kThreads, smem, s>>>(
         static_cast<T*>(dx), partial, static_cast<const T*>(dy_a), static_cast<const T*>(dy_b), static_cast<const T*>(x),
         static_cast<const T*>(w_a), static_cast<const T*>(w_b), static_cast<const T*>(res), static_cast<long long>(rows),
         static_cast<int>(hidden), eps);
@@ -482,12 +483,17 @@ int launch_backward_dual(void* dx, void* dw_a, void* dw_b, const void* dy_a, con
     void* scratch = nullptr;
     CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(grid) * 2 * hidden * sizeof(float), s));
     float* partial = static_cast<float*>(scratch);
+    const bool exact = hidden == static_cast<std::size_t>(cpt) * 256;      // no column checks in the kernel
+#define CGPT_RMS_BWD_DUAL(CPT)                                                                                                    \
+    CGPT_TRY((exact ? launch_backward_dual_cpt<T, CPT, true>(dx, partial, dy_a, dy_b, x, w_a, w_b, res, rows, hidden, eps, grid, s) \
+                    : launch_backward_dual_cpt<T, CPT, false>(dx, partial, dy_a, dy_b, x, w_a, w_b, res, rows, hidden, eps, grid, s)))
     switch (cpt) {
-        case 1: CGPT_TRY((launch_backward_dual_cpt<T, 1>(dx, partial, dy_a, dy_b, x, w_a, w_b, res, rows, hidden, eps, grid, s))); break;
-        case 2: CGPT_TRY((launch_backward_dual_cpt<T, 2>(dx, partial, dy_a, dy_b, x, w_a, w_b, res, rows, hidden, eps, grid, s))); break;
-        case 3: CGPT_TRY((launch_backward_dual_cpt<T, 3>(dx, partial, dy_a, dy_b, x, w_a, w_b, res, rows, hidden, eps, grid, s))); break;
-        default: CGPT_TRY((launch_backward_dual_cpt<T, 4>(dx, partial, dy_a, dy_b, x, w_a, w_b, res, rows, hidden, eps, grid, s))); break;
+        case 1: CGPT_RMS_BWD_DUAL(1); break;
+        case 2: CGPT_RMS_BWD_DUAL(2); break;
+        case 3: CGPT_RMS_BWD_DUAL(3); break;
+        default: CGPT_RMS_BWD_DUAL(4); break;
     }
+#undef CGPT_RMS_BWD_DUAL
     warp_rows::dw_reduce_dual_kernel<T><<<static_cast<unsigned>((2 * hidden + 31) / 32), 1024, 0, s>>>(
         static_cast<T*>(dw_a), static_cast<T*>(dw_b), partial, grid, static_cast<int>(hidden));
     count_launch();

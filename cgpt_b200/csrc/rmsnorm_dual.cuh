@@ -15,7 +15,8 @@
 namespace warp_rows {
 
 // y_a = x * inv * w_a, y_b = x * inv * w_b; two rows per warp per trip.
-template <typename T, int CPT>
+// EXACT: hidden == CPT * 256, so every chunk of every lane is inside the row (no column checks, no zero fills).
+template <typename T, int CPT, bool EXACT>
 __global__ void __launch_bounds__(kThreads, 2)
 rmsnorm_forward_dual_warp_kernel(T* __restrict__ y_a, T* __restrict__ y_b, const T* __restrict__ x, const T* __restrict__ w_a,
                                  const T* __restrict__ w_b, long long rows, int hidden, float epsilon) {
@@ -30,8 +31,8 @@ rmsnorm_forward_dual_warp_kernel(T* __restrict__ y_a, T* __restrict__ y_b, const
 #pragma unroll
     for (int c = 0; c < CPT; ++c) {
         const int col = (c * 32 + lane) * 8;
-        wa[c] = col < hidden ? *reinterpret_cast<const uint4*>(w_a + col) : zero;
-        wb[c] = col < hidden ? *reinterpret_cast<const uint4*>(w_b + col) : zero;
+        wa[c] = (EXACT || col < hidden) ? *reinterpret_cast<const uint4*>(w_a + col) : zero;
+        wb[c] = (EXACT || col < hidden) ? *reinterpret_cast<const uint4*>(w_b + col) : zero;
     }
     for (long long row0 = warp_id * R; row0 < rows; row0 += warps_total * R) {
         uint4 xp[R][CPT];
@@ -41,7 +42,7 @@ rmsnorm_forward_dual_warp_kernel(T* __restrict__ y_a, T* __restrict__ y_b, const
 #pragma unroll
             for (int c = 0; c < CPT; ++c) {
                 const int col = (c * 32 + lane) * 8;
-                xp[r][c] = (row < rows && col < hidden) ? __ldcs(reinterpret_cast<const uint4*>(x + row * hidden + col)) : zero;
+                xp[r][c] = (row < rows && (EXACT || col < hidden)) ? __ldcs(reinterpret_cast<const uint4*>(x + row * hidden + col)) : zero;
             }
         }
 #pragma unroll
@@ -63,7 +64,7 @@ rmsnorm_forward_dual_warp_kernel(T* __restrict__ y_a, T* __restrict__ y_b, const
 #pragma unroll
                 for (int c = 0; c < CPT; ++c) {
                     const int col = (c * 32 + lane) * 8;
-                    if (col < hidden) {
+                    if (EXACT || col < hidden) {
                         float xv[8], wv[8], out[8];
                         unpack8<T>(xv, xp[r][c]);
                         unpack8<T>(wv, wa[c]);
@@ -84,7 +85,7 @@ rmsnorm_forward_dual_warp_kernel(T* __restrict__ y_a, T* __restrict__ y_b, const
 // dx = res + (dy_a*w_a*inv - x*c_a) + (dy_b*w_b*inv - x*c_b); per-CTA dw partial rows in dw_partial[blockIdx.x][2][hidden]
 // (norm a first). dx may alias res. Shared memory: the thread's running dw sums ([2][CPT*2][kThreads] float4, its own
 // slots: no conflicts, no synchronisation) and both weight vectors ([2][CPT*32] uint4).
-template <typename T, int CPT>
+template <typename T, int CPT, bool EXACT>
 __global__ void __launch_bounds__(kThreads, 2)
 rmsnorm_backward_dual_warp_kernel(T* dx, float* __restrict__ dw_partial, const T* __restrict__ dy_a, const T* __restrict__ dy_b,
                                   const T* __restrict__ x, const T* __restrict__ w_a, const T* __restrict__ w_b, const T* res,
@@ -115,7 +116,7 @@ rmsnorm_backward_dual_warp_kernel(T* dx, float* __restrict__ dw_partial, const T
         uint4 xp[CPT], ap[CPT], bp[CPT], rp[CPT];
 #pragma unroll
         for (int c = 0; c < CPT; ++c) {
-            const bool in = c * 256 + lane * 8 < hidden;
+            const bool in = EXACT || c * 256 + lane * 8 < hidden;
             xp[c] = in ? __ldcs(reinterpret_cast<const uint4*>(x + off + c * 256)) : zero;
             ap[c] = in ? __ldcs(reinterpret_cast<const uint4*>(dy_a + off + c * 256)) : zero;
             bp[c] = in ? __ldcs(reinterpret_cast<const uint4*>(dy_b + off + c * 256)) : zero;
@@ -143,7 +144,7 @@ rmsnorm_backward_dual_warp_kernel(T* dx, float* __restrict__ dw_partial, const T
             keep_packed(xp[c]);
             keep_packed(ap[c]);
             keep_packed(bp[c]);
-            rp[c] = (res != nullptr && c * 256 + lane * 8 < hidden) ? __ldcs(reinterpret_cast<const uint4*>(res + off + c * 256)) : zero;
+            rp[c] = (res != nullptr && (EXACT || c * 256 + lane * 8 < hidden)) ? __ldcs(reinterpret_cast<const uint4*>(res + off + c * 256)) : zero;
         }
         sx = warp_sum(sx);
         sa = warp_sum(sa);
@@ -153,7 +154,7 @@ rmsnorm_backward_dual_warp_kernel(T* dx, float* __restrict__ dw_partial, const T
         const float corr_a = sa * scale3, corr_b = sb * scale3;
 #pragma unroll
         for (int c = 0; c < CPT; ++c) {
-            if (c * 256 + lane * 8 < hidden) {
+            if (EXACT || c * 256 + lane * 8 < hidden) {
                 float xv[8], gv[8], wv[8], out[8], xn[8];
                 unpack8<T>(xv, xp[c]);
                 unpack8<T>(out, rp[c]);                       // zeros without a residual
