@@ -13,6 +13,7 @@
 // at workspace creation maps chunk -> (tensor, offset). CTAs walk the chunk list with a grid stride,
 // so 90 tensors of very different sizes load all SMs evenly. HBM bytes per element: 2 (statistics,
 // 16-bit grads) + 28 (update: grad 2r, master/m/v 12r + 12w, param 2w).
+#include <cmath>
 #include <vector>
 
 #include "common.cuh"
@@ -40,8 +41,16 @@ struct Chunk {
     unsigned long long offset;
 };
 
-template <typename T>
-__device__ __forceinline__ void stats_chunk(const T* __restrict__ g, unsigned long long n, float loss_scale,
+// g / loss_scale as the reference writes it. POW2: loss_scale is a power of two, so multiplying by its (exact) reciprocal
+// gives the same correctly rounded value as the division, bit for bit, at a tenth of the instructions; the statistics
+// pass reads 2 bytes per element and is bound by those divisions otherwise.
+template <bool POW2>
+__device__ __forceinline__ float unscale(float g, float loss_scale, float inv_loss_scale) {
+    return POW2 ? g * inv_loss_scale : g / loss_scale;
+}
+
+template <typename T, bool POW2>
+__device__ __forceinline__ void stats_chunk(const T* __restrict__ g, unsigned long long n, float loss_scale, float inv_loss_scale,
                                             float& sum, bool& bad) {
     constexpr int V = 16 / sizeof(T);
     const bool vec = (reinterpret_cast<std::uintptr_t>(g) & 15u) == 0;
@@ -52,27 +61,28 @@ __device__ __forceinline__ void stats_chunk(const T* __restrict__ g, unsigned lo
                 load_vec<T, V>(x, g + i);
 #pragma unroll
                 for (int k = 0; k < V; ++k) {
-                    const float u = x[k] / loss_scale;
+                    const float u = unscale<POW2>(x[k], loss_scale, inv_loss_scale);
                     if (isfinite(u)) sum = fmaf(u, u, sum); else bad = true;
                 }
             } else {
                 for (unsigned long long j = i; j < n; ++j) {
-                    const float u = to_f32<T>(g[j]) / loss_scale;
+                    const float u = unscale<POW2>(to_f32<T>(g[j]), loss_scale, inv_loss_scale);
                     if (isfinite(u)) sum = fmaf(u, u, sum); else bad = true;
                 }
             }
         }
     } else {
         for (unsigned long long i = threadIdx.x; i < n; i += kAdamThreads) {
-            const float u = to_f32<T>(g[i]) / loss_scale;
+            const float u = unscale<POW2>(to_f32<T>(g[i]), loss_scale, inv_loss_scale);
             if (isfinite(u)) sum = fmaf(u, u, sum); else bad = true;
         }
     }
 }
 
+template <bool POW2>
 __global__ void __launch_bounds__(kAdamThreads)
 adamw_stats_kernel(const DevTensor* __restrict__ tensors, const Chunk* __restrict__ chunks, unsigned int n_chunks,
-                   float loss_scale, float* __restrict__ partial_sums, unsigned int* __restrict__ partial_bad) {
+                   float loss_scale, float inv_loss_scale, float* __restrict__ partial_sums, unsigned int* __restrict__ partial_bad) {
     __shared__ float red[kAdamThreads / 32];
     __shared__ int any_bad;
     if (threadIdx.x == 0) any_bad = 0;
@@ -85,9 +95,9 @@ adamw_stats_kernel(const DevTensor* __restrict__ tensors, const Chunk* __restric
         unsigned long long n = t.count - ch.offset;
         if (n > kChunk) n = kChunk;
         switch (t.dtype) {
-            case CGPT_DTYPE_F16: stats_chunk(static_cast<const __half*>(t.grad) + ch.offset, n, loss_scale, sum, bad); break;
-            case CGPT_DTYPE_BF16: stats_chunk(static_cast<const __nv_bfloat16*>(t.grad) + ch.offset, n, loss_scale, sum, bad); break;
-            default: stats_chunk(static_cast<const float*>(t.grad) + ch.offset, n, loss_scale, sum, bad); break;
+            case CGPT_DTYPE_F16: stats_chunk<__half, POW2>(static_cast<const __half*>(t.grad) + ch.offset, n, loss_scale, inv_loss_scale, sum, bad); break;
+            case CGPT_DTYPE_BF16: stats_chunk<__nv_bfloat16, POW2>(static_cast<const __nv_bfloat16*>(t.grad) + ch.offset, n, loss_scale, inv_loss_scale, sum, bad); break;
+            default: stats_chunk<float, POW2>(static_cast<const float*>(t.grad) + ch.offset, n, loss_scale, inv_loss_scale, sum, bad); break;
         }
     }
     if (bad) any_bad = 1;
@@ -279,7 +289,7 @@ extern "C" int cgpt_adamw_create(cgpt_adamw_workspace** out, const cgpt_adamw_te
     ws->n_chunks = static_cast<unsigned int>(host_chunks.size());
     // every CTA of the chunk loops resident from the start (the smaller of what the two kernels fit per SM)
     int per_sm = resident_ctas_per_sm(reinterpret_cast<const void*>(adamw_update_kernel), kAdamThreads, 0);
-    const int per_sm_stats = resident_ctas_per_sm(reinterpret_cast<const void*>(adamw_stats_kernel), kAdamThreads, 0);
+    const int per_sm_stats = resident_ctas_per_sm(reinterpret_cast<const void*>(adamw_stats_kernel<false>), kAdamThreads, 0);
     if (per_sm_stats < per_sm) per_sm = per_sm_stats;
     const unsigned int cap = static_cast<unsigned int>(kNumSMs * per_sm);
     ws->grid = static_cast<int>(ws->n_chunks < cap ? ws->n_chunks : cap);
@@ -327,8 +337,17 @@ int adamw_step_impl(cgpt_adamw_workspace* ws, const cgpt_adamw_options* o, const
         !(o->epsilon > 0.f) || !(o->weight_decay >= 0.f) || !(o->loss_scale > 0.f) || !(o->max_grad_norm > 0.f))
         return CGPT_ERR_OPTION;
     auto s = static_cast<cudaStream_t>(stream);
-    adamw_stats_kernel<<<ws->grid, kAdamThreads, 0, s>>>(ws->d_tensors, ws->d_chunks, ws->n_chunks, o->loss_scale,
-                                                        ws->d_partial_sums, ws->d_partial_bad);
+    {   // a power-of-two loss scale (the trainer's 1024) is divided out by an exact multiplication
+        int exponent = 0;
+        const bool pow2 = std::frexp(o->loss_scale, &exponent) == 0.5f && exponent > -100 && exponent < 100;
+        const float inv = 1.0f / o->loss_scale;
+        if (pow2)
+            adamw_stats_kernel<true><<<ws->grid, kAdamThreads, 0, s>>>(ws->d_tensors, ws->d_chunks, ws->n_chunks, o->loss_scale, inv,
+                                                                      ws->d_partial_sums, ws->d_partial_bad);
+        else
+            adamw_stats_kernel<false><<<ws->grid, kAdamThreads, 0, s>>>(ws->d_tensors, ws->d_chunks, ws->n_chunks, o->loss_scale, inv,
+                                                                       ws->d_partial_sums, ws->d_partial_bad);
+    }
     count_launch();
     CGPT_LAUNCH_CHECK();
     adamw_prepare_kernel<<<1, 256, 0, s>>>(ws->d_partial_sums, ws->d_partial_bad, ws->grid, ws->d_state, ws->d_step,
