@@ -83,7 +83,8 @@ template <int BN> struct GemmCfg {
 // Device status word shared by the contraction kernels: non-zero means a bounded wait ran out.
 __device__ unsigned int g_gemm_status = 0;
 
-enum : int { kEpiStore = 0, kEpiAccumulate = 1, kEpiPartial = 2, kEpiNone = 3, kEpiStoreTma = 4, kEpiStageOnly = 5, kEpiStoreTmaFixed = 6, kEpiStoreTmaResidual = 7 };
+enum : int { kEpiStore = 0, kEpiAccumulate = 1, kEpiPartial = 2, kEpiNone = 3, kEpiStoreTma = 4, kEpiStageOnly = 5, kEpiStoreTmaFixed = 6, kEpiStoreTmaResidual = 7,
+              kEpiRowTilesFastest = 0x100 /* flag for the pair kernel, or-ed to the mode: order of its work units */ };
 
 // Optional timing of the tensor-core GEMM launches (eager mode only, never during stream capture):
 // a CUDA event pair around every tensor-core GEMM launch plus its algorithmic FLOPs.
@@ -347,6 +348,9 @@ int launch_tc(T* C, const T* const* As, const T* const* Bs, const int* Ks, int s
         }
         outs.c[1] = outs.c[2] = outs.c[0];
         T* c_arg = epi == kEpiStoreTmaResidual ? const_cast<T*>(residual) : C;    // that epilogue reads it, the store goes through the map
+        // B larger than A and larger than a fraction of L2 (an LM-head-shaped product): walk the row tiles first
+        if (PAIR && splits == 1 && static_cast<long long>(N) > static_cast<long long>(M) && static_cast<long long>(N) * K * 2 > (32ll << 20))
+            epi |= kEpiRowTilesFastest;
         pkernel<<<grid, kGemmThreads, smem_bytes, s>>>(ops, outs, c_arg, partial, M, N, total_kb, tiles_m, tiles_n, splits, kb_per_split, epi);
     }
     count_launch();

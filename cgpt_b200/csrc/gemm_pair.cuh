@@ -76,6 +76,13 @@ __device__ __forceinline__ void gemm_pair_body(const GemmOperands& ops, const Ge
     const int pairs = static_cast<int>(gridDim.x >> 1);
     const int tiles = tiles_m * tiles_n;
     const int units = tiles * splits;
+    // Order of the work units. Column tiles fastest (default): the pairs running at the same time share a few row tiles of
+    // A and the whole of a small B (a weight matrix). Row tiles fastest (kEpiRowTilesFastest, and every softmax epilogue):
+    // for an LM-head-shaped product, where B (the vocabulary matrix) is the large operand, the running pairs share a few
+    // column tiles of B and B streams from memory once instead of once per row tile (measured on the 8192 x 32000 x 1024
+    // logits product: DRAM traffic 1.23 GB -> its algorithmic 0.6 GB, the loss layer 7 % faster).
+    const bool m_fastest = SOFTMAX != kSoftmaxNone || (epilogue & kEpiRowTilesFastest) != 0;
+    epilogue &= ~kEpiRowTilesFastest;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -98,7 +105,8 @@ __device__ __forceinline__ void gemm_pair_body(const GemmOperands& ops, const Ge
             int it = 0;
             for (int u = pair; u < units && !failed; u += pairs) {
                 const int split = u / tiles, t = u % tiles;
-                const int tile_m = t / tiles_n, tile_n = t % tiles_n;
+                const int tile_m = m_fastest ? t % tiles_m : t / tiles_n;
+                const int tile_n = m_fastest ? t / tiles_m : t % tiles_n;
                 const int kb_begin = split * kb_per_split;
                 int nkb = total_kb - kb_begin;
                 if (nkb > kb_per_split) nkb = kb_per_split;
@@ -183,7 +191,8 @@ __device__ __forceinline__ void gemm_pair_body(const GemmOperands& ops, const Ge
         int stage_buf = 0;
         for (int u = pair; u < units; u += pairs, ++j) {
             const int split = u / tiles, t = u % tiles;
-            const int tile_m = t / tiles_n, tile_n = t % tiles_n;
+            const int tile_m = m_fastest ? t % tiles_m : t / tiles_n;
+            const int tile_n = m_fastest ? t / tiles_m : t % tiles_n;
             const int buf = j & 1;
             if (!mbar_wait(&acc_full[buf], (j >> 1) & 1)) failed = true;
             failed = __any_sync(0xffffffffu, failed);
