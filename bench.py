@@ -42,7 +42,7 @@ PUBLISHED_TOKENS_PER_S = 151400.0   # reference README.md:168 (4.62 steps/s at 3
 # (python -m cgpt_b200.profile_ops gemm_fwd under ncu, CTA-pair kernel): dram__bytes_read.sum 71.4 MB + dram__bytes_write.sum 85.2 MB.
 GEMM_TRAFFIC_BYTES = 156.6e6
 GEMM_TRAFFIC_NOTE = ("ncu, one launch of the 32768x2048x1024 forward GEMM (algorithmic A+B+C = 205.5 MB; part of C is still "
-                     "in L2 when the kernel ends); the step's 116 launches have other shapes, none re-reads its operands from DRAM")
+                     "in L2 when the kernel ends); the step's 108 launches have other shapes, none re-reads its operands from DRAM")
 
 
 def workload_config(n_gpus: int) -> dict:
@@ -349,7 +349,8 @@ def run_ours(args) -> None:
             line["roofline"] = {"bound": "tensor", "achieved": gemm["tflops"], "peak": peak, "unit": "TFLOP/s",
                                 "frac": gemm["tflops"] / peak, "traffic": GEMM_TRAFFIC_BYTES,
                                 "traffic_note": GEMM_TRAFFIC_NOTE,
-                                "kernel": "gemm_tcgen05_pair_kernel (forward, dX, logits) + gemm_tcgen05_persistent_kernel (dW)",
+                                "kernel": "gemm_tcgen05_pair_kernel (forward, dX) + gemm_pair_softmax_kernel (LM-head logits with the softmax "
+                                          "statistics epilogue) + gemm_tcgen05_persistent_kernel (dW)",
                                 "launches_per_step": gemm["launches"], "ms_per_step_in_kernel": gemm["ms"],
                                 "share_of_step": gemm["ms"] / ms_step, "peak_source": which,
                                 "model_flops_per_step": gemm["model_flops"], "model_tflops": gemm["model_flops"] / ms_step / 1e9}
