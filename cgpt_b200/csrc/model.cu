@@ -136,16 +136,21 @@ bool dual_norm_enabled() {
 int mlp_forward(const void* in, const cgpt_block_params* w, const cgpt_block_saved* sv, const BlockScratch& ws, const Dims& m,
                 int dt, float eps, bool with_norm, bool with_down, cudaStream_t stream) {
     if (with_norm) CGPT_TRY(cgpt_rmsnorm_forward(sv->norm, in, w->ffn_norm, m.rows, m.d, eps, dt, stream));
-    // gate, up and the activation (two GEMMs and an activation pass in the reference, :566-579). The one-launch form
-    // (cgpt_linear_swiglu_forward, same results bit for bit) measured 300 us against 292 us for the three launches at
-    // the 104m shape, so the block uses it only in diagnosis builds with CGPT_B200_FUSED_SWIGLU=1.
+    // gate, up and the activation (two GEMMs and an activation pass in the reference, :566-579). The form with the
+    // activation in the product's epilogue (cgpt_linear_swiglu_forward, same results bit for bit) measured 300 us against
+    // 292 us for separate launches at the 104m shape (a third output stream costs the product what the activation pass
+    // costs), so the block uses it only in diagnosis builds with CGPT_B200_FUSED_SWIGLU=1.
     static const bool fused_swiglu = [] { const char* e = diagnosis_env("CGPT_B200_FUSED_SWIGLU"); return e && e[0] == '1'; }();
     if (fused_swiglu) {
         CGPT_TRY(cgpt_linear_swiglu_forward(sv->gate, sv->up, sv->activated, sv->norm, w->gate_proj, w->up_proj, m.rows, m.d,
                                             m.inter, dt, stream));
     } else {
-        CGPT_TRY(cgpt_linear_forward(sv->gate, sv->norm, w->gate_proj, m.rows, m.d, m.inter, dt, stream));
-        CGPT_TRY(cgpt_linear_forward(sv->up, sv->norm, w->up_proj, m.rows, m.d, m.inter, dt, stream));
+        {   // gate and up projections of the same input as one launch (it falls back to two where grouping does not apply)
+            void* ys[2] = {sv->gate, sv->up};
+            const void* wts[2] = {w->gate_proj, w->up_proj};
+            const size_t outs[2] = {m.inter, m.inter};
+            CGPT_TRY(cgpt_linear_forward_fused(ys, sv->norm, wts, outs, 2, m.rows, m.d, dt, stream));
+        }
         CGPT_TRY(cgpt_swiglu_forward(sv->activated, sv->gate, sv->up, m.rows * m.inter, dt, stream));
     }
     if (!with_down) return CGPT_OK;     // the caller folds the down projection into the block's final product
