@@ -77,7 +77,7 @@ __device__ __forceinline__ void bwd_cta(const CUtensorMap& map_x1, const CUtenso
         mbar_init(bars.uw_free, 1);
         for (int s = 0; s < kTBufs; ++s) {
             mbar_init(&bars.t_full[s], 1);
-            mbar_init(&bars.w_full[s], kRows);          // one warpgroup owns each of the two T buffers
+            mbar_init(&bars.w_full[s], kRows);          // the 128 threads of the warpgroup that took the tile arrive
         }
         mbar_init(bars.acc_done, 1);
         mbar_init_fence();

@@ -171,8 +171,8 @@ __device__ __forceinline__ bool bwd_mma_issuer(unsigned char* smem, const BwdBar
         const std::uint32_t u_tmem = tmem + TM::kT1 + s * kCols, w_tmem = tmem + TM::kT2 + s * kCols;   // over T1 / T2 of this tile
 #pragma unroll
         for (int k = 0; k < kCols / 16; ++k) {
-            // A: TMEM, lanes = stationary rows, 16 streaming rows (one K step) = 8 packed columns; the two compute
-            // warpgroups wrote streaming rows 0-31 at columns [0,16) and rows 32-63 at columns [32,48).
+            // A: TMEM, lanes = stationary rows, 16 streaming rows (one K step) = 8 packed columns; the tile's compute
+            // warpgroup wrote streaming rows 0-31 at columns [0,16) and rows 32-63 at columns [32,48).
             // B: streaming tile as N-major: 16 rows of 128 B per K step, 64-column chunks of D kCols*128 bytes apart.
             const std::uint32_t a_col = (k >> 1) * 32 + (k & 1) * 8;
             if (MODE == MODE_DKV) {

@@ -15,9 +15,10 @@
 // storage dtype before the second products (:1336-1343, :1567-1586); everything else is fp32.
 //
 // Both kernels are one template. A "stationary" pair of [128, D] tiles (X1, X2) stays in shared memory,
-// a "streaming" pair of [64, D] tiles (Y1, Y2) runs through a 3-stage TMA ring:
-//     T1 = X1 Y1^T, T2 = X2 Y2^T            two 128x64 fp32 tiles in TMEM (double-buffered)
-//     threads (two per TMEM lane = stationary row) turn T1/T2 into 16-bit tiles U (P^T) and W (dS or dS^T),
+// a "streaming" pair of [64, D] tiles (Y1, Y2) runs through a 4-stage (D 128) or 6-stage (D 64) TMA ring:
+//     T1 = X1 Y1^T, T2 = X2 Y2^T            two 128x64 fp32 tiles in TMEM (triple-buffered where 512 columns allow, else double)
+//     threads (one per TMEM lane = stationary row; two warpgroups take alternate tiles) turn T1/T2 into 16-bit tiles
+//     U (P^T) and W (dS or dS^T),
 //     written back into TMEM over the columns of T1/T2 they were computed from (A operands read from TMEM)
 //     acc1 += U Y2, acc2 += W Y1 (dKV)   or   acc1 += W Y1 (dQ)      accumulators stay in TMEM
 // The streaming tiles serve twice from the same bytes: as K-major B operands of T1/T2 and as N-major
@@ -39,7 +40,7 @@ using namespace sm100;
 
 constexpr int kRows = 128;   // stationary tile rows = TMEM lanes
 constexpr int kCols = 64;    // streaming tile rows = columns of T1/T2
-constexpr int kBwdThreads = 320;   // warps 0-7 compute (two warpgroups, each half of the tile's columns), 8 TMA, 9 MMA
+constexpr int kBwdThreads = 320;   // warps 0-7 compute (two warpgroups taking alternate streaming tiles), 8 TMA, 9 MMA
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int MODE_DQ = 0, MODE_DKV = 1;
 
