@@ -48,7 +48,11 @@ int cut_cross_entropy_form(int form, float* loss, void* dx, void* dc, const void
         static const int forced = [] { const char* e = diagnosis_env("CGPT_B200_CCE_FORM"); return e ? std::atoi(e) : 0; }();
         form = forced >= kCceRows && forced <= kCceRecompute ? forced : kCceDefault;
     }
-    if (chunk_rows == 0) chunk_rows = 8192;
+    // Default chunk: 74 row tiles of 256 (one tile per CTA pair of the GPU), so that the dX product of a chunk, whose work
+    // list is (row tiles) x (hidden / 256 column tiles), is a whole number of waves for any hidden size. Measured at
+    // 32768 x 1024 x 32000: 5.30-5.32 ms against 5.42-5.44 ms with 8192-row chunks (128 units on 74 pairs = 2 waves, the
+    // second one a quarter empty); scratch 1.2 GB instead of 0.5 GB.
+    if (chunk_rows == 0) chunk_rows = static_cast<size_t>(kNumSMs / 2) * 256;
     if (chunk_rows > rows) chunk_rows = rows;
     const std::size_t esz = dtype_size(dtype);
     auto pad = [](std::size_t b) { return (b + 255) & ~std::size_t{255}; };

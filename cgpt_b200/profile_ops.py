@@ -35,6 +35,7 @@ def main() -> None:
                     help="attention ops: 8/2 heads of 128 (the 104m layer) or 12/4 heads of 64")
     ap.add_argument("--cce-form", type=int, default=0, help="cce: 0 default, 1 row kernel, 2 tile statistics, 3 recompute")
     ap.add_argument("--rows", type=int, default=8192, help="cce: rows (8192 is one chunk)")
+    ap.add_argument("--cce-chunk", type=int, default=0, help="cce: rows per chunk (0 = the library's choice)")
     a = ap.parse_args()
     h = lambda *s: torch.randn(*s, device="cuda").half()
     T, d, I = 32768, 1024, 2048
@@ -115,8 +116,9 @@ def main() -> None:
         x, c = h(rows, d), h(V, d) * 0.02
         t = torch.randint(0, V, (rows,), device="cuda", dtype=torch.int32)
         loss, dx, dc = torch.zeros(1, device="cuda"), torch.empty_like(x), torch.empty_like(c)
-        ms = _run(lambda: M.cut_cross_entropy_forward_backward(loss, dx, dc, x, c, t, rows, None, 1024.0, form=a.cce_form), a.iters)
-        print(f"cce form {a.cce_form} {rows}x{d}x{V}: {ms * 1e3:.1f} us, {3 * 2.0 * rows * d * V / ms / 1e9:.1f} TFLOP/s on 3 products, "
+        ms = _run(lambda: M.cut_cross_entropy_forward_backward(loss, dx, dc, x, c, t, rows, None, 1024.0, form=a.cce_form,
+                                                               chunk_rows=a.cce_chunk), a.iters)
+        print(f"cce form {a.cce_form} chunk {a.cce_chunk} {rows}x{d}x{V}: {ms * 1e3:.1f} us, {3 * 2.0 * rows * d * V / ms / 1e9:.1f} TFLOP/s on 3 products, "
               f"loss {float(loss.item()):.6f}")
     elif a.op == "adamw":
         sizes = [32000 * 1024] + [1024 * 1024, 2048 * 1024, 2048 * 1024, 1024 * 2048] * 8

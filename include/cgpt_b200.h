@@ -365,8 +365,8 @@ int cgpt_adamw_last_stats(cgpt_adamw_workspace* ws, float* squared_norm, float* 
  * x, dx: [rows, hidden]; c (classifier), dc: [vocab, hidden]; targets: uint32 [rows]; loss: fp32 [1].
  *   loss = mean_rows(log sum exp(x C^T) - (x C^T)[target]);  G = (softmax - onehot) / rows * gradient_scale
  *   dx = G C;  dc (+)= G^T x.   Rows whose target >= vocab add no loss and no -1 (as cross_entropy).
- * Rows are processed in chunks of at most chunk_rows (0 = library default): logits of one chunk live in
- * scratch ([chunk_rows, vocab]), are turned into G in place and feed the two gradient GEMMs.
+ * Rows are processed in chunks of at most chunk_rows (0 = library default, 18944 = 74 x 256 rows): logits of one chunk
+ * live in scratch ([chunk_rows, vocab]), are turned into G in place and feed the two gradient GEMMs.
  * accumulate_dc != 0 adds into dc instead of overwriting it.
  * ---------------------------------------------------------------------------------------------- */
 int cgpt_cut_cross_entropy(float* loss, void* dx, void* dc, const void* x, const void* c,
