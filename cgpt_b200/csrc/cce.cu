@@ -28,8 +28,8 @@ using namespace cgpt;
 
 namespace {
 enum : int { kCceAuto = 0, kCceRows = 1, kCceTiles = 2, kCceRecompute = 3 };
-// Measured at 32768 x 1024 x 32000 fp16 on one B200: rows 5.82-5.89 ms, tiles 5.77 ms, recompute 6.77 ms per call
-// (per 8192-row chunk: logits product 412 us, with the statistics epilogue 445 us; row kernel 218 us, streaming
+// Measured at 32768 x 1024 x 32000 fp16 on one B200, 8192-row chunks: tiles 5.43 ms, rows 5.51-5.53 ms, recompute 6.36 ms per
+// call (per chunk under a profiler: logits product 412 us, with the statistics epilogue 445 us; row kernel 218 us, streaming
 // gradient pass 185 us; statistics-only product 402 us + gradient-writing product 435 us).
 constexpr int kCceDefault = kCceTiles;
 

@@ -95,6 +95,22 @@ def test_cce_forms_agree(M, rows, vocab, hidden, chunk, dt, form):
     assert_close(out[form][1], out[1][1], tol / 10, "dx vs rows form"); assert_close(out[form][2], out[1][2], tol / 10, "dc vs rows form", metric="max")
 
 
+def test_cce_form_argument_is_validated(M):
+    x, cl = dev(np.ones((256, 64)), "f16"), dev(np.ones((512, 64)), "f16")
+    loss = torch.zeros(1, device="cuda"); dx, dc = torch.empty_like(x), torch.empty_like(cl)
+    t = ids_dev(np.zeros(256, dtype=np.int64))
+    for bad in (-1, 4):
+        with pytest.raises(Exception):
+            M.cut_cross_entropy_forward_backward(loss, dx, dc, x, cl, t, 256, None, 1.0, form=bad)
+    # a float32 call has no tile form: the explicit request is refused, the default falls back to the row kernel
+    xf, cf = x.float(), cl.float()
+    dxf, dcf = torch.empty_like(xf), torch.empty_like(cf)
+    with pytest.raises(Exception):
+        M.cut_cross_entropy_forward_backward(loss, dxf, dcf, xf, cf, t, 256, None, 1.0, form=2)
+    M.cut_cross_entropy_forward_backward(loss, dxf, dcf, xf, cf, t, 256, None, 1.0)
+    assert np.isfinite(float(loss.item()))
+
+
 # --------------------------------------------------------------------------------------------- block
 @pytest.mark.parametrize("batch,seq,opts", [(2, 128, (256, 688, 4, 2, 64, 64)), (1, 96, (64, 64, 2, 1, 32, 32)), (2, 64, (256, 512, 2, 1, 128, 128))])
 def test_block_forward_backward(M, batch, seq, opts):
