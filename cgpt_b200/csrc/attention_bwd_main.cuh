@@ -161,12 +161,14 @@ int launch_backward(void* dq, void* dk, void* dv, const void* dout, const void* 
     CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(qrows) * 2 * sizeof(float), s));
     float* delta_t = static_cast<float*>(scratch);
     float* lse2_t = delta_t + qrows;
+    if (qrows >= (1ll << 31)) return CGPT_ERR_UNSUPPORTED;      // 32-bit row indices in the preparation pass
     const long long prep_rows_per_cta = 8LL * (32 / (D / 8)) * kPrepUnroll;
     const long long prep_need = (qrows + prep_rows_per_cta - 1) / prep_rows_per_cta;
     const long long prep_cap = static_cast<long long>(kNumSMs) *
-                               resident_ctas_per_sm(reinterpret_cast<const void*>(attention_bwd_prep_kernel<T>), 256, 0);
-    attention_bwd_prep_kernel<T><<<static_cast<unsigned>(prep_need < prep_cap ? prep_need : prep_cap), 256, 0, s>>>(
-        delta_t, lse2_t, static_cast<const T*>(dout), static_cast<const T*>(out), lse, dm.batch, dm.sq, dm.hq, D);
+                               resident_ctas_per_sm(reinterpret_cast<const void*>(attention_bwd_prep_kernel<T, D>), 256, 0);
+    attention_bwd_prep_kernel<T, D><<<static_cast<unsigned>(prep_need < prep_cap ? prep_need : prep_cap), 256, 0, s>>>(
+        delta_t, lse2_t, static_cast<const T*>(dout), static_cast<const T*>(out), lse, static_cast<unsigned>(qrows), dm.sq, dm.hq,
+        FastDiv(static_cast<unsigned>(dm.hq)), FastDiv(static_cast<unsigned>(dm.sq)));
     count_launch();
     CGPT_LAUNCH_CHECK();
 

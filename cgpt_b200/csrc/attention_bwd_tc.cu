@@ -103,30 +103,33 @@ template <> __device__ __forceinline__ std::uint32_t pack2<__nv_bfloat16>(float 
 // first use (memory-bound: 2 * D * 2 bytes per row).
 constexpr int kPrepUnroll = 4;
 
-template <typename T>
+template <typename T, int D>
 __global__ void __launch_bounds__(256)
 attention_bwd_prep_kernel(float* __restrict__ delta_t, float* __restrict__ lse2_t, const T* __restrict__ dout,
-                          const T* __restrict__ out, const float* __restrict__ lse, int batch, int sq, int hq, int d) {
-    const int lpr = d / 8;                         // lanes per row (8 or 16)
-    const int rows_per_group = 32 / lpr;
+                          const T* __restrict__ out, const float* __restrict__ lse, unsigned rows, int sq, int hq,
+                          FastDiv div_hq, FastDiv div_sq) {
+    // rows = batch * sq * hq fits 31 bits (a tensor of 2^31 rows of D 16-bit values cannot exist on this device); the row's
+    // (batch, query, head) comes from two multiply-shift divisions, and the lane group's width is a compile-time constant
+    constexpr int lpr = D / 8;                     // lanes per row (8 or 16)
+    constexpr int rows_per_group = 32 / lpr;
     const int lane = threadIdx.x & 31;
     const int sub = lane / lpr, l = lane % lpr;
-    const long long rows = static_cast<long long>(batch) * sq * hq;
-    const long long warp_id = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-    const long long warps_total = static_cast<long long>(gridDim.x) * 8;
-    const long long per_trip = static_cast<long long>(rows_per_group) * kPrepUnroll;
+    const unsigned warp_id = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const unsigned warps_total = gridDim.x * 8;
+    constexpr unsigned per_trip = rows_per_group * kPrepUnroll;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    for (long long base = warp_id * per_trip; base < rows; base += warps_total * per_trip) {
+    for (unsigned base = warp_id * per_trip; base < rows; base += warps_total * per_trip) {
         uint4 a[kPrepUnroll], o[kPrepUnroll];
 #pragma unroll
         for (int u = 0; u < kPrepUnroll; ++u) {
-            const long long row = base + u * rows_per_group + sub;
-            a[u] = row < rows ? __ldcs(reinterpret_cast<const uint4*>(dout + row * d + l * 8)) : zero;
-            o[u] = row < rows ? __ldg(reinterpret_cast<const uint4*>(out + row * d + l * 8)) : zero;
+            const unsigned row = base + u * rows_per_group + sub;
+            const long long off = static_cast<long long>(row) * D + l * 8;
+            a[u] = row < rows ? __ldcs(reinterpret_cast<const uint4*>(dout + off)) : zero;
+            o[u] = row < rows ? __ldg(reinterpret_cast<const uint4*>(out + off)) : zero;
         }
 #pragma unroll
         for (int u = 0; u < kPrepUnroll; ++u) {
-            const long long row = base + u * rows_per_group + sub;
+            const unsigned row = base + u * rows_per_group + sub;
             Pack<T, 8> pa, po;
             *reinterpret_cast<uint4*>(&pa) = a[u];
             *reinterpret_cast<uint4*>(&po) = o[u];
@@ -136,13 +139,13 @@ attention_bwd_prep_kernel(float* __restrict__ delta_t, float* __restrict__ lse2_
             float s = 0.f;
 #pragma unroll
             for (int e = 0; e < 8; ++e) s = fmaf(fa[e], fo[e], s);
+#pragma unroll
             for (int off = lpr >> 1; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
             if (l == 0 && row < rows) {
-                const int h = static_cast<int>(row % hq);
-                const long long bq = row / hq;
-                const int q = static_cast<int>(bq % sq);
-                const long long b = bq / sq;
-                const long long t = (b * hq + h) * sq + q;
+                unsigned bq, h, b, q;
+                div_hq.divmod(row, bq, h);
+                div_sq.divmod(bq, b, q);
+                const long long t = (static_cast<long long>(b) * hq + h) * sq + q;
                 delta_t[t] = s;
                 lse2_t[t] = lse[row] * kLog2e;
             }

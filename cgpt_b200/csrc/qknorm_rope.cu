@@ -20,8 +20,16 @@ constexpr int kQkThreads = 256;
 constexpr int kFwdUnroll = 8;   // row groups a warp has in flight per trip
 constexpr int kBwdUnroll = 4;
 
+// Sum over the lanes that share a row. LPR (lanes per row) known at compile time: an unrolled butterfly; LPR == 0: the
+// run-time width (a real loop: shift, compare and branch around every shuffle).
+template <int LPR>
 __device__ __forceinline__ float group_sum(float v, int lanes_per_row) {
-    for (int o = lanes_per_row >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if constexpr (LPR > 0) {
+#pragma unroll
+        for (int o = LPR >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    } else {
+        for (int o = lanes_per_row >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    }
     return v;
 }
 
@@ -53,18 +61,20 @@ __device__ __forceinline__ void unpack4(float (&out)[4], const uint2& raw) {
 // per token instead of once per row (8 query heads: one table fetch and conversion per 8 rows), and the token / head of
 // a row follow from the run's first row by counting: one division per run, none per row.
 // Row indices fit 31 bits (checked by the host); divisions by heads and seq use precomputed multipliers.
-template <typename T, bool BACKWARD, int U>
+// LPR: head_dim / 8 when the host knows it at compile time (8 or 16: head_dim 64 or 128), else 0 = read from dm.
+template <typename T, bool BACKWARD, int U, int LPR>
 __global__ void __launch_bounds__(kQkThreads)
 qknorm_rope_kernel(T* __restrict__ out_q, T* __restrict__ out_k, const T* __restrict__ in_q, const T* __restrict__ in_k,
                    const T* __restrict__ x_q, const T* __restrict__ x_k, const T* __restrict__ w_q, const T* __restrict__ w_k,
                    const T* __restrict__ cos_t, const T* __restrict__ sin_t, float* __restrict__ dw_partial, QkDims dm,
                    FastDiv div_qh, FastDiv div_kh, FastDiv div_seq) {
-    const int lpr = dm.head_dim / 8;                 // lanes per row
+    const int hd = LPR > 0 ? LPR * 8 : dm.head_dim;    // head_dim (a compile-time constant for the common sizes)
+    const int lpr = LPR > 0 ? LPR : dm.head_dim / 8;   // lanes per row
     const int rows_per_warp = 32 / lpr;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = lane / lpr, l = lane % lpr;      // row slot inside the warp, chunk inside the row
     const int d0 = l * 8;
-    const float inv_d = 1.0f / static_cast<float>(dm.head_dim);
+    const float inv_d = 1.0f / static_cast<float>(hd);
     const int half_rot = dm.rotary_dim / 2;
     const bool rotate = d0 < dm.rotary_dim;
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
@@ -87,13 +97,13 @@ qknorm_rope_kernel(T* __restrict__ out_q, T* __restrict__ out_k, const T* __rest
         const unsigned trips = (rows + group * warps_total - 1) / (group * warps_total);
         for (unsigned trip = 0; trip < trips; ++trip) {
             const unsigned r0 = (trip * warps_total + warp_id) * group + sub * U;   // first row of this lane group's run
-            const long long off0 = static_cast<long long>(r0) * dm.head_dim + d0;
+            const long long off0 = static_cast<long long>(r0) * hd + d0;
             uint4 raw_in[U], raw_x[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const bool active = r0 + u < rows;
-                raw_in[u] = active ? __ldcs(reinterpret_cast<const uint4*>(in + off0 + u * dm.head_dim)) : zero4;
-                if (BACKWARD) raw_x[u] = active ? __ldcs(reinterpret_cast<const uint4*>(xs + off0 + u * dm.head_dim)) : zero4;
+                raw_in[u] = active ? __ldcs(reinterpret_cast<const uint4*>(in + off0 + u * hd)) : zero4;
+                if (BACKWARD) raw_x[u] = active ? __ldcs(reinterpret_cast<const uint4*>(xs + off0 + u * hd)) : zero4;
             }
             unsigned token = div_heads.div(r0);
             unsigned head = r0 - token * div_heads.d;
@@ -102,7 +112,7 @@ qknorm_rope_kernel(T* __restrict__ out_q, T* __restrict__ out_k, const T* __rest
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const bool active = r0 + u < rows;
-                const long long off = off0 + u * dm.head_dim;
+                const long long off = off0 + u * hd;
                 // the rotary tables are small and stay in L1/L2: fetched here, not ahead, to keep registers for the row data
                 if (fetch_tables && active && rotate) {
                     const unsigned pos = token - div_seq.div(token) * div_seq.d + dm.offset;
@@ -118,7 +128,7 @@ qknorm_rope_kernel(T* __restrict__ out_q, T* __restrict__ out_k, const T* __rest
                     float ss = 0.f;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
-                    ss = group_sum(ss, lpr);
+                    ss = group_sum<LPR>(ss, lpr);
                     const float inv = rsqrtf(ss * inv_d + dm.eps);
                     float y[8];
 #pragma unroll
@@ -155,8 +165,8 @@ qknorm_rope_kernel(T* __restrict__ out_q, T* __restrict__ out_k, const T* __rest
                         sx = fmaf(x[i], x[i], sx);
                         sg = fmaf(g[i] * w[i], x[i], sg);
                     }
-                    sx = group_sum(sx, lpr);
-                    sg = group_sum(sg, lpr);
+                    sx = group_sum<LPR>(sx, lpr);
+                    sg = group_sum<LPR>(sg, lpr);
                     const float inv = rsqrtf(sx * inv_d + dm.eps);
                     const float corr = sg * inv_d * inv * inv * inv;
                     float dx[8];
@@ -176,10 +186,10 @@ qknorm_rope_kernel(T* __restrict__ out_q, T* __restrict__ out_k, const T* __rest
 #pragma unroll
             for (int i = 0; i < 8; ++i) red[threadIdx.x][i] = dw[i];
             __syncthreads();
-            for (int col = threadIdx.x; col < dm.head_dim; col += kQkThreads) {
+            for (int col = threadIdx.x; col < hd; col += kQkThreads) {
                 float acc = 0.f;
                 for (int t = col >> 3; t < kQkThreads; t += lpr) acc += red[t][col & 7];
-                dw_partial[(static_cast<long long>(blockIdx.x) * 2 + which) * dm.head_dim + col] = acc;
+                dw_partial[(static_cast<long long>(blockIdx.x) * 2 + which) * hd + col] = acc;
             }
         }
     }
@@ -238,20 +248,22 @@ extern "C" int cgpt_qknorm_rope_forward(void* q, void* k, const void* q_pre, con
                     static_cast<int>(kv_heads), static_cast<int>(head_dim), static_cast<int>(rotary_dim),
                     static_cast<int>(position_offset), epsilon};
     const FastDiv div_qh(static_cast<unsigned>(q_heads)), div_kh(static_cast<unsigned>(kv_heads)), div_seq(static_cast<unsigned>(seq));
-    const void* kernel = dtype == CGPT_DTYPE_F16 ? reinterpret_cast<const void*>(qknorm_rope_kernel<__half, false, kFwdUnroll>)
-                                                 : reinterpret_cast<const void*>(qknorm_rope_kernel<__nv_bfloat16, false, kFwdUnroll>);
-    const unsigned grid = kNumSMs * resident_ctas_per_sm(kernel, kQkThreads, 0);    // every CTA resident: no partial last wave
-    if (dtype == CGPT_DTYPE_F16)
-        qknorm_rope_kernel<__half, false, kFwdUnroll><<<grid, kQkThreads, 0, s>>>(
-            static_cast<__half*>(q), static_cast<__half*>(k), static_cast<const __half*>(q_pre), static_cast<const __half*>(k_pre),
-            nullptr, nullptr, static_cast<const __half*>(q_norm), static_cast<const __half*>(k_norm),
-            static_cast<const __half*>(cos_table), static_cast<const __half*>(sin_table), nullptr, dm, div_qh, div_kh, div_seq);
-    else
-        qknorm_rope_kernel<__nv_bfloat16, false, kFwdUnroll><<<grid, kQkThreads, 0, s>>>(
-            static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(q_pre),
-            static_cast<const __nv_bfloat16*>(k_pre), nullptr, nullptr, static_cast<const __nv_bfloat16*>(q_norm),
-            static_cast<const __nv_bfloat16*>(k_norm), static_cast<const __nv_bfloat16*>(cos_table),
-            static_cast<const __nv_bfloat16*>(sin_table), nullptr, dm, div_qh, div_kh, div_seq);
+#define CGPT_QK_FWD(T, LPR)                                                                                                    \
+    {                                                                                                                          \
+        auto* kernel = qknorm_rope_kernel<T, false, kFwdUnroll, LPR>;                                                         \
+        const unsigned grid = kNumSMs * resident_ctas_per_sm(reinterpret_cast<const void*>(kernel), kQkThreads, 0);           \
+        kernel<<<grid, kQkThreads, 0, s>>>(static_cast<T*>(q), static_cast<T*>(k), static_cast<const T*>(q_pre),              \
+                                           static_cast<const T*>(k_pre), nullptr, nullptr, static_cast<const T*>(q_norm),     \
+                                           static_cast<const T*>(k_norm), static_cast<const T*>(cos_table),                   \
+                                           static_cast<const T*>(sin_table), nullptr, dm, div_qh, div_kh, div_seq);           \
+    }
+    // every CTA resident (no partial last wave); lanes per row as a compile-time constant for the common head sizes
+    if (dtype == CGPT_DTYPE_F16) {
+        if (head_dim == 128) CGPT_QK_FWD(__half, 16) else if (head_dim == 64) CGPT_QK_FWD(__half, 8) else CGPT_QK_FWD(__half, 0)
+    } else {
+        if (head_dim == 128) CGPT_QK_FWD(__nv_bfloat16, 16) else if (head_dim == 64) CGPT_QK_FWD(__nv_bfloat16, 8) else CGPT_QK_FWD(__nv_bfloat16, 0)
+    }
+#undef CGPT_QK_FWD
     count_launch();
     CGPT_LAUNCH_CHECK();
     return CGPT_OK;
@@ -279,36 +291,33 @@ extern "C" int cgpt_qknorm_rope_backward(void* dq_pre, void* dk_pre, void* dq_no
                     static_cast<int>(kv_heads), static_cast<int>(head_dim), static_cast<int>(rotary_dim),
                     static_cast<int>(position_offset), epsilon};
     const FastDiv div_qh(static_cast<unsigned>(q_heads)), div_kh(static_cast<unsigned>(kv_heads)), div_seq(static_cast<unsigned>(seq));
-    const void* kernel = dtype == CGPT_DTYPE_F16 ? reinterpret_cast<const void*>(qknorm_rope_kernel<__half, true, kBwdUnroll>)
-                                                 : reinterpret_cast<const void*>(qknorm_rope_kernel<__nv_bfloat16, true, kBwdUnroll>);
-    const unsigned grid = kNumSMs * resident_ctas_per_sm(kernel, kQkThreads, 0);
+    // the same grid for every instantiation of a dtype (the partial buffer is sized by it): the smallest residency
+    unsigned grid = 0;
     void* scratch = nullptr;
-    CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(grid) * 2 * head_dim * sizeof(float), s));
-    float* partial = static_cast<float*>(scratch);
     const unsigned rgrid = static_cast<unsigned>((2 * head_dim + 31) / 32);
-    if (dtype == CGPT_DTYPE_F16) {
-        qknorm_rope_kernel<__half, true, kBwdUnroll><<<grid, kQkThreads, 0, s>>>(
-            static_cast<__half*>(dq_pre), static_cast<__half*>(dk_pre), static_cast<const __half*>(dq_rot),
-            static_cast<const __half*>(dk_rot), static_cast<const __half*>(q_pre), static_cast<const __half*>(k_pre),
-            static_cast<const __half*>(q_norm), static_cast<const __half*>(k_norm), static_cast<const __half*>(cos_table),
-            static_cast<const __half*>(sin_table), partial, dm, div_qh, div_kh, div_seq);
-        count_launch();
-        CGPT_LAUNCH_CHECK();
-        qknorm_dw_reduce_kernel<__half><<<rgrid, 1024, 0, s>>>(static_cast<__half*>(dq_norm), static_cast<__half*>(dk_norm), partial,
-                                                             static_cast<int>(grid), static_cast<int>(head_dim));
-    } else {
-        qknorm_rope_kernel<__nv_bfloat16, true, kBwdUnroll><<<grid, kQkThreads, 0, s>>>(
-            static_cast<__nv_bfloat16*>(dq_pre), static_cast<__nv_bfloat16*>(dk_pre), static_cast<const __nv_bfloat16*>(dq_rot),
-            static_cast<const __nv_bfloat16*>(dk_rot), static_cast<const __nv_bfloat16*>(q_pre),
-            static_cast<const __nv_bfloat16*>(k_pre), static_cast<const __nv_bfloat16*>(q_norm),
-            static_cast<const __nv_bfloat16*>(k_norm), static_cast<const __nv_bfloat16*>(cos_table),
-            static_cast<const __nv_bfloat16*>(sin_table), partial, dm, div_qh, div_kh, div_seq);
-        count_launch();
-        CGPT_LAUNCH_CHECK();
-        qknorm_dw_reduce_kernel<__nv_bfloat16><<<rgrid, 1024, 0, s>>>(static_cast<__nv_bfloat16*>(dq_norm),
-                                                                    static_cast<__nv_bfloat16*>(dk_norm), partial,
-                                                                    static_cast<int>(grid), static_cast<int>(head_dim));
+#define CGPT_QK_BWD(T, LPR)                                                                                                    \
+    {                                                                                                                          \
+        auto* kernel = qknorm_rope_kernel<T, true, kBwdUnroll, LPR>;                                                          \
+        grid = kNumSMs * resident_ctas_per_sm(reinterpret_cast<const void*>(kernel), kQkThreads, 0);                          \
+        CGPT_TRY(scratch_get(&scratch, static_cast<std::size_t>(grid) * 2 * head_dim * sizeof(float), s));                    \
+        kernel<<<grid, kQkThreads, 0, s>>>(static_cast<T*>(dq_pre), static_cast<T*>(dk_pre), static_cast<const T*>(dq_rot),   \
+                                           static_cast<const T*>(dk_rot), static_cast<const T*>(q_pre),                       \
+                                           static_cast<const T*>(k_pre), static_cast<const T*>(q_norm),                       \
+                                           static_cast<const T*>(k_norm), static_cast<const T*>(cos_table),                   \
+                                           static_cast<const T*>(sin_table), static_cast<float*>(scratch), dm, div_qh, div_kh, \
+                                           div_seq);                                                                          \
+        count_launch();                                                                                                        \
+        CGPT_LAUNCH_CHECK();                                                                                                   \
+        qknorm_dw_reduce_kernel<T><<<rgrid, 1024, 0, s>>>(static_cast<T*>(dq_norm), static_cast<T*>(dk_norm),                 \
+                                                          static_cast<const float*>(scratch), static_cast<int>(grid),         \
+                                                          static_cast<int>(head_dim));                                        \
     }
+    if (dtype == CGPT_DTYPE_F16) {
+        if (head_dim == 128) CGPT_QK_BWD(__half, 16) else if (head_dim == 64) CGPT_QK_BWD(__half, 8) else CGPT_QK_BWD(__half, 0)
+    } else {
+        if (head_dim == 128) CGPT_QK_BWD(__nv_bfloat16, 16) else if (head_dim == 64) CGPT_QK_BWD(__nv_bfloat16, 8) else CGPT_QK_BWD(__nv_bfloat16, 0)
+    }
+#undef CGPT_QK_BWD
     count_launch();
     CGPT_LAUNCH_CHECK();
     return CGPT_OK;
