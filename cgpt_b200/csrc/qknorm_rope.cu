@@ -17,8 +17,11 @@ namespace cgpt {
 namespace {
 
 constexpr int kQkThreads = 256;
-constexpr int kFwdUnroll = 8;   // row groups a warp has in flight per trip
-constexpr int kBwdUnroll = 4;
+// Rows a lane group has in flight per trip. Measured at 32768 tokens, 8 + 2 heads of 128: forward 8 rows (80 registers, 3 CTAs
+// per SM) 38.5 us, 4 rows (55 registers, 4 CTAs) 32.7 us, 2 rows 33.1 us; backward 4 rows (126 registers, 2 CTAs) 62.2 us,
+// 2 rows (74 registers, 3 CTAs) 61.3 us: the kernels are bound by instruction issue, so resident warps beat loads in flight.
+constexpr int kFwdUnroll = 4;
+constexpr int kBwdUnroll = 2;
 
 // Sum over the lanes that share a row. LPR (lanes per row) known at compile time: an unrolled butterfly; LPR == 0: the
 // run-time width (a real loop: shift, compare and branch around every shuffle).
